@@ -1,0 +1,127 @@
+/*
+ * qwc.h -- C ABI of the B200 (sm_100a) quantized-matmul library, libqwcuda.so.
+ *
+ * Every entry point is the CUDA twin of one "door" of the reference's Swift
+ * operator layer (Sources/Operators/QWGEMM).  The reference encodes kernels
+ * into an MTLComputeCommandEncoder and addresses memory through
+ * QWTensorValue / QWWeightView; here an encoder becomes a CUDA stream and a
+ * tensor value becomes a raw device pointer plus extents.  Rules carried over
+ * from the reference ("Encode path allocates nothing",
+ * Sources/Operators/QWGEMM/QWGemm.swift:216-217):
+ *
+ *   - the caller owns every buffer, scratch included;
+ *   - no encode-class call allocates, synchronises or copies host<->device;
+ *   - every refusal happens before the first launch and leaves the stream
+ *     untouched; the status code mirrors QWGemmError
+ *     (Sources/Operators/QWGEMM/QWGemm.swift:66-80) and qwc_last_error()
+ *     returns the message (thread-local).
+ *
+ * Paths in comments are paths inside the reference project.
+ */
+#ifndef QWC_H
+#define QWC_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct qwc_hal qwc_hal; /* device context: replaces QWHal (Sources/Foundation/QWHAL/QWHal.swift:81-235) */
+typedef void* qwc_stream;       /* a cudaStream_t; replaces the MTLComputeCommandEncoder argument */
+
+/* QWGemmError cases (QWGemm.swift:66-80) plus a CUDA runtime failure. */
+enum {
+    QWC_OK = 0,
+    QWC_ERR_BLOCKED = 1,      /* .f3Blocked: the plan has no kernel for this shape */
+    QWC_ERR_BAD_WEIGHTS = 2,  /* .badWeights */
+    QWC_ERR_BAD_SHAPE = 3,    /* .badShape */
+    QWC_ERR_BAD_GEOMETRY = 4, /* .badGeometry */
+    QWC_ERR_CUDA = 5
+};
+
+/* QWWeightView.ContainerKind (Sources/Foundation/QWAlloc/QWWeightView.swift:11-31). */
+enum {
+    QWC_KIND_HQ4_G32_M5 = 0, /* .incumbentHQ4G32: 20-byte block, interleaved nibbles, +1024 decode */
+    QWC_KIND_ROTATED_HQ = 1  /* .rotatedHQ(bits, group): f16 scale, f16 bias, linear bit stream */
+};
+
+/* QWDType subset used by this path (Sources/Foundation/QWCore/QWDType.swift:5-23). */
+enum { QWC_F16 = 0, QWC_F32 = 1 };
+
+/* QWEpilogue (QWGemm.swift:19-22) plus the fused-FWHT mode bit of
+ * qwg_gemv_q4g_silu_pair_dx_h16 (Sources/QWMetal/gemm/qwgemm.metal:204-379). */
+enum { QWC_EPI_NONE = 0, QWC_EPI_SILU_PAIR = 1, QWC_EPI_SILU_PAIR_FWHT = 2 };
+
+/* QWGemmFamily (QWGemm.swift:11-17). */
+enum { QWC_FAMILY_F1_DECODE_GEMV = 1, QWC_FAMILY_F2_LMHEAD_GEMV = 2, QWC_FAMILY_F3_PREFILL_GEMM = 3,
+       QWC_FAMILY_F4_BLOCKED_GEMM = 4, QWC_FAMILY_F5_SKINNY_GEMM = 5 };
+
+/* Which kernel a plan selects. */
+enum { QWC_BACKEND_BLOCKED = 0, QWC_BACKEND_STREAM_MMA = 1, QWC_BACKEND_TCGEN05 = 2, QWC_BACKEND_ROWWISE = 3 };
+
+/* QWWeightView (QWWeightView.swift:9-152): one weight bank, row-major [n][k/group] blocks. */
+typedef struct {
+    const void* blocks; /* device pointer to the first block */
+    int64_t n, k;
+    int32_t kind, bits, group;
+} qwc_weight_view;
+
+/* QWGemmPlan (QWGemm.swift:35-64). */
+typedef struct {
+    int32_t family, backend, epilogue, threads_per_cta;
+    char kernel[48];
+} qwc_plan;
+
+/* ---- context -------------------------------------------------------------- */
+/* QWHal.init (QWHal.swift:81-145).  Allocates a small device status word; the only allocation in the library. */
+int qwc_hal_create(int device, qwc_hal** out);
+void qwc_hal_destroy(qwc_hal* hal);
+const char* qwc_last_error(void);
+/* Synchronises the device and returns the kernels' status word: 0, or the code of the first bounded wait that
+ * gave up (the CUDA stand-in for MTLCommandBuffer.error, Sources/Runtime/QWEngine/Driver/DriverDecode.swift:142-158). */
+int qwc_hal_device_status(qwc_hal* hal, int32_t* status_out);
+int qwc_sm_count(const qwc_hal* hal);
+
+/* ---- weights -------------------------------------------------------------- */
+/* QWWeightView.init? (QWWeightView.swift:108-152): fills *view or refuses (k % group, bank too short, unknown kind). */
+int qwc_weight_view_init(qwc_weight_view* view, const void* blocks, size_t bank_bytes, int64_t n, int64_t k,
+                         int32_t kind, int32_t bits, int32_t group);
+int64_t qwc_block_bytes(int32_t kind, int32_t bits, int32_t group);
+
+/* ---- dispatch table ------------------------------------------------------- */
+/* QWGemm.plan (QWGemm.swift:92-133): pure function of the shape. */
+int qwc_gemm_plan(int64_t m, int64_t n, int64_t k, int32_t kind, int32_t bits, int32_t group, int32_t epilogue,
+                  int64_t vocab, qwc_plan* out);
+
+/* ---- kernels -------------------------------------------------------------- */
+/* QWGemm.encodeFwht32 (QWGemm.swift:285-300): in-place f16 Walsh-Hadamard per aligned 32 block; count % 32 == 0. */
+int qwc_fwht32_f16(qwc_hal* hal, qwc_stream stream, void* x_f16, int64_t count);
+
+/* Host decode twin Pack.dequantHQ4Slab / dequantHQBlockSlab (Sources/Foundation/QWQuant/QWPack.swift:205-321),
+ * on the device: blocks -> [n, k] values, bit-exact with the reference decode.  standard_domain != 0 applies the
+ * inverse rotation (FWHT-32).  out_dtype QWC_F32, or QWC_F16 (one extra rounding). */
+int qwc_dequant(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, void* out, int32_t out_dtype,
+                int32_t standard_domain);
+
+/* The single matmul door: QWGemm.encode / encodeH16 (QWGemm.swift:135-283), QWGemmAQ.encode / encodeDecodeT4
+ * (Sources/Operators/QWGEMM/QWGemmAQ.swift:192-304), the batched verify doors
+ * (Sources/Runtime/QWEngine/SpeculativeMTP/QWMTPBatchedMLP.swift:92-288) and the prefill doors
+ * QWGemm.encodeNaxF32 / encodeDenseProjF32 (Sources/Operators/QWGEMM/QWGemmF32.swift:366-441).
+ *   y[m, n_out] = epilogue( rot(x)[m, k] . W_rot[n, k]^T ),  f32 accumulate.
+ * x: f16 [m, k] rows ldx apart.  x_is_rotated == 0: x is in the standard basis and is rotated inside the call
+ * (FWHT-32 along k, rounded once to f16); != 0: x already is (the reference's dataflow).
+ * epilogue NONE: n_out = n.  SILU_PAIR: rows [0, n/2) are gate, [n/2, n) up; n_out = n/2,
+ * y = silu(gate) * up.  SILU_PAIR_FWHT: same, then FWHT-32 along n_out (n_out % 32 == 0).
+ * y: f16 or f32 [m, n_out] rows ldy apart.  workspace may be NULL when qwc_gemm_workspace_bytes() is 0. */
+int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx,
+             void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace,
+             size_t workspace_bytes);
+size_t qwc_gemm_workspace_bytes(const qwc_hal* hal, const qwc_weight_view* w, int64_t m, int32_t epilogue,
+                                int32_t x_is_rotated);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QWC_H */

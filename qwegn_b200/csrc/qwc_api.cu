@@ -1,0 +1,209 @@
+// C ABI of libqwcuda.so: context, weight-view validation, the dispatch table and the matmul door.
+// Host logic mirrors the reference's Swift operator layer (Sources/Operators/QWGEMM/QWGemm.swift,
+// QWGemmAQ.swift, QWGemmF32.swift; Sources/Foundation/QWAlloc/QWWeightView.swift): same refusals, same order
+// (every check happens before the first launch).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "qwc_common.cuh"
+
+int qwc_launch_dequant(const qwc_hal*, cudaStream_t, const qwc_weight_view*, void*, int, int);
+int qwc_launch_fwht32_f16(const qwc_hal*, cudaStream_t, void*, int64_t);
+int qwc_launch_gemv(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int,
+                    int64_t, int, int, bool);
+
+static thread_local char g_err[512] = "";
+
+int qwc_fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+void qwc_clear_error() { g_err[0] = 0; }
+
+extern "C" {
+
+const char* qwc_last_error(void) { return g_err; }
+
+int qwc_hal_create(int device, qwc_hal** out) {
+    qwc_clear_error();
+    if (!out) return qwc_fail(QWC_ERR_BAD_SHAPE, "qwc_hal_create: out is null");
+    *out = nullptr;
+    int count = 0;
+    QWC_CUDA_TRY(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return qwc_fail(QWC_ERR_CUDA, "device %d out of range (%d visible)", device, count);
+    QWC_CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    QWC_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return qwc_fail(QWC_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+    qwc_hal* h = new (std::nothrow) qwc_hal();
+    if (!h) return qwc_fail(QWC_ERR_CUDA, "out of host memory");
+    h->device = device;
+    h->sm_count = prop.multiProcessorCount;
+    h->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+    cudaError_t e = cudaMalloc(&h->status, 4 * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMemset(h->status, 0, 4 * sizeof(int32_t));
+    if (e != cudaSuccess) {
+        delete h;
+        return qwc_fail(QWC_ERR_CUDA, "status word: %s", cudaGetErrorString(e));
+    }
+    *out = h;
+    return QWC_OK;
+}
+
+void qwc_hal_destroy(qwc_hal* hal) {
+    if (!hal) return;
+    cudaFree(hal->status);
+    delete hal;
+}
+
+int qwc_hal_device_status(qwc_hal* hal, int32_t* status_out) {
+    qwc_clear_error();
+    if (!hal || !status_out) return qwc_fail(QWC_ERR_BAD_SHAPE, "null argument");
+    QWC_CUDA_TRY(cudaDeviceSynchronize());
+    QWC_CUDA_TRY(cudaMemcpy(status_out, hal->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    return QWC_OK;
+}
+
+int qwc_sm_count(const qwc_hal* hal) { return hal ? hal->sm_count : 0; }
+
+int64_t qwc_block_bytes(int32_t kind, int32_t bits, int32_t group) {
+    if (kind == QWC_KIND_HQ4_G32_M5) return 20;
+    if (kind == QWC_KIND_ROTATED_HQ) return static_cast<int64_t>(group) * bits / 8 + 4;
+    return 0;
+}
+
+// QWWeightView.init? (QWWeightView.swift:108-152): k % group == 0 and the bank must hold n * (k/group) blocks.
+int qwc_weight_view_init(qwc_weight_view* view, const void* blocks, size_t bank_bytes, int64_t n, int64_t k,
+                         int32_t kind, int32_t bits, int32_t group) {
+    qwc_clear_error();
+    if (!view) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "view is null");
+    if (kind == QWC_KIND_HQ4_G32_M5) {
+        bits = 4;
+        group = 32;
+    } else if (kind == QWC_KIND_ROTATED_HQ) {
+        const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 6 || bits == 8;
+        const bool group_ok = group == 32 || group == 64 || group == 128 || group == 256;
+        if (!bits_ok || !group_ok) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "rotatedHQ(%d, %d) is not a container of the family", bits, group);
+    } else {
+        return qwc_fail(QWC_ERR_BAD_WEIGHTS, "unknown container kind %d", kind);
+    }
+    if (n <= 0 || k <= 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "empty bank (n=%lld k=%lld)", (long long)n, (long long)k);
+    if (k % group != 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "k=%lld is not a multiple of group %d", (long long)k, group);
+    const int64_t need = n * (k / group) * qwc_block_bytes(kind, bits, group);
+    if (bank_bytes < static_cast<size_t>(need))
+        return qwc_fail(QWC_ERR_BAD_WEIGHTS, "bank holds %zu bytes, view needs %lld", bank_bytes, (long long)need);
+    if (!blocks) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "blocks is null");
+    if (reinterpret_cast<uintptr_t>(blocks) % 4 != 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "blocks must be 4-byte aligned");
+    view->blocks = blocks;
+    view->n = n;
+    view->k = k;
+    view->kind = kind;
+    view->bits = bits;
+    view->group = group;
+    return QWC_OK;
+}
+
+// QWGemmShape.family + QWGemm.plan (QWGemm.swift:24-33, 92-133) with the live thresholds of the shipped engine
+// (GEMV at M = 1, batched verify for 2 <= M <= 16, tensor GEMM above; QWGemmF32.swift:413-440).
+int qwc_gemm_plan(int64_t m, int64_t n, int64_t k, int32_t kind, int32_t bits, int32_t group, int32_t epilogue,
+                  int64_t vocab, qwc_plan* out) {
+    qwc_clear_error();
+    if (!out) return qwc_fail(QWC_ERR_BAD_SHAPE, "plan out is null");
+    memset(out, 0, sizeof(*out));
+    if (m <= 0 || n <= 0 || k <= 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "m, n, k must be positive");
+    int fam;
+    if (m == 1 && vocab > 0 && n == vocab) fam = QWC_FAMILY_F2_LMHEAD_GEMV;
+    else if (m == 1) fam = QWC_FAMILY_F1_DECODE_GEMV;
+    else if (m >= 512) fam = QWC_FAMILY_F3_PREFILL_GEMM;
+    else if (m <= 8) fam = QWC_FAMILY_F5_SKINNY_GEMM;
+    else fam = QWC_FAMILY_F4_BLOCKED_GEMM;
+    out->family = fam;
+    out->epilogue = epilogue;
+    qwc_weight_view v{nullptr, n, k, kind, bits, group};
+    if (kind == QWC_KIND_HQ4_G32_M5) { v.bits = 4; v.group = 32; }
+    const int fmt = qwc_fmt_of(v);
+    if (fmt == FMT_UNSUPPORTED || k % v.group != 0 || epilogue < QWC_EPI_NONE || epilogue > QWC_EPI_SILU_PAIR_FWHT) {
+        out->backend = QWC_BACKEND_BLOCKED;
+        return QWC_OK;
+    }
+    const int64_t row_bytes = (k / v.group) * qwc_block_bytes(v.kind, v.bits, v.group);
+    const char* fname = fmt == FMT_HQ4_G32_M5 ? "hq4g32m5" : (fmt == FMT_HQ8_G32 ? "hq8g32" : "hq4g64");
+    if (row_bytes % 16 != 0) {
+        out->backend = QWC_BACKEND_ROWWISE;
+        out->threads_per_cta = 256;
+        snprintf(out->kernel, sizeof(out->kernel), "qwc_gemv_rowwise_%s", fname);
+    } else {
+        out->backend = QWC_BACKEND_STREAM_MMA;
+        out->threads_per_cta = 16 * 32;
+        snprintf(out->kernel, sizeof(out->kernel), "qwc_gemv_stream_%s_m%d", fname, m <= 8 ? 8 : 16);
+    }
+    return QWC_OK;
+}
+
+int qwc_fwht32_f16(qwc_hal* hal, qwc_stream stream, void* x_f16, int64_t count) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (count < 0 || count % 32 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "count=%lld is not a multiple of 32", (long long)count);
+    if (count > 0 && !x_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "x is null");
+    return qwc_launch_fwht32_f16(hal, static_cast<cudaStream_t>(stream), x_f16, count);
+}
+
+static int check_view(const qwc_weight_view* w) {
+    if (!w || !w->blocks) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "weight view is null");
+    if (w->n <= 0 || w->k <= 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "empty weight view");
+    if (qwc_fmt_of(*w) == FMT_UNSUPPORTED)
+        return qwc_fail(QWC_ERR_BAD_WEIGHTS, "no kernel for container kind %d bits %d group %d (supported: HQ4_G32_M5, HQ8_G32, HQ4_G64)",
+                        w->kind, w->bits, w->group);
+    if (w->k % w->group != 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "k=%lld is not a multiple of group %d", (long long)w->k, w->group);
+    if (reinterpret_cast<uintptr_t>(w->blocks) % 4 != 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "blocks must be 4-byte aligned");
+    if (w->n >= (int64_t(1) << 31) || w->k >= (int64_t(1) << 31)) return qwc_fail(QWC_ERR_BAD_SHAPE, "n, k must fit 31 bits");
+    return QWC_OK;
+}
+
+int qwc_dequant(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, void* out, int32_t out_dtype,
+                int32_t standard_domain) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (int rc = check_view(w)) return rc;
+    if (!out) return qwc_fail(QWC_ERR_BAD_SHAPE, "out is null");
+    if (out_dtype != QWC_F16 && out_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "out dtype must be f16 or f32");
+    return qwc_launch_dequant(hal, static_cast<cudaStream_t>(stream), w, out, out_dtype, standard_domain);
+}
+
+size_t qwc_gemm_workspace_bytes(const qwc_hal*, const qwc_weight_view*, int64_t, int32_t, int32_t) { return 0; }
+
+int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx,
+             void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace,
+             size_t workspace_bytes) {
+    (void)workspace;
+    (void)workspace_bytes;
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (int rc = check_view(w)) return rc;
+    if (m < 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "m=%lld is negative", (long long)m);
+    if (m == 0) return QWC_OK;
+    if (!x_f16 || !y) return qwc_fail(QWC_ERR_BAD_SHAPE, "x or y is null");
+    if (y_dtype != QWC_F16 && y_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "y dtype must be f16 or f32");
+    if (epilogue < QWC_EPI_NONE || epilogue > QWC_EPI_SILU_PAIR_FWHT) return qwc_fail(QWC_ERR_BAD_SHAPE, "unknown epilogue %d", epilogue);
+    int64_t n_out = w->n;
+    if (epilogue != QWC_EPI_NONE) {
+        // QWGemm.encode refuses an odd packed gate||up bank (QWGemm.swift:135-283: badWeights).
+        if (w->n % 2 != 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "silu-pair needs an even row count, got n=%lld", (long long)w->n);
+        n_out = w->n / 2;
+        if (epilogue == QWC_EPI_SILU_PAIR_FWHT && n_out % 32 != 0)
+            return qwc_fail(QWC_ERR_BAD_GEOMETRY, "fused FWHT needs n/2 %% 32 == 0, got %lld", (long long)n_out);
+    }
+    if (ldx < w->k) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldx=%lld < k=%lld", (long long)ldx, (long long)w->k);
+    if (ldy < n_out) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldy=%lld < output width %lld", (long long)ldy, (long long)n_out);
+    if (reinterpret_cast<uintptr_t>(x_f16) % 2 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "x must be 2-byte aligned");
+    return qwc_launch_gemv(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, epilogue,
+                           x_is_rotated, true);
+}
+
+}  // extern "C"

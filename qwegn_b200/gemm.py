@@ -1,0 +1,213 @@
+"""Host-side mirror of the reference's QWGEMM operator surface over the C ABI.
+
+Names follow Sources/Operators/QWGEMM/QWGemm.swift: `QWGemm.plan`,
+`QWGemm.encode`, `QWGemm.encodeH16`, `QWGemm.encodeFwht32`, `QWGemmError`,
+`QWWeightView`.  An encoder is a CUDA stream, a tensor value is a torch CUDA
+tensor (torch is used for device memory and streams only; every kernel is in
+libqwcuda.so).  Encode calls allocate nothing: the caller passes the output.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import (EPI_NONE, EPI_SILU_PAIR, EPI_SILU_PAIR_FWHT, F16, F32, KIND_HQ4_G32_M5, KIND_ROTATED_HQ,
+                   PlanC, WeightViewC)
+
+_CODE_NAMES = {1: "f3Blocked", 2: "badWeights", 3: "badShape", 4: "badGeometry", 5: "cuda"}
+
+
+class QWGemmError(RuntimeError):
+    """QWGemmError (QWGemm.swift:66-80): .f3Blocked / .badWeights / .badShape / .badGeometry, plus .cuda."""
+
+    def __init__(self, code: int, message: str):
+        self.code = code
+        self.case = _CODE_NAMES.get(code, f"code{code}")
+        super().__init__(f"QWGEMM: {self.case} - {message}")
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise QWGemmError(rc, _lib.last_error())
+
+
+@dataclass(frozen=True)
+class ContainerKind:
+    """QWWeightView.ContainerKind (Sources/Foundation/QWAlloc/QWWeightView.swift:11-31)."""
+    kind: int
+    bits: int
+    group: int
+
+    @property
+    def block_bytes(self) -> int:
+        return 20 if self.kind == KIND_HQ4_G32_M5 else self.group * self.bits // 8 + 4
+
+    def row_bytes(self, k: int) -> int:
+        return (k // self.group) * self.block_bytes
+
+
+incumbentHQ4G32 = ContainerKind(KIND_HQ4_G32_M5, 4, 32)
+
+
+def rotatedHQ(bits: int, group: int) -> ContainerKind:
+    return ContainerKind(KIND_ROTATED_HQ, bits, group)
+
+
+CONTAINERS = {"HQ4_G32": incumbentHQ4G32, "HQ8_G32": rotatedHQ(8, 32), "HQ4_G64": rotatedHQ(4, 64)}
+
+
+class QWHal:
+    """Device context: stands where QWHal (Sources/Foundation/QWHAL/QWHal.swift:81-235) stands in the reference."""
+
+    def __init__(self, device: int = 0):
+        lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("qwegn_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        torch.cuda.init()
+        h = ctypes.c_void_p()
+        _check(lib.qwc_hal_create(device, ctypes.byref(h)))
+        self._h = h
+        self._lib = lib
+
+    @property
+    def handle(self) -> ctypes.c_void_p:
+        return self._h
+
+    @property
+    def sm_count(self) -> int:
+        return int(self._lib.qwc_sm_count(self._h))
+
+    def device_status(self) -> int:
+        """Synchronise and return the kernels' status word (0 = no bounded wait gave up)."""
+        out = ctypes.c_int32(0)
+        _check(self._lib.qwc_hal_device_status(self._h, ctypes.byref(out)))
+        return int(out.value)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.qwc_hal_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _stream_ptr(stream: Optional[torch.cuda.Stream]) -> ctypes.c_void_p:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+class QWWeightView:
+    """QWWeightView (QWWeightView.swift:9-152): one bank of packed blocks resident in device memory."""
+
+    def __init__(self, blocks: torch.Tensor, n: int, k: int, container: ContainerKind = incumbentHQ4G32,
+                 byte_offset: int = 0):
+        if blocks.dtype != torch.uint8 or not blocks.is_cuda or not blocks.is_contiguous():
+            raise QWGemmError(2, "blocks must be a contiguous CUDA uint8 tensor")
+        self.bank = blocks
+        self.container = container
+        self.c = WeightViewC()
+        avail = blocks.numel() - byte_offset
+        if avail < 0:
+            raise QWGemmError(2, "byte offset beyond the bank")
+        _check(_lib.load().qwc_weight_view_init(ctypes.byref(self.c), ctypes.c_void_p(blocks.data_ptr() + byte_offset),
+                                                avail, n, k, container.kind, container.bits, container.group))
+
+    @property
+    def n(self) -> int:
+        return int(self.c.n)
+
+    @property
+    def k(self) -> int:
+        return int(self.c.k)
+
+    @property
+    def isRotated(self) -> bool:
+        return True
+
+    def rows(self, r0: int, r1: int) -> "QWWeightView":
+        """A view of rows [r0, r1) (column-parallel shard, or one expert of a stacked bank)."""
+        rb = self.container.row_bytes(self.k)
+        base = self.c.blocks - self.bank.data_ptr()
+        return QWWeightView(self.bank, r1 - r0, self.k, self.container, byte_offset=base + r0 * rb)
+
+
+@dataclass(frozen=True)
+class QWGemmPlan:
+    family: int
+    backend: int
+    epilogue: int
+    threadsPerTG: int
+    kernel: str
+
+
+class QWGemm:
+    """The matmul door (QWGemm.swift:82-330)."""
+
+    @staticmethod
+    def plan(m: int, n: int, k: int, container: ContainerKind = incumbentHQ4G32, epi: int = EPI_NONE,
+             vocab: int = 0) -> QWGemmPlan:
+        out = PlanC()
+        _check(_lib.load().qwc_gemm_plan(m, n, k, container.kind, container.bits, container.group, epi, vocab,
+                                         ctypes.byref(out)))
+        return QWGemmPlan(out.family, out.backend, out.epilogue, out.threads_per_cta, out.kernel.decode())
+
+    @staticmethod
+    def encode(hal: QWHal, w: QWWeightView, x: torch.Tensor, y: torch.Tensor, epi: int = EPI_NONE,
+               x_is_rotated: bool = False, stream: Optional[torch.cuda.Stream] = None,
+               workspace: Optional[torch.Tensor] = None) -> None:
+        """y[m, n_out] = epilogue(rot(x) . W_rot^T).  x f16 [m, k] (or [k]); y f16/f32 [m, n_out] (or [n_out])."""
+        if x.dtype != torch.float16 or not x.is_cuda:
+            raise QWGemmError(3, "x must be a CUDA float16 tensor")
+        if y.dtype not in (torch.float16, torch.float32) or not y.is_cuda:
+            raise QWGemmError(3, "y must be a CUDA float16/float32 tensor")
+        x2 = x if x.dim() == 2 else x.view(1, -1)
+        y2 = y if y.dim() == 2 else y.view(1, -1)
+        if x2.stride(1) != 1 or y2.stride(1) != 1:
+            raise QWGemmError(3, "x and y rows must be contiguous")
+        m = x2.shape[0]
+        if x2.shape[1] != w.k:
+            raise QWGemmError(3, f"x has {x2.shape[1]} columns, the bank has k={w.k}")
+        n_out = w.n if epi == EPI_NONE else w.n // 2
+        if y2.shape[0] != m or y2.shape[1] != n_out:
+            raise QWGemmError(3, f"y is {tuple(y2.shape)}, expected ({m}, {n_out})")
+        ws_ptr, ws_bytes = (None, 0) if workspace is None else (workspace.data_ptr(), workspace.numel() * workspace.element_size())
+        _check(_lib.load().qwc_gemm(hal.handle, _stream_ptr(stream), ctypes.byref(w.c), x2.data_ptr(), m,
+                                    x2.stride(0) if m > 1 else max(x2.stride(0), w.k), y2.data_ptr(),
+                                    F16 if y.dtype == torch.float16 else F32,
+                                    y2.stride(0) if m > 1 else max(y2.stride(0), n_out), epi, int(x_is_rotated),
+                                    ws_ptr, ws_bytes))
+
+    # The reference's f16-store door (QWGemm.swift:137) is the same call with an f16 output tensor.
+    encodeH16 = encode
+
+    @staticmethod
+    def workspaceBytes(hal: QWHal, w: QWWeightView, m: int, epi: int = EPI_NONE, x_is_rotated: bool = False) -> int:
+        return int(_lib.load().qwc_gemm_workspace_bytes(hal.handle, ctypes.byref(w.c), m, epi, int(x_is_rotated)))
+
+    @staticmethod
+    def encodeFwht32(hal: QWHal, x: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """In-place activation rotation (QWGemm.swift:285-300)."""
+        if x.dtype != torch.float16 or not x.is_cuda or not x.is_contiguous():
+            raise QWGemmError(3, "x must be a contiguous CUDA float16 tensor")
+        _check(_lib.load().qwc_fwht32_f16(hal.handle, _stream_ptr(stream), x.data_ptr(), x.numel()))
+
+    @staticmethod
+    def dequant(hal: QWHal, w: QWWeightView, out: torch.Tensor, standard_domain: bool = False,
+                stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Device twin of Pack.dequantHQ4Slab / dequantHQBlockSlab (Sources/Foundation/QWQuant/QWPack.swift:205-321)."""
+        if out.dtype not in (torch.float16, torch.float32) or not out.is_cuda or not out.is_contiguous():
+            raise QWGemmError(3, "out must be a contiguous CUDA float16/float32 tensor")
+        if out.numel() != w.n * w.k:
+            raise QWGemmError(3, f"out has {out.numel()} elements, expected {w.n * w.k}")
+        _check(_lib.load().qwc_dequant(hal.handle, _stream_ptr(stream), ctypes.byref(w.c), out.data_ptr(),
+                                       F16 if out.dtype == torch.float16 else F32, int(standard_domain)))
