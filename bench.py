@@ -1,0 +1,361 @@
+#!/usr/bin/env python3
+"""Headline benchmark: HQ4_G32 dequant-GEMV effective HBM bandwidth (M = 1) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--sections LIST]
+
+One step = one decode GEMV y[1, N] = x[1, K] . W^T over one packed HQ4_G32 weight bank (N = 17408, K = 5120,
+the M = 1 point of the speculative-verify sweep).  The timed loop rotates through enough distinct weight banks
+to exceed the 126 MB L2, so every step streams its weights from HBM.  Synthetic data: W ~ N(0, 0.02) (seeded)
+quantized on the device by the library's own packer; x ~ N(0, 1) f16.
+
+`--impl reference` times the CPU restatement of the reference's path (oracle/) on the host cores for the same
+metric.  Prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOAD = {"name": "verify-sweep M=1 point: HQ4_G32 GEMV N=17408 K=5120", "n": 17408, "k": 5120, "m": 1}
+METRIC = "HQ4_G32 dequant-GEMV effective HBM bandwidth (M=1)"
+UNIT = "GB/s"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def gemv_bytes(n, k, m, block_bytes=20, group=32, out_bytes=4):
+    """Algorithmic bytes of one call: packed weights + activations + outputs."""
+    return n * (k // group) * block_bytes + m * k * 2 + m * n * out_bytes
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 0)),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", 0)), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except (ValueError, IndexError):
+            return local_rank
+    return local_rank
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def run_reference(args):
+    """The reference's CPU path for this metric (fused dequant-GEMV restatement, all host threads)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import qw_oracle as qo
+    qo.build()
+    n, k, m = WORKLOAD["n"], WORKLOAD["k"], WORKLOAD["m"]
+    rng = np.random.default_rng(1)
+    w = rng.normal(0.0, 0.02, (n, k)).astype(np.float32)
+    blocks = qo.quantize(w, qo.HQ4_G32)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    nbytes = gemv_bytes(n, k, m)
+    for _ in range(max(args.warmup, 1)):
+        qo.matmul(blocks, qo.HQ4_G32, x)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        qo.matmul(blocks, qo.HQ4_G32, x)
+    dt = time.perf_counter() - t0
+    val = nbytes * args.steps / dt / 1e9
+    cores = qo.num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 weights x f16 activations, f64 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "n": n, "k": k, "m": m, "format": "HQ4_G32"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{args.steps} full GEMV calls of the workload (the reference ships no fused CPU kernel; "
+                                   "this is the C restatement of its decode + group dot, OpenMP over rows)"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def time_region(fn, steps, dist, stream):
+    """Barrier + synchronize on both sides, CUDA events on the launching stream, max over ranks (ms)."""
+    import torch
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(steps):
+        fn(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def make_banks(q, hal, n, k, container, copies, seed):
+    import torch
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    banks = []
+    for _ in range(copies):
+        w = torch.randn((n, k), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+        bank = q.QWGemm.quantize(hal, w, container)
+        banks.append(q.QWWeightView(bank, n, k, container))
+        del w
+    return banks
+
+
+def bench_gemv_point(q, hal, n, k, m, cname, steps, warmup, dist=None, seed=0):
+    """Device-resident timing of one (format, M) point; returns (ms_per_step, bytes_per_step, banks, x, y)."""
+    import torch
+    cont = q.CONTAINERS[cname]
+    per_bank = n * cont.row_bytes(k)
+    copies = max(2, -(-3 * L2_BYTES // per_bank))   # >= 3x L2 of distinct weights in rotation
+    banks = make_banks(q, hal, n, k, cont, copies, seed)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed + 1000)
+    x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32).to(torch.float16)
+    y = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def step(i):
+        q.QWGemm.encode(hal, banks[i % copies], x, y)
+
+    for i in range(warmup):
+        step(i)
+    ms = time_region(step, steps, dist, stream)
+    nbytes = gemv_bytes(n, k, m, cont.block_bytes, cont.group)
+    return ms / steps, nbytes, banks, x, y
+
+
+def run_ours(args):
+    import torch
+    import qwegn_b200 as q
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    hal = q.QWHal(local_rank)
+    peaks = measured_peaks()
+    n, k, m = WORKLOAD["n"], WORKLOAD["k"], WORKLOAD["m"]
+    sections = set(args.sections.split(",")) if args.sections else {"sweep", "c1", "cpu"}
+
+    # ---- headline: device-resident GEMV, weights rotating through > L2 of distinct banks -------------------
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    cont = q.CONTAINERS["HQ4_G32"]
+    per_bank = n * cont.row_bytes(k)
+    copies = max(2, -(-3 * L2_BYTES // per_bank))
+    banks = make_banks(q, hal, n, k, cont, copies, seed=rank)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234 + rank)
+    x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32).to(torch.float16)
+    y = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def step(i):
+        q.QWGemm.encode(hal, banks[i % copies], x, y)
+
+    for i in range(args.warmup):
+        step(i)
+    sampler.start()
+    ms = time_region(step, args.steps, dist, stream)
+    clocks = sampler.stop()
+    nbytes = gemv_bytes(n, k, m)
+    ms_per_step = ms / args.steps
+    value = world * nbytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public API with host buffers: H2D of x and D2H of y inside the timed region ----
+    x_host = x.cpu().pin_memory()
+    y_host = torch.empty((m, n), dtype=torch.float32).pin_memory()
+    x_dev = torch.empty_like(x)
+
+    def step_e2e(i):
+        x_dev.copy_(x_host, non_blocking=True)
+        q.QWGemm.encode(hal, banks[i % copies], x_dev, y)
+        y_host.copy_(y, non_blocking=True)
+        stream.synchronize()   # the caller reads y on the host every step
+
+    for i in range(args.warmup):
+        step_e2e(i)
+    ms_e2e = time_region(step_e2e, args.steps, dist, stream)
+    e2e_val = world * nbytes / (ms_e2e / args.steps * 1e-3) / 1e9
+
+    status = hal.device_status()
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 (f16 weights decoded from u4, f16 activations, f32 accumulate)", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "n": n, "k": k, "m": m, "format": "HQ4_G32",
+                   "l2": f"rotation over {copies} distinct weight banks ({copies * per_bank / 1e6:.0f} MB > 126 MB L2)",
+                   "parallelism": "one replica of the projection per GPU (column-parallel shards, no collective)" if world > 1 else "1 GPU"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel() * 2),
+                "d2h_bytes_per_step": int(y_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "hbm", "achieved": nbytes / (ms_per_step * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": nbytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": peaks["source"], "kernel": "qwc_gemv_stream_kernel<HQ4_G32_M5, M<=8>",
+                     "algorithmic_bytes_per_launch": nbytes},
+        "device_status": status,
+    }
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            line["roofline"]["traffic"] = json.load(open(traffic_file)).get("gemv_hq4g32_m1_bytes_per_launch")
+        except (ValueError, OSError):
+            pass
+
+    extra = {}
+    if rank == 0 and world == 1:
+        del banks
+        torch.cuda.empty_cache()
+        if "c1" in sections:
+            t, b, *_ = bench_gemv_point(q, hal, 12288, 4096, 1, "HQ4_G32", args.steps, args.warmup)
+            extra["c1_gemv_N12288_K4096"] = {"GBps": b / (t * 1e-3) / 1e9, "us": t * 1e3, "frac_of_peak": b / (t * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        if "sweep" in sections:
+            sweep = {}
+            for cname in ("HQ4_G32", "HQ8_G32", "HQ4_G64"):
+                for mm in (1, 2, 4, 8, 16):
+                    t, b, *_ = bench_gemv_point(q, hal, n, k, mm, cname, max(20, args.steps // 4), args.warmup)
+                    sweep[f"{cname}_M{mm}"] = {"GBps": round(b / (t * 1e-3) / 1e9, 1), "us": round(t * 1e3, 2)}
+                    torch.cuda.empty_cache()
+            extra["verify_sweep_N17408_K5120"] = sweep
+        if "cpu" in sections:
+            line["cpu_baseline"] = cpu_baseline(q, hal, n, k, m)
+    if extra:
+        line["extra"] = extra
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_baseline(q, hal, n, k, m):
+    """The CPU restatement timed on this box's host cores on a bounded sample, and used as the checker of the
+    device result at the timed shape."""
+    import numpy as np
+    import torch
+    from oracle import qw_oracle as qo
+    qo.build()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    w = torch.randn((n, k), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+    bank = q.QWGemm.quantize(hal, w, q.CONTAINERS["HQ4_G32"])
+    view = q.QWWeightView(bank, n, k, q.CONTAINERS["HQ4_G32"])
+    x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32).to(torch.float16)
+    y = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    q.QWGemm.encode(hal, view, x, y)
+    blocks = bank.cpu().numpy().reshape(n, k // 32, 20)
+    xh = x.cpu().numpy()
+    yref = qo.matmul(blocks, qo.HQ4_G32, xh)
+    err = float(np.abs(y.cpu().numpy() - yref).max() / np.abs(yref).max())
+    qo.matmul(blocks, qo.HQ4_G32, xh)
+    reps, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < 10.0 and reps < 500:
+        qo.matmul(blocks, qo.HQ4_G32, xh)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": gemv_bytes(n, k, m) / dt / 1e9, "unit": UNIT, "cores": qo.num_threads(), "kind": "port",
+            "sample": f"{reps} full GEMV calls of the workload in ~10 s", "ms_per_call": dt * 1e3,
+            "device_vs_cpu_max_rel_err": err}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sections", default="", help="comma list of extra sections at N=1: sweep,c1,cpu")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        if args.steps > 200:
+            args.steps = 200
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

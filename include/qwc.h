@@ -105,6 +105,14 @@ int qwc_fwht32_f16(qwc_hal* hal, qwc_stream stream, void* x_f16, int64_t count);
 int qwc_dequant(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, void* out, int32_t out_dtype,
                 int32_t standard_domain);
 
+/* Load-time quantizer: HQ4Quantizer / qwg_quantize_bf16_to_hq4_g32_m5 (Sources/Foundation/QWLoad,
+ * Sources/QWMetal/quant/qw_online_quant.metal:17-55) and the Python packers it mirrors
+ * (Scripts/quantize/hq4.py:54-123, hq_blocks.py:436-517).  w: f32 [n, k] row-major on the device; blocks_out
+ * receives n * (k/group) blocks whose bytes equal the Python packer's.  A non-finite weight sets the device
+ * status word (the Python packer raises). */
+int qwc_quantize(qwc_hal* hal, qwc_stream stream, const float* w_f32, int64_t n, int64_t k, int32_t kind, int32_t bits,
+                 int32_t group, void* blocks_out);
+
 /* The single matmul door: QWGemm.encode / encodeH16 (QWGemm.swift:135-283), QWGemmAQ.encode / encodeDecodeT4
  * (Sources/Operators/QWGEMM/QWGemmAQ.swift:192-304), the batched verify doors
  * (Sources/Runtime/QWEngine/SpeculativeMTP/QWMTPBatchedMLP.swift:92-288) and the prefill doors

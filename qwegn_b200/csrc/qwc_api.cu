@@ -11,6 +11,7 @@
 
 int qwc_launch_dequant(const qwc_hal*, cudaStream_t, const qwc_weight_view*, void*, int, int);
 int qwc_launch_fwht32_f16(const qwc_hal*, cudaStream_t, void*, int64_t);
+int qwc_launch_quantize(const qwc_hal*, cudaStream_t, const float*, int64_t, int64_t, int, void*);
 int qwc_launch_gemv(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int,
                     int64_t, int, int, bool);
 
@@ -174,6 +175,17 @@ int qwc_dequant(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, void*
     if (!out) return qwc_fail(QWC_ERR_BAD_SHAPE, "out is null");
     if (out_dtype != QWC_F16 && out_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "out dtype must be f16 or f32");
     return qwc_launch_dequant(hal, static_cast<cudaStream_t>(stream), w, out, out_dtype, standard_domain);
+}
+
+int qwc_quantize(qwc_hal* hal, qwc_stream stream, const float* w_f32, int64_t n, int64_t k, int32_t kind, int32_t bits,
+                 int32_t group, void* blocks_out) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    qwc_weight_view v{blocks_out, n, k, kind, bits, group};
+    if (kind == QWC_KIND_HQ4_G32_M5) { v.bits = 4; v.group = 32; }
+    if (int rc = check_view(&v)) return rc;
+    if (!w_f32) return qwc_fail(QWC_ERR_BAD_SHAPE, "w is null");
+    return qwc_launch_quantize(hal, static_cast<cudaStream_t>(stream), w_f32, n, k, qwc_fmt_of(v), blocks_out);
 }
 
 size_t qwc_gemm_workspace_bytes(const qwc_hal*, const qwc_weight_view*, int64_t, int32_t, int32_t) { return 0; }

@@ -211,3 +211,22 @@ class QWGemm:
             raise QWGemmError(3, f"out has {out.numel()} elements, expected {w.n * w.k}")
         _check(_lib.load().qwc_dequant(hal.handle, _stream_ptr(stream), ctypes.byref(w.c), out.data_ptr(),
                                        F16 if out.dtype == torch.float16 else F32, int(standard_domain)))
+
+    @staticmethod
+    def quantize(hal: QWHal, w: torch.Tensor, container: ContainerKind = incumbentHQ4G32,
+                 out: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """Load-time quantizer (HQ4Quantizer in Sources/Foundation/QWLoad; Scripts/quantize/hq4.py:54-123):
+        f32 [n, k] on the device -> packed blocks, byte-identical to the reference's Python packer."""
+        if w.dtype != torch.float32 or not w.is_cuda or not w.is_contiguous() or w.dim() != 2:
+            raise QWGemmError(3, "w must be a contiguous 2-D CUDA float32 tensor")
+        n, k = w.shape
+        if k % container.group:
+            raise QWGemmError(2, f"k={k} is not a multiple of group {container.group}")
+        nbytes = n * container.row_bytes(k)
+        if out is None:
+            out = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+        if out.dtype != torch.uint8 or out.numel() < nbytes or not out.is_contiguous():
+            raise QWGemmError(3, "out must be a contiguous uint8 tensor large enough for the bank")
+        _check(_lib.load().qwc_quantize(hal.handle, _stream_ptr(stream), w.data_ptr(), n, k, container.kind,
+                                        container.bits, container.group, out.data_ptr()))
+        return out

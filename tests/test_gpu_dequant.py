@@ -115,3 +115,26 @@ def test_dequant_round_trip_full_size(hal, oracle):
     scale = blocks[..., 0:2].copy().view(np.float16).astype(np.float32)
     err = np.abs(wrot - rot).reshape(n, k // 32, 32).max(axis=-1)
     assert (err <= scale[..., 0] * 0.5 + 1032 * scale[..., 0] * 2.0 ** -11 + 1e-7).all()
+
+
+@pytest.mark.parametrize("name", FMTS)
+def test_device_quantizer_bytes_equal_the_packer(hal, oracle, golden, name):
+    # qwc_quantize must write the bytes the reference's Python packer writes (golden) and the oracle writes.
+    import qwegn_b200 as q
+    g = golden["formats"]
+    got = q.QWGemm.quantize(hal, torch.from_numpy(g["w"]).cuda(), q.CONTAINERS[name]).cpu().numpy()
+    assert np.array_equal(got, g[f"{name}_blocks"].reshape(-1))
+    rng = np.random.default_rng(77)
+    w = rng.normal(0.0, 0.02, (777, 2048)).astype(np.float32)
+    w[5] = 0.0
+    w[6, 3] = 500.0   # drives the HQ4_G32 scale clamp
+    got = q.QWGemm.quantize(hal, torch.from_numpy(w).cuda(), q.CONTAINERS[name]).cpu().numpy()
+    assert np.array_equal(got, oracle.quantize(w, oracle.FORMATS[name]).reshape(-1))
+
+
+def test_aq_quantizer_golden_on_device(hal, golden):
+    import qwegn_b200 as q
+    g = golden["ref_fixtures"]
+    vals = (g["aqq_bf16"].astype(np.uint32) << 16).view(np.float32)
+    got = q.QWGemm.quantize(hal, torch.from_numpy(np.ascontiguousarray(vals)).cuda()).cpu().numpy()
+    assert np.array_equal(got, g["aqq_blocks"].reshape(-1))
