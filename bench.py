@@ -189,9 +189,11 @@ def bench_gemv_point(q, hal, n, k, m, cname, steps, warmup, dist=None, seed=0):
     x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32).to(torch.float16)
     y = torch.empty((m, n), dtype=torch.float32, device="cuda")
     stream = torch.cuda.current_stream()
+    nws = q.QWGemm.workspaceBytes(hal, banks[0], m)
+    ws = torch.empty(nws, dtype=torch.uint8, device="cuda") if nws else None
 
     def step(i):
-        q.QWGemm.encode(hal, banks[i % copies], x, y)
+        q.QWGemm.encode(hal, banks[i % copies], x, y, workspace=ws)
 
     for i in range(warmup):
         step(i)

@@ -13,7 +13,8 @@ int qwc_launch_dequant(const qwc_hal*, cudaStream_t, const qwc_weight_view*, voi
 int qwc_launch_fwht32_f16(const qwc_hal*, cudaStream_t, void*, int64_t);
 int qwc_launch_quantize(const qwc_hal*, cudaStream_t, const float*, int64_t, int64_t, int, void*);
 int qwc_launch_gemv(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int,
-                    int64_t, int, int, bool);
+                    int64_t, int, int, void*, size_t);
+size_t qwc_gemv_workspace_bytes(const qwc_weight_view*, int64_t);
 
 static thread_local char g_err[512] = "";
 
@@ -47,6 +48,15 @@ int qwc_hal_create(int device, qwc_hal** out) {
     h->device = device;
     h->sm_count = prop.multiProcessorCount;
     h->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+    h->encode_tiled = nullptr;
+    {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            h->encode_tiled = fn;
+        (void)cudaGetLastError();
+    }
     cudaError_t e = cudaMalloc(&h->status, 4 * sizeof(int32_t));
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, 4 * sizeof(int32_t));
     if (e != cudaSuccess) {
@@ -188,13 +198,14 @@ int qwc_quantize(qwc_hal* hal, qwc_stream stream, const float* w_f32, int64_t n,
     return qwc_launch_quantize(hal, static_cast<cudaStream_t>(stream), w_f32, n, k, qwc_fmt_of(v), blocks_out);
 }
 
-size_t qwc_gemm_workspace_bytes(const qwc_hal*, const qwc_weight_view*, int64_t, int32_t, int32_t) { return 0; }
+size_t qwc_gemm_workspace_bytes(const qwc_hal*, const qwc_weight_view* w, int64_t m, int32_t, int32_t) {
+    if (!w || w->k <= 0 || w->group <= 0 || qwc_fmt_of(*w) == FMT_UNSUPPORTED) return 0;
+    return qwc_gemv_workspace_bytes(w, m);
+}
 
 int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx,
              void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace,
              size_t workspace_bytes) {
-    (void)workspace;
-    (void)workspace_bytes;
     qwc_clear_error();
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
     if (int rc = check_view(w)) return rc;
@@ -215,7 +226,7 @@ int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const vo
     if (ldy < n_out) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldy=%lld < output width %lld", (long long)ldy, (long long)n_out);
     if (reinterpret_cast<uintptr_t>(x_f16) % 2 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "x must be 2-byte aligned");
     return qwc_launch_gemv(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, epilogue,
-                           x_is_rotated, true);
+                           x_is_rotated, workspace, workspace_bytes);
 }
 
 }  // extern "C"

@@ -12,6 +12,7 @@ struct qwc_hal {
     int sm_count;
     int max_smem_optin;
     int32_t* status;  // device: [0] first error code written by a kernel, [1] detail
+    void* encode_tiled;  // driver entry point cuTensorMapEncodeTiled (null if unavailable)
 };
 
 // Error reporting (thread-local message, status code returned).

@@ -3,32 +3,42 @@
 // (Sources/QWMetal/gemm/qwgemm.metal, qwgemm_aq.metal, qwg_skinny.metal, Sources/QWMetal/mtp/qwmtp_mlp.metal).
 //
 // The path is bound by HBM: every weight byte is read exactly once.  Design:
-//  * one persistent CTA per SM owns a contiguous range of output rows; the packed rows are streamed, unchanged,
-//    into a 4-stage shared-memory ring with 1-D bulk async copies (cp.async.bulk + mbarrier tx counts), 16 rows x
-//    one K-chunk per stage, each row padded by 16 B so the per-lane word reads are bank-conflict free; the duty of
-//    refilling a stage rotates over the warps so no warp is set aside (512 threads keep 128 registers each);
-//  * the 16 warps split K: warp w owns the 32-element units w, w+16, ... of the chunk and keeps the matching
-//    activation fragments in registers for every row tile of the CTA (x is read once per CTA, rotated in
-//    registers by FWHT-32 with two xor-shuffle stages when the caller passes standard-basis activations);
-//  * nibbles/bytes are expanded in registers straight into m16n8k16 A fragments by the magic-bias form
-//    (0x6400 | q as f16 = 1024 + q, then one f16 FMA with scale and bias -- the reference's decode class,
-//    Sources/QWMetal/include/qw_dequant.metalh:53-61) and the dot products run on mma.sync with f32 accumulate.
-//    A SIMT FMA dot needs >3 issue slots per weight and cannot keep up with the bulk-copy stream; the k order
-//    inside a unit is permuted per format so that each lane's A words and B activations line up without shuffles;
-//  * the split-K partial sums of the 16 warps are combined through shared memory in a fixed order (deterministic).
+//  * one persistent CTA per SM owns a contiguous range of output rows.  A producer warp streams the packed rows,
+//    unchanged, into a ring of shared-memory stages with 1-D bulk async copies (cp.async.bulk + mbarrier tx
+//    counts): 16 rows x one K chunk per stage, rows padded by 16 B so per-lane word reads hit 32 distinct banks;
+//  * the activations are rotated (FWHT-32, f32 butterflies, one rounding to f16) once per CTA into shared memory,
+//    stored in the k order and 16-byte-chunk swizzle the fragment loads want;
+//  * the 16 consumer warps form T teams of W warps.  A team owns one 16-row tile at a time (all K chunks), so the
+//    accumulators stay in registers for the whole tile; teams work on different tiles concurrently.  Inside a team
+//    the 4-unit groups of a chunk are dealt round-robin to the warps; the W partial tiles are summed in a fixed
+//    order through shared memory (deterministic);
+//  * each lane decodes one whole block per row (5 or 9 word loads, one header) straight into m16n8k16 A fragments
+//    by the magic-bias form (0x6400 | q as f16 = 1024 + q, then one f16 FMA with scale and bias: the reference's
+//    decode class, Sources/QWMetal/include/qw_dequant.metalh:53-61); the dot products run on mma.sync with f32
+//    accumulate.  A SIMT FMA dot needs > 3 issue slots per weight and cannot keep up with the copy stream.  The k
+//    slots of an MMA are permuted (4 k from each of the 4 units a quad holds), which A and B share, so no shuffle
+//    is needed between the packed layout and the fragment layout.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
+
 #include "qwc_common.cuh"
 
 namespace {
 
-constexpr int kWarps = 16;
-constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 4;
+constexpr int kConsumerWarps = 16;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
 constexpr int kTileRows = 16;
+constexpr int kMaxStages = 24;
+constexpr int kRowPad = 16;  // smem row stride = chunk bytes + 16: (stride / 4) % 32 == 4 -> conflict-free word reads
+constexpr int kSmemBudget = 227 * 1024;
+constexpr int kBarrierBytes = 512;  // 2 x kMaxStages mbarriers + the abort flag, padded to keep the stages 128-byte aligned
 
 template <int FMT> struct StreamCfg;
-template <> struct StreamCfg<FMT_HQ4_G32_M5> { static constexpr int kUnitBytes = 20, kMaxChunkUnits = 128; };
-template <> struct StreamCfg<FMT_HQ8_G32> { static constexpr int kUnitBytes = 36, kMaxChunkUnits = 64; };
-template <> struct StreamCfg<FMT_HQ4_G64> { static constexpr int kUnitBytes = 18, kMaxChunkUnits = 128; };
+template <> struct StreamCfg<FMT_HQ4_G32_M5> { static constexpr int kUnitBytes = 20, kGroupUnits = 4; };
+template <> struct StreamCfg<FMT_HQ8_G32> { static constexpr int kUnitBytes = 36, kGroupUnits = 4; };
+template <> struct StreamCfg<FMT_HQ4_G64> { static constexpr int kUnitBytes = 18, kGroupUnits = 4; };
 
 struct GemvParams {
     const uint8_t* blocks;
@@ -37,75 +47,82 @@ struct GemvParams {
     int64_t ldx;
     void* y;
     int64_t ldy;
+    float* partial;   // [m, n] f32 raw dot products carried between the K slices of one call (may be null)
     int32_t* status;
+    int n;            // weight rows
     int n_out;        // output rows (n, or n/2 for the silu-pair epilogues)
     int m;            // tokens, <= 8 * NT
-    int units;        // k / 32
-    int nchunks;      // K chunks
-    int chunk_units;  // units per chunk (multiple of 16; the last chunk may be shorter)
+    int unit0;        // first 32-element unit of this launch's K slice
+    int units;        // units in this launch's K slice
+    int nchunks;      // K chunks per tile
+    int chunk_units;  // units per chunk (the last chunk may be shorter)
+    int stages;       // ring depth
+    int stride;       // smem row stride in bytes
+    int team_warps;   // W
     int y_f16;
     int epilogue;
     int x_is_rotated;
+    int acc_in;       // add `partial` before the epilogue
+    int acc_out;      // store raw sums to `partial` instead of y
     int row_quantum;  // CTA row ranges start on multiples of this (32 for the fused-FWHT epilogue)
-};
-
-template <int FMT, int NT>
-struct Smem {
-    using C = StreamCfg<FMT>;
-    static constexpr int kStride = C::kMaxChunkUnits * C::kUnitBytes + 16;  // (kStride / 4) % 32 == 4
-    static constexpr int kStageBytes = kTileRows * kStride;
-    static constexpr int kRT = NT == 1 ? 8 : 4;  // weight-row tiles per pass
-    static constexpr int kRedBytes = 8 * kRT * NT * 32 * 16;
-    static constexpr int kHBufBytes = 8 * NT * (kRT * kTileRows / 2) * 4;
-    static constexpr int kOffRed = kStages * kStageBytes;
-    static constexpr int kOffHBuf = kOffRed + kRedBytes;
-    static constexpr int kOffBars = kOffHBuf + kHBufBytes;
-    static constexpr int kTotal = kOffBars + 2 * kStages * 8 + 16;
-    static_assert((kStride / 4) % 32 == 4 && kStride % 16 == 0, "row padding must shift banks by 4 words");
+    int x_bytes;      // smem bytes of the activation region
+    int red_bytes;    // smem bytes of the team reduction region
+    uint32_t sh4, sh8, sh12;  // 2^28, 2^24, 2^20: mul.hi by these is a right shift by 4, 8, 12
+    int use_tmap;     // full 16-row tiles arrive by one 2-D tensor copy instead of 16 row copies
 };
 
 __device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
-__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, __half2 s2, __half2 b2) {
+    const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), s2, b2);
+    return *reinterpret_cast<const uint32_t*>(&r);
 }
-__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
+__device__ __forceinline__ uint32_t hsub2_1024(uint32_t a) {
+    const uint32_t k = 0x64006400u;
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&k));
+    return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-// Decode this lane's share of one unit of one row into four f16x2 A-fragment registers
-// (a[0], a[1] feed the first k16 MMA, a[2], a[3] the second).  srow = the row's chunk in shared memory.
+// Decode one whole unit (32 k of one row) into 16 f16x2 registers a[P], P = pair index.  The k each pair holds
+// is fixed per format (natural order for HQ4_G32_M5 / HQ8_G32; (8w+p, 8w+p+4) for the linear-nibble HQ4_G64) and
+// the activation staging writes x in the same order.  ublk = address of the unit's header word in shared memory;
+// wofs = byte offset of the unit's first payload word from the header.
+//
+// The integer/logic pipe is the scarce resource of this kernel, so the nibble shifts v >> 4, 8, 12 are computed
+// as mul.hi(v, 2^28 / 2^24 / 2^20) on the FMA pipe; sh = {2^28, 2^24, 2^20} arrives as kernel parameters so the
+// compiler cannot turn the multiplies back into shifts.
+__device__ __forceinline__ uint32_t shr_fma(uint32_t v, uint32_t pow2) { return __umulhi(v, pow2); }
+
 template <int FMT>
-__device__ __forceinline__ void decode_unit(const uint8_t* srow, int u, int t, uint32_t a[4]) {
+__device__ __forceinline__ void decode_unit(const uint8_t* ublk, int wofs, const uint32_t sh[3], uint32_t a[16]) {
+    const uint32_t hdr = lds32(ublk);
+    const __half2 h = *reinterpret_cast<const __half2*>(&hdr);
+    const __half2 s2 = __half2half2(__low2half(h)), b2 = __half2half2(__high2half(h));
     if (FMT == FMT_HQ4_G32_M5) {
-        const uint8_t* blk = srow + u * 20;
-        const uint32_t hdr = lds32(blk);
-        const uint32_t w = lds32(blk + 4 + 4 * t);
-        const uint32_t s2 = __byte_perm(hdr, hdr, 0x1010), b2 = __byte_perm(hdr, hdr, 0x3232);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) a[i] = hfma2_u32(((w >> (4 * i)) & 0x000F000Fu) | 0x64006400u, s2, b2);
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t v = lds32(ublk + wofs + 4 * w);
+            a[4 * w] = hfma2_u32((v & 0x000F000Fu) | 0x64006400u, s2, b2);
+#pragma unroll
+            for (int i = 1; i < 4; ++i)
+                a[4 * w + i] = hfma2_u32((shr_fma(v, sh[i - 1]) & 0x000F000Fu) | 0x64006400u, s2, b2);
+        }
     } else if (FMT == FMT_HQ8_G32) {
-        const uint8_t* blk = srow + u * 36;
-        const uint32_t hdr = lds32(blk);
-        const uint32_t w0 = lds32(blk + 4 + 4 * t), w1 = lds32(blk + 20 + 4 * t);
-        const uint32_t s2 = __byte_perm(hdr, hdr, 0x1010), b2 = __byte_perm(hdr, hdr, 0x3232);
-        const uint32_t k1024 = 0x64006400u;
-        a[0] = hfma2_u32(hsub2_u32(__byte_perm(w0, 0x64646464u, 0x4140), k1024), s2, b2);
-        a[1] = hfma2_u32(hsub2_u32(__byte_perm(w0, 0x64646464u, 0x4342), k1024), s2, b2);
-        a[2] = hfma2_u32(hsub2_u32(__byte_perm(w1, 0x64646464u, 0x4140), k1024), s2, b2);
-        a[3] = hfma2_u32(hsub2_u32(__byte_perm(w1, 0x64646464u, 0x4342), k1024), s2, b2);
-    } else {
-        const uint8_t* blk = srow + (u >> 1) * 36;
-        const uint32_t hdr = lds32(blk);
-        const uint32_t w = lds32(blk + 4 + 16 * (u & 1) + 4 * t);
-        const uint32_t s2 = __byte_perm(hdr, hdr, 0x1010), b2 = __byte_perm(hdr, hdr, 0x3232);
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-            a[i] = hfma2_u32(hsub2_u32(((w >> (4 * i)) & 0x000F000Fu) | 0x64006400u, 0x64006400u), s2, b2);
+        for (int w = 0; w < 8; ++w) {
+            const uint32_t v = lds32(ublk + wofs + 4 * w);
+            a[2 * w] = hfma2_u32(hsub2_1024(__byte_perm(v, 0x64646464u, 0x4140)), s2, b2);
+            a[2 * w + 1] = hfma2_u32(hsub2_1024(__byte_perm(v, 0x64646464u, 0x4342)), s2, b2);
+        }
+    } else {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t v = lds32(ublk + wofs + 4 * w);
+            a[4 * w] = hfma2_u32(hsub2_1024((v & 0x000F000Fu) | 0x64006400u), s2, b2);
+#pragma unroll
+            for (int i = 1; i < 4; ++i)
+                a[4 * w + i] = hfma2_u32(hsub2_1024((shr_fma(v, sh[i - 1]) & 0x000F000Fu) | 0x64006400u), s2, b2);
+        }
     }
 }
 
@@ -117,313 +134,361 @@ __device__ __forceinline__ void mma_16816(float d[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Activation fragment of one unit for one token: this lane's 8 k values, in the k order decode_unit<FMT> uses.
-// Natural layout: lane t of a quad holds elements 8t .. 8t+7 of the unit.
-template <int FMT>
-__device__ __forceinline__ void load_x_frag(const __half* xrow /* token row + unit*32, or nullptr */, int t, bool rotate,
-                                            uint32_t xb[4]) {
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (xrow != nullptr) raw = *reinterpret_cast<const uint4*>(xrow + 8 * t);
-    uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
-    if (rotate) {
-        float f[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const __half2 h = *reinterpret_cast<const __half2*>(&r[i]);
-            f[2 * i] = __low2float(h);
-            f[2 * i + 1] = __high2float(h);
-        }
-#pragma unroll
-        for (int h = 1; h < 8; h <<= 1) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if ((i & h) == 0) {
-                    const float u = f[i], v = f[i + h];
-                    f[i] = __fadd_rn(u, v);
-                    f[i + h] = __fsub_rn(u, v);
-                }
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 1, (t & 1) != 0);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 2, (t & 2) != 0);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const __half2 h = __floats2half2_rn(__fmul_rn(f[2 * i], qwc_inv_sqrt32()), __fmul_rn(f[2 * i + 1], qwc_inv_sqrt32()));
-            r[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-    }
-    if (FMT == FMT_HQ4_G32_M5) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) xb[i] = r[i];
-    } else if (FMT == FMT_HQ4_G64) {
-        // pair i of the word is (element 8t+i, element 8t+i+4)
-        xb[0] = __byte_perm(r[0], r[2], 0x5410);
-        xb[1] = __byte_perm(r[0], r[2], 0x7632);
-        xb[2] = __byte_perm(r[1], r[3], 0x5410);
-        xb[3] = __byte_perm(r[1], r[3], 0x7632);
-    } else {
-        // lane t needs elements 4t..4t+3 (held by lane t>>1, half t&1) and 16+4t..16+4t+3 (lane 2+(t>>1), half t&1)
-        const int lane = threadIdx.x & 31;
-        const int src_lo = (lane & ~3) | (t >> 1), src_hi = src_lo | 2;
-        const uint32_t l0 = __shfl_sync(0xFFFFFFFFu, r[0], src_lo), l1 = __shfl_sync(0xFFFFFFFFu, r[1], src_lo);
-        const uint32_t l2 = __shfl_sync(0xFFFFFFFFu, r[2], src_lo), l3 = __shfl_sync(0xFFFFFFFFu, r[3], src_lo);
-        const uint32_t h0 = __shfl_sync(0xFFFFFFFFu, r[0], src_hi), h1 = __shfl_sync(0xFFFFFFFFu, r[1], src_hi);
-        const uint32_t h2 = __shfl_sync(0xFFFFFFFFu, r[2], src_hi), h3 = __shfl_sync(0xFFFFFFFFu, r[3], src_hi);
-        const bool odd = (t & 1) != 0;
-        xb[0] = odd ? l2 : l0;
-        xb[1] = odd ? l3 : l1;
-        xb[2] = odd ? h2 : h0;
-        xb[3] = odd ? h3 : h1;
-    }
+// 2-D tiled tensor copy global -> shared, completion counted on an mbarrier.  x is in elements of the map's data
+// type (8-byte here, so x must be even: the copy starts on a 16-byte boundary); y is the row.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
 }
 
-__device__ __forceinline__ void cta_bar_sync() { __syncthreads(); }
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
-// Position of one stage fill in the CTA's fixed schedule: pass (group of row tiles) -> K chunk -> row tile.
-struct FillIter {
-    int pass, c, rt;
-    int r0, rows, tiles_out, ntiles;
-    bool done;
-};
+// Byte offset of (token, unit, 16-byte chunk c) in the staged activations: chunks are xor-swizzled so that the
+// four lanes of a quad (units u..u+3, or u, u+2, u+4, u+6) and two adjacent tokens hit 8 distinct 16-byte bank groups.
+template <int FMT> __device__ __forceinline__ int x_offset(int tok, int unit, int c, int units) {
+    const int usel = FMT == FMT_HQ4_G64 ? (unit >> 1) : unit;
+    return (tok * units + unit) * 64 + ((c ^ (usel & 3) ^ (tok & 1)) << 4);
+}
 
-template <int FMT, int NT>
-__global__ void __launch_bounds__(kThreads, 1) qwc_gemv_stream_kernel(const GemvParams p) {
-    using S = Smem<FMT, NT>;
+template <int FMT, int NT, int SUB>
+__global__ void __launch_bounds__(kThreads, 1)
+qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) {
     using C = StreamCfg<FMT>;
-    constexpr int kRT = S::kRT;
-    constexpr int kXU = C::kMaxChunkUnits / kWarps;
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kOffBars);
-    uint64_t* empty = full + kStages;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kStages);
+    // layout: [x region][reduction region][barriers][stages...]
+    uint8_t* xs = smem;
+    float4* red = reinterpret_cast<float4*>(smem + p.x_bytes);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.x_bytes + p.red_bytes);
+    uint64_t* empty = full + kMaxStages;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMaxStages);
+    uint8_t* stage0 = smem + p.x_bytes + p.red_bytes + kBarrierBytes;  // 128-byte aligned
+    const int stage_bytes = kTileRows * p.stride;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int W = p.team_warps, T = kConsumerWarps / W;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kWarps);
+            mbar_init(&empty[s], W);
         }
         *abort_flag = 0;
         fence_barrier_init();
     }
     __syncthreads();
 
-    // This CTA's output rows [rb, re).
-    const int quanta = p.n_out / p.row_quantum;  // n_out % row_quantum == 0 is checked on the host
+    // This CTA's output rows [rb, re) and its jobs: one job = 16 output rows (32 for the fused-FWHT epilogue) =
+    // SUB weight sub-tiles of 16 rows.  Job i goes to team i % T in round i / T.
+    const int quanta = p.n_out / p.row_quantum;
     const int rb = static_cast<int>((static_cast<int64_t>(quanta) * blockIdx.x) / gridDim.x) * p.row_quantum;
     const int re = static_cast<int>((static_cast<int64_t>(quanta) * (blockIdx.x + 1)) / gridDim.x) * p.row_quantum;
-    const bool paired = p.epilogue != QWC_EPI_NONE;
-    const int out_rows_per_pass = (paired ? kRT / 2 : kRT) * kTileRows;
-    const int npasses = (re - rb + out_rows_per_pass - 1) / out_rows_per_pass;
+    constexpr int kJobRows = SUB == 4 ? 32 : 16;
+    const int njobs = (re - rb + kJobRows - 1) / kJobRows;
+    const int E = SUB * p.nchunks;  // stage fills per job
+    const int rounds = (njobs + T - 1) / T;
 
-    auto set_pass = [&](FillIter& it) {
-        it.r0 = rb + it.pass * out_rows_per_pass;
-        it.rows = min(re - it.r0, out_rows_per_pass);
-        it.tiles_out = (it.rows + kTileRows - 1) / kTileRows;
-        it.ntiles = paired ? 2 * it.tiles_out : it.tiles_out;
+    // Weight row of (job, sub-tile): SUB 1: rows; SUB 2: gate, up; SUB 4: gate lo, gate hi, up lo, up hi.
+    auto first_weight_row = [&](int job, int sub, int& valid) {
+        const int out0 = rb + job * kJobRows + (SUB == 4 ? (sub & 1) * 16 : 0);
+        valid = min(kTileRows, re - out0);
+        const bool up = SUB == 2 ? sub == 1 : (SUB == 4 ? sub >= 2 : false);
+        return static_cast<int64_t>(out0) + (up ? p.n_out : 0);
     };
-    auto advance = [&](FillIter& it) {
-        if (++it.rt < it.ntiles) return;
-        it.rt = 0;
-        if (++it.c < p.nchunks) return;
-        it.c = 0;
-        if (++it.pass < npasses) set_pass(it);
-        else it.done = true;
-    };
-    bool ok = true;
-    // Fill one stage: wait until its previous contents were consumed by all warps, then one bulk copy per row.
-    // Executed by a whole warp; the duty rotates over the warps (fill number seq is issued by warp seq % 16).
-    auto fill = [&](const FillIter& it, uint32_t seq) {
-        const int stage = seq % kStages;
-        if (seq >= kStages && ok && !*abort_flag) {
-            ok = mbar_wait(&empty[stage], ((seq / kStages) - 1) & 1);
-            if (!ok) {
-                *abort_flag = 1;
-                if (lane == 0) atomicCAS(p.status, 0, QWC_DEV_WAIT_EMPTY_TIMEOUT);
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------ producer warp ------------------------------
+        uint32_t q = 0;
+        bool ok = true;
+        for (int r = 0; r < rounds && ok; ++r) {
+            const int tl = min(T, njobs - r * T);
+            for (int e = 0; e < E && ok; ++e) {
+                const int sub = e / p.nchunks, c = e % p.nchunks;
+                const int u0 = c * p.chunk_units;
+                const uint32_t cbytes = static_cast<uint32_t>(min(p.chunk_units, p.units - u0)) * C::kUnitBytes;
+                for (int tau = 0; tau < tl; ++tau, ++q) {
+                    const int slot = q % p.stages;
+                    if (q >= static_cast<uint32_t>(p.stages)) {
+                        if (*abort_flag || !mbar_wait(&empty[slot], ((q / p.stages) - 1) & 1)) {
+                            if (!*abort_flag && lane == 0) atomicCAS(p.status, 0, QWC_DEV_WAIT_EMPTY_TIMEOUT);
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                    }
+                    int valid;
+                    const int64_t wrow = first_weight_row(r * T + tau, sub, valid);
+                    if (valid <= 0) {
+                        // sub-tile past the CTA's rows (second half of a short FWHT job): nothing to copy
+                        if (lane == 0) mbar_arrive(&full[slot]);
+                        continue;
+                    }
+                    if (p.use_tmap && valid == kTileRows) {
+                        // one 2-D tensor copy per stage: 16 rows x (chunk + 16 pad bytes), rows land `stride` apart
+                        if (lane == 0) {
+                            mbar_arrive_expect_tx(&full[slot], static_cast<uint32_t>(stage_bytes));
+                            tma_load_2d(stage0 + slot * stage_bytes, &tmap,
+                                        static_cast<int>((static_cast<int64_t>(p.unit0 + u0) * C::kUnitBytes) >> 3),
+                                        static_cast<int>(wrow), &full[slot]);
+                        }
+                        continue;
+                    }
+                    if (lane == 0) mbar_arrive_expect_tx(&full[slot], cbytes * valid);
+                    __syncwarp();
+                    if (lane < valid) {
+                        const uint8_t* src = p.blocks + (wrow + lane) * p.row_bytes +
+                                             static_cast<int64_t>(p.unit0 + u0) * C::kUnitBytes;
+                        bulk_g2s(stage0 + slot * stage_bytes + lane * p.stride, src, cbytes, &full[slot]);
+                    }
+                }
             }
         }
-        if (!ok || *abort_flag) return;
-        const int u0 = it.c * p.chunk_units;
-        const uint32_t cbytes = static_cast<uint32_t>(min(p.chunk_units, p.units - u0)) * C::kUnitBytes;
-        const bool up = paired && it.rt >= it.tiles_out;
-        const int first = it.r0 + (up ? it.rt - it.tiles_out : it.rt) * kTileRows;  // first output row of the tile
-        const int valid = min(kTileRows, it.r0 + it.rows - first);
-        const int64_t wrow = static_cast<int64_t>(first) + (up ? p.n_out : 0);
-        if (lane == 0) mbar_arrive_expect_tx(&full[stage], cbytes * valid);
-        __syncwarp();
-        if (lane < valid) {
-            const uint8_t* src = p.blocks + (wrow + lane) * p.row_bytes + static_cast<int64_t>(u0) * C::kUnitBytes;
-            bulk_g2s(smem + stage * S::kStageBytes + lane * S::kStride, src, cbytes, &full[stage]);
+        // After a failed wait the consumers stop draining: let this CTA's own copies land (bounded) before exit.
+        if (!ok && lane == 0) {
+            for (uint32_t s = 0; s < static_cast<uint32_t>(p.stages) && s < q; ++s) {
+                const uint32_t last = ((q - 1 - s) / p.stages) * p.stages + s;
+                mbar_wait(&full[s], (last / p.stages) & 1);
+            }
         }
-    };
-
-    FillIter pit{};  // the next fill to issue (runs kStages - 1 ahead of consumption)
-    pit.done = npasses == 0;
-    if (!pit.done) set_pass(pit);
-    uint32_t fill_seq = 0;
-    for (; fill_seq < kStages - 1 && !pit.done; ++fill_seq) {
-        if (warp == static_cast<int>(fill_seq % kWarps)) fill(pit, fill_seq);
-        advance(pit);
+        return;
     }
 
-    const int gid = lane >> 2, t = lane & 3;
-    float* red = reinterpret_cast<float*>(smem + S::kOffRed);
-    float* hbuf = reinterpret_cast<float*>(smem + S::kOffHBuf);
-    uint32_t seq = 0;
-    for (int pass = 0; pass < npasses; ++pass) {
-        const int r0 = rb + pass * out_rows_per_pass;
-        const int rows = min(re - r0, out_rows_per_pass);
-        const int tiles_out = (rows + kTileRows - 1) / kTileRows;
-        const int ntiles = paired ? 2 * tiles_out : tiles_out;
-        float d[kRT][NT][4];
+    // ---------------- consumers: stage the rotated activations once per CTA ----------------
+    // A quad handles one (token, unit): lane t holds elements 8t..8t+7, rotates them with three in-lane butterfly
+    // stages and two xor-shuffle stages (the reference's h = 1, 2, 4, 8, 16 order), and writes one 16-byte chunk.
+    {
+        const int t4 = lane & 3, sub8 = lane >> 2;
+        const int items = p.m * p.units;  // (token, unit) pairs
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.ldx % 8 == 0);
+        for (int base = warp * 8; base < items; base += kConsumerWarps * 8) {
+            const int it = base + sub8;
+            const bool live = it < items;
+            const int tok = live ? it / p.units : 0, unit = live ? it % p.units : 0;
+            const __half* src = p.x + tok * p.ldx + static_cast<int64_t>(p.unit0 + unit) * 32 + 8 * t4;
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (live) {
+                if (vec_ok) raw = *reinterpret_cast<const uint4*>(src);
+                else {
+                    __half tmp[8];
 #pragma unroll
-        for (int rt = 0; rt < kRT; ++rt)
+                    for (int i = 0; i < 8; ++i) tmp[i] = src[i];
+                    raw = *reinterpret_cast<const uint4*>(tmp);
+                }
+            }
+            __half2 hv[4] = {*reinterpret_cast<__half2*>(&raw.x), *reinterpret_cast<__half2*>(&raw.y),
+                             *reinterpret_cast<__half2*>(&raw.z), *reinterpret_cast<__half2*>(&raw.w)};
+            if (!p.x_is_rotated) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(hv[i]); f[2 * i + 1] = __high2float(hv[i]); }
+#pragma unroll
+                for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if ((i & h) == 0) {
+                            const float u = f[i], v = f[i + h];
+                            f[i] = __fadd_rn(u, v);
+                            f[i + h] = __fsub_rn(u, v);
+                        }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 1, (t4 & 1) != 0);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 2, (t4 & 2) != 0);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    hv[i] = __floats2half2_rn(__fmul_rn(f[2 * i], qwc_inv_sqrt32()), __fmul_rn(f[2 * i + 1], qwc_inv_sqrt32()));
+            }
+            if (live) {
+                uint4 outv;
+                if (FMT == FMT_HQ4_G64) {
+                    // slot order inside a chunk: e0 e4 e1 e5 e2 e6 e3 e7
+                    outv.x = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[2]), 0x5410);
+                    outv.y = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[2]), 0x7632);
+                    outv.z = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[1]), *reinterpret_cast<uint32_t*>(&hv[3]), 0x5410);
+                    outv.w = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[1]), *reinterpret_cast<uint32_t*>(&hv[3]), 0x7632);
+                } else {
+                    outv = make_uint4(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[1]),
+                                      *reinterpret_cast<uint32_t*>(&hv[2]), *reinterpret_cast<uint32_t*>(&hv[3]));
+                }
+                *reinterpret_cast<uint4*>(xs + x_offset<FMT>(tok, unit, t4, p.units)) = outv;
+            }
+        }
+    }
+    named_bar_sync(9, kConsumerWarps * 32);
+
+    const int gid = lane >> 2, t = lane & 3;
+    const int team = warp / W, wj = warp % W;
+    const int team_threads = W * 32;
+    bool ok = true;
+    const uint32_t sh[3] = {p.sh4, p.sh8, p.sh12};
+    // Per-lane constants of the activation fragment loads: the chunk swizzle depends only on (t, token parity)
+    // because chunk starts and group starts are multiples of 4 units (8 for HQ4_G64).
+    const uint8_t* xtok[NT];
+    int xsw[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int tok = min(nt * 8 + gid, p.m - 1);
+        xtok[nt] = xs + static_cast<size_t>(tok) * p.units * 64;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) xsw[nt][cc] = (cc ^ t ^ (tok & 1)) << 4;
+    }
+
+    for (int r = 0; r < rounds; ++r) {
+        const int job = r * T + team;
+        const int tl = min(T, njobs - r * T);
+        if (job >= njobs) break;  // uniform inside a team
+        float d[SUB][NT][2][4];
+#pragma unroll
+        for (int s = 0; s < SUB; ++s)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) d[rt][nt][i] = 0.0f;
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) d[s][nt][h][i] = 0.0f;
 
-        for (int c = 0; c < p.nchunks; ++c) {
-            const int u0 = c * p.chunk_units;
-            const int cu = min(p.chunk_units, p.units - u0);
-            uint32_t xb[kXU][NT][4];
 #pragma unroll
-            for (int j = 0; j < kXU; ++j) {
-                const int u = warp + kWarps * j;
-                if (u < cu) {
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        const int tok = nt * 8 + gid;
-                        const __half* xr = tok < p.m ? p.x + tok * p.ldx + static_cast<int64_t>(u0 + u) * 32 : nullptr;
-                        load_x_frag<FMT>(xr, t, p.x_is_rotated == 0, xb[j][nt]);
+        for (int sub = 0; sub < SUB; ++sub) {
+            for (int c = 0; c < p.nchunks; ++c) {
+                const uint32_t q = static_cast<uint32_t>(r) * E * T + static_cast<uint32_t>(sub * p.nchunks + c) * tl + team;
+                const int slot = q % p.stages;
+                if (ok && !*abort_flag) {
+                    ok = mbar_wait(&full[slot], (q / p.stages) & 1);
+                    if (!ok) {
+                        *abort_flag = 1;
+                        if (lane == 0) atomicCAS(p.status, 0, QWC_DEV_WAIT_FULL_TIMEOUT);
                     }
                 }
-            }
+                const int u0 = c * p.chunk_units;
+                const int cu = min(p.chunk_units, p.units - u0);
+                if (ok && !*abort_flag) {
+                    const uint8_t* row_lo = stage0 + slot * stage_bytes + gid * p.stride;
+                    const uint8_t* row_hi = row_lo + 8 * p.stride;
+                    const int ngroups = cu / C::kGroupUnits;
+                    for (int g = wj; g < ngroups; g += W) {
+                        // this lane's unit inside the chunk, and where its header / payload sit in the row
+                        int ul, hofs, wofs;
+                        if (FMT == FMT_HQ4_G64) {
+                            ul = 8 * (g >> 1) + (g & 1) + 2 * t;   // even units, then odd units, of an 8-unit span
+                            hofs = (ul >> 1) * 36;
+                            wofs = 4 + 16 * (ul & 1);
+                        } else {
+                            ul = 4 * g + t;
+                            hofs = ul * C::kUnitBytes;
+                            wofs = 4;
+                        }
+                        uint32_t alo[16], ahi[16];
+                        decode_unit<FMT>(row_lo + hofs, wofs, sh, alo);
+                        decode_unit<FMT>(row_hi + hofs, wofs, sh, ahi);
 #pragma unroll
-            for (int rt = 0; rt < kRT; ++rt) {
-                if (rt < ntiles) {
-                    if (!pit.done) {
-                        if (warp == static_cast<int>(fill_seq % kWarps)) fill(pit, fill_seq);
-                        advance(pit);
-                        ++fill_seq;
-                    }
-                    const int stage = seq % kStages;
-                    if (ok && !*abort_flag) {
-                        ok = mbar_wait(&full[stage], (seq / kStages) & 1);
-                        if (!ok) {
-                            *abort_flag = 1;
-                            if (lane == 0) atomicCAS(p.status, 0, QWC_DEV_WAIT_FULL_TIMEOUT);
+                        for (int nt = 0; nt < NT; ++nt) {
+                            const uint8_t* xu = xtok[nt] + (u0 + ul) * 64;
+                            uint4 xv[4];
+#pragma unroll
+                            for (int cc = 0; cc < 4; ++cc) xv[cc] = *reinterpret_cast<const uint4*>(xu + xsw[nt][cc]);
+                            const uint32_t* xp = reinterpret_cast<const uint32_t*>(xv);
+#pragma unroll
+                            for (int s = 0; s < 8; ++s)
+                                mma_16816(d[sub][nt][s & 1], alo[2 * s], ahi[2 * s], alo[2 * s + 1], ahi[2 * s + 1],
+                                          xp[2 * s], xp[2 * s + 1]);
                         }
                     }
-                    if (ok && !*abort_flag) {
-                        const uint8_t* row_lo = smem + stage * S::kStageBytes + gid * S::kStride;
-                        const uint8_t* row_hi = row_lo + 8 * S::kStride;
-#pragma unroll
-                        for (int j = 0; j < kXU; ++j) {
-                            const int u = warp + kWarps * j;
-                            if (u < cu) {
-                                uint32_t alo[4], ahi[4];
-                                decode_unit<FMT>(row_lo, u, t, alo);
-                                decode_unit<FMT>(row_hi, u, t, ahi);
-#pragma unroll
-                                for (int nt = 0; nt < NT; ++nt) {
-                                    mma_16816(d[rt][nt], alo[0], ahi[0], alo[1], ahi[1], xb[j][nt][0], xb[j][nt][1]);
-                                    mma_16816(d[rt][nt], alo[2], ahi[2], alo[3], ahi[3], xb[j][nt][2], xb[j][nt][3]);
-                                }
-                            }
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty[stage]);
-                    ++seq;
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);
             }
         }
 
-        // ---- split-K reduction over the 16 warps, fixed order: (w) + (w+8), then slots 0..7 in sequence ----
-        float4* red4 = reinterpret_cast<float4*>(red);
-        if (warp >= 8) {
+        // ---- team reduction (fixed order) and epilogue ----
+        // red layout per team: [warp_in_team][sub][nt][lane] float4
+        float4* tred = red + static_cast<size_t>(team) * W * SUB * NT * 32;
 #pragma unroll
-            for (int rt = 0; rt < kRT; ++rt)
+        for (int s = 0; s < SUB; ++s)
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-                    red4[(((warp - 8) * kRT + rt) * NT + nt) * 32 + lane] =
-                        make_float4(d[rt][nt][0], d[rt][nt][1], d[rt][nt][2], d[rt][nt][3]);
-        }
-        cta_bar_sync();
-        if (warp < 8) {
+            for (int nt = 0; nt < NT; ++nt)
+                tred[((wj * SUB + s) * NT + nt) * 32 + lane] =
+                    make_float4(d[s][nt][0][0] + d[s][nt][1][0], d[s][nt][0][1] + d[s][nt][1][1],
+                                d[s][nt][0][2] + d[s][nt][1][2], d[s][nt][0][3] + d[s][nt][1][3]);
+        if (W > 1) named_bar_sync(1 + team, team_threads); else __syncwarp();
+
+        const int out0 = rb + job * kJobRows;
+        constexpr int kOutTiles = SUB == 4 ? 2 : 1;  // 16-row output tiles per job
+        float* hbuf = reinterpret_cast<float*>(tred);  // reused after the sums are in registers (FWHT epilogue)
+        float hval[kOutTiles][NT][4];
+        bool mine[kOutTiles][NT];
 #pragma unroll
-            for (int rt = 0; rt < kRT; ++rt)
+        for (int ot = 0; ot < kOutTiles; ++ot)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                mine[ot][nt] = (ot * NT + nt) % W == wj;  // spread the (ot, nt) tiles over the team's warps
+#pragma unroll
+                for (int i = 0; i < 4; ++i) hval[ot][nt][i] = 0.0f;
+                if (!mine[ot][nt]) continue;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), accu = acc;
+                const int sg = SUB == 4 ? ot : 0, su = SUB == 4 ? 2 + ot : 1;
+                for (int w = 0; w < W; ++w) {
+                    const float4 v = tred[((w * SUB + sg) * NT + nt) * 32 + lane];
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    if (SUB > 1) {
+                        const float4 u = tred[((w * SUB + su) * NT + nt) * 32 + lane];
+                        accu.x += u.x; accu.y += u.y; accu.z += u.z; accu.w += u.w;
+                    }
+                }
+                float g4[4] = {acc.x, acc.y, acc.z, acc.w}, u4[4] = {accu.x, accu.y, accu.z, accu.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = out0 + ot * 16 + gid + 8 * (i >> 1);
+                    const int tok = nt * 8 + 2 * t + (i & 1);
+                    const bool live = row < re && tok < p.m;
+                    float v = g4[i], u = u4[i];
+                    if (live && p.acc_in) {
+                        v += p.partial[static_cast<int64_t>(tok) * p.n + row];
+                        if (SUB > 1) u += p.partial[static_cast<int64_t>(tok) * p.n + p.n_out + row];
+                    }
+                    if (live && p.acc_out) {
+                        p.partial[static_cast<int64_t>(tok) * p.n + row] = v;
+                        if (SUB > 1) p.partial[static_cast<int64_t>(tok) * p.n + p.n_out + row] = u;
+                    } else if (live) {
+                        if (SUB > 1) v = (v / (1.0f + expf(-v))) * u;
+                        if (SUB == 4) {
+                            hval[ot][nt][i] = __half2float(__float2half_rn(v));
+                        } else {
+                            const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
+                            if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(v);
+                            else static_cast<float*>(p.y)[o] = v;
+                        }
+                    }
+                }
+            }
+        if (SUB == 4 && !p.acc_out) {
+            // fused FWHT-32 over the job's 32 output rows: h (already rounded to f16) -> smem -> one warp per token
+            if (W > 1) named_bar_sync(1 + team, team_threads); else __syncwarp();
+#pragma unroll
+            for (int ot = 0; ot < kOutTiles; ++ot)
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    float4* slot = &red4[((warp * kRT + rt) * NT + nt) * 32 + lane];
-                    const float4 o = *slot;
-                    *slot = make_float4(d[rt][nt][0] + o.x, d[rt][nt][1] + o.y, d[rt][nt][2] + o.z, d[rt][nt][3] + o.w);
-                }
-        }
-        cta_bar_sync();
-        const int out_tiles = paired ? kRT / 2 : kRT;
-        for (int item = threadIdx.x; item < out_tiles * NT * 32; item += kThreads) {
-            const int l = item & 31, nt = (item >> 5) % NT, rt = item / (32 * NT);
-            if (rt >= tiles_out) continue;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), acc_up = acc;
+                    if (!mine[ot][nt]) continue;
 #pragma unroll
-            for (int s = 0; s < 8; ++s) {
-                const float4 v = red4[((s * kRT + rt) * NT + nt) * 32 + l];
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-            if (paired) {
-#pragma unroll
-                for (int s = 0; s < 8; ++s) {
-                    const float4 v = red4[((s * kRT + rt + tiles_out) * NT + nt) * 32 + l];
-                    acc_up.x += v.x; acc_up.y += v.y; acc_up.z += v.z; acc_up.w += v.w;
+                    for (int i = 0; i < 4; ++i) {
+                        const int lrow = ot * 16 + gid + 8 * (i >> 1), tok = nt * 8 + 2 * t + (i & 1);
+                        if (tok < p.m) hbuf[tok * 32 + lrow] = hval[ot][nt][i];
+                    }
                 }
-            }
-            const int g = l >> 2, tt = l & 3;
-            const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
-            const float ups[4] = {acc_up.x, acc_up.y, acc_up.z, acc_up.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int lrow = rt * kTileRows + g + 8 * (i >> 1);  // row inside the pass
-                const int tok = nt * 8 + 2 * tt + (i & 1);
-                if (lrow >= rows || tok >= p.m) continue;
-                float v = vals[i];
-                if (paired) v = (v / (1.0f + expf(-v))) * ups[i];
-                if (p.epilogue == QWC_EPI_SILU_PAIR_FWHT) {
-                    hbuf[tok * (out_tiles * kTileRows) + lrow] = __half2float(__float2half_rn(v));
-                } else {
-                    const int64_t o = static_cast<int64_t>(tok) * p.ldy + r0 + lrow;
-                    if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(v);
-                    else static_cast<float*>(p.y)[o] = v;
-                }
-            }
-        }
-        if (p.epilogue == QWC_EPI_SILU_PAIR_FWHT) {
-            cta_bar_sync();
-            // rows is a multiple of 32 here; one warp rotates one (token, 32-row block).
-            const int blocks32 = rows / 32;
-            for (int item = warp; item < p.m * blocks32; item += kWarps) {
-                const int tok = item / blocks32, b = item % blocks32;
-                float v = hbuf[tok * (out_tiles * kTileRows) + b * 32 + lane];
+            if (W > 1) named_bar_sync(1 + team, team_threads); else __syncwarp();
+            for (int tok = wj; tok < p.m; tok += W) {
+                float v = hbuf[tok * 32 + lane];
 #pragma unroll
                 for (int h = 1; h < 32; h <<= 1) v = fwht_xor_stage(v, h, (lane & h) != 0);
                 v = __fmul_rn(v, qwc_inv_sqrt32());
-                const int64_t o = static_cast<int64_t>(tok) * p.ldy + r0 + b * 32 + lane;
+                const int64_t o = static_cast<int64_t>(tok) * p.ldy + out0 + lane;
                 if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(v);
                 else static_cast<float*>(p.y)[o] = __half2float(__float2half_rn(v));
             }
         }
-        cta_bar_sync();  // red / hbuf are reused by the next pass
-    }
-    // After a failed wait some fills may never have been consumed: let this CTA's own copies land (bounded
-    // wait on the last phase of every stage that was filled) before the CTA exits.
-    if (*abort_flag && threadIdx.x == 0) {
-        for (uint32_t s = 0; s < kStages && s < fill_seq; ++s) {
-            const uint32_t last = ((fill_seq - 1 - s) / kStages) * kStages + s;  // last fill number that used stage s
-            mbar_wait(&full[s], (last / kStages) & 1);
-        }
+        if (W > 1) named_bar_sync(1 + team, team_threads); else __syncwarp();  // red is reused by the next job
     }
 }
 
@@ -486,30 +551,143 @@ __global__ void __launch_bounds__(256) qwc_gemv_rowwise_kernel(const GemvParams 
     }
 }
 
-template <int FMT, int NT>
-int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p) {
-    using S = Smem<FMT, NT>;
+// ---------------------------------------------------------------------------------------------------------------
+// Host side: geometry of one launch (chunking, team shape, ring depth) and K slicing when the activations of all
+// tokens do not fit in shared memory next to the ring.
+
+struct StreamGeom {
+    int chunk_units, nchunks, team_warps, stages, stride, x_bytes, red_bytes, smem_bytes;
+};
+
+constexpr int kXCapBytes = 112 * 1024;  // at most this much shared memory for the staged activations of a K slice
+
+// units: 32-element units of this launch's K slice; jobs: 16-row (32 for FWHT) jobs per CTA.  The team count T
+// follows the jobs a CTA has (teams work on different jobs concurrently), the chunk is the largest one that
+// still leaves the ring T + max(2, T/2) stages deep.  QWC_GEMV_W / QWC_GEMV_CHUNK override both (tuning knobs).
+// Returns false when no geometry fits.
+template <int FMT>
+bool plan_geometry(int units, int m, int nt, int sub, int jobs, StreamGeom* g) {
     using C = StreamCfg<FMT>;
+    const int quantum = FMT == FMT_HQ4_G64 ? 8 : 4;      // units per chunk must be a multiple of this
+    // chunk bytes + 16 pad <= 2048: the box of the 2-D tensor copy is at most 256 8-byte elements wide
+    const int max_chunk = FMT == FMT_HQ4_G32_M5 ? 100 : (FMT == FMT_HQ8_G32 ? 56 : 112);
+    g->x_bytes = ((m * units * 64 + 127) / 128) * 128;
+    g->red_bytes = kConsumerWarps * sub * nt * 32 * 16;
+    const int fixed = g->x_bytes + g->red_bytes + kBarrierBytes;
+    int teams = 1;
+    while (teams < jobs && teams < kConsumerWarps) teams <<= 1;
+    static const int env_w = getenv("QWC_GEMV_W") ? atoi(getenv("QWC_GEMV_W")) : 0;
+    static const int env_chunk = getenv("QWC_GEMV_CHUNK") ? atoi(getenv("QWC_GEMV_CHUNK")) : 0;
+    if (env_w == 1 || env_w == 2 || env_w == 4 || env_w == 8 || env_w == 16) teams = kConsumerWarps / env_w;
+    for (; teams >= 1; teams >>= 1) {
+        const int w = kConsumerWarps / teams;
+        const int want = teams + (teams / 2 > 2 ? teams / 2 : 2);
+        int best_per = 0, best_stages = 0;
+        for (int nch = 1; nch <= units / quantum; ++nch) {
+            int per = (units + nch - 1) / nch;
+            per = ((per + quantum - 1) / quantum) * quantum;
+            if (env_chunk > 0) per = ((env_chunk + quantum - 1) / quantum) * quantum;
+            if (per > max_chunk) continue;
+            const int stage_bytes = kTileRows * (per * C::kUnitBytes + kRowPad);
+            int stages = (kSmemBudget - fixed) / stage_bytes;
+            if (stages > kMaxStages) stages = kMaxStages;
+            if (stages >= want || (env_chunk > 0 && stages >= teams + 1)) { best_per = per; best_stages = stages; break; }
+            if (env_chunk > 0) break;
+        }
+        if (best_per == 0) continue;
+        if (best_per / C::kGroupUnits < w && teams > 1 && env_w == 0) continue;  // fewer groups than warps: idle warps
+        g->chunk_units = best_per;
+        g->nchunks = (units + best_per - 1) / best_per;
+        g->stride = best_per * C::kUnitBytes + kRowPad;
+        g->team_warps = w;
+        g->stages = best_stages;
+        g->smem_bytes = fixed + best_stages * kTileRows * g->stride;
+        return true;
+    }
+    return false;
+}
+
+template <int FMT, int NT, int SUB>
+int launch_stream_inst(const qwc_hal* hal, cudaStream_t st, const GemvParams& p, const CUtensorMap& tmap, int smem_bytes,
+                       int grid) {
     static bool configured[64] = {};
     if (!configured[hal->device & 63]) {
-        QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemv_stream_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+        QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemv_stream_kernel<FMT, NT, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kSmemBudget));
         configured[hal->device & 63] = true;
     }
-    p.nchunks = (p.units + C::kMaxChunkUnits - 1) / C::kMaxChunkUnits;
-    const int per = (p.units + p.nchunks - 1) / p.nchunks;
-    p.chunk_units = ((per + 15) / 16) * 16;
-    p.nchunks = (p.units + p.chunk_units - 1) / p.chunk_units;
-    const int quanta = p.n_out / p.row_quantum;
-    int grid = hal->sm_count;
-    if (grid > quanta) grid = quanta;
-    if (grid < 1) grid = 1;
-    qwc_gemv_stream_kernel<FMT, NT><<<grid, kThreads, S::kTotal, st>>>(p);
+    qwc_gemv_stream_kernel<FMT, NT, SUB><<<grid, kThreads, smem_bytes, st>>>(p, tmap);
     QWC_CUDA_TRY(cudaGetLastError());
     return QWC_OK;
 }
 
+template <int FMT, int NT>
+int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_units, float* workspace) {
+    const int sub = p.epilogue == QWC_EPI_NONE ? 1 : (p.epilogue == QWC_EPI_SILU_PAIR ? 2 : 4);
+    // K slices: as few as keep the staged activations within their share of shared memory.
+    const int quantum = FMT == FMT_HQ4_G64 ? 8 : 4;
+    const int x_cap_units = kXCapBytes / (p.m * 64);
+    int slices = 1;
+    if (total_units > x_cap_units) slices = (total_units + x_cap_units - 1) / x_cap_units;
+    int per_slice = (total_units + slices - 1) / slices;
+    per_slice = ((per_slice + quantum - 1) / quantum) * quantum;
+    slices = (total_units + per_slice - 1) / per_slice;
+    if (slices > 1 && workspace == nullptr)
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "this call needs a workspace of qwc_gemm_workspace_bytes() bytes");
+    const int quanta = p.n_out / p.row_quantum;
+    int grid = hal->sm_count;
+    if (grid > quanta) grid = quanta;
+    if (grid < 1) grid = 1;
+    for (int s = 0; s < slices; ++s) {
+        GemvParams q = p;
+        q.unit0 = s * per_slice;
+        q.units = total_units - q.unit0 < per_slice ? total_units - q.unit0 : per_slice;
+        q.partial = workspace;
+        q.acc_in = s > 0;
+        q.acc_out = s + 1 < slices;
+        StreamGeom g;
+        const int rows_per_cta = (p.n_out + grid - 1) / grid;
+        const int job_rows = sub == 4 ? 32 : 16;
+        if (!plan_geometry<FMT>(q.units, q.m, NT, sub, (rows_per_cta + job_rows - 1) / job_rows, &g))
+            return qwc_fail(QWC_ERR_BAD_GEOMETRY, "no shared-memory geometry fits this k slice");
+        q.chunk_units = g.chunk_units;
+        q.nchunks = g.nchunks;
+        q.team_warps = g.team_warps;
+        q.stages = g.stages;
+        q.stride = g.stride;
+        q.x_bytes = g.x_bytes;
+        q.red_bytes = g.red_bytes;
+        // Tensor map over the bank as [n rows][row_bytes / 8] 8-byte elements; box = 16 rows x stride bytes.
+        alignas(64) CUtensorMap tmap;
+        memset(&tmap, 0, sizeof(tmap));
+        q.use_tmap = 0;
+        static const bool no_tmap = getenv("QWC_GEMV_NO_TMAP") != nullptr;
+        if (hal->encode_tiled != nullptr && g.stride / 8 <= 256 && !no_tmap) {
+            using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                          const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                          CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+            const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(p.row_bytes / 8), static_cast<cuuint64_t>(p.n)};
+            const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(p.row_bytes)};
+            const cuuint32_t box[2] = {static_cast<cuuint32_t>(g.stride / 8), static_cast<cuuint32_t>(kTileRows)};
+            const cuuint32_t estr[2] = {1, 1};
+            const CUresult cr = reinterpret_cast<EncodeFn>(hal->encode_tiled)(
+                &tmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(p.blocks), gdim, gstride, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            q.use_tmap = cr == CUDA_SUCCESS;
+        }
+        int rc;
+        if (sub == 1) rc = launch_stream_inst<FMT, NT, 1>(hal, st, q, tmap, g.smem_bytes, grid);
+        else if (sub == 2) rc = launch_stream_inst<FMT, NT, 2>(hal, st, q, tmap, g.smem_bytes, grid);
+        else rc = launch_stream_inst<FMT, NT, 4>(hal, st, q, tmap, g.smem_bytes, grid);
+        if (rc) return rc;
+    }
+    return QWC_OK;
+}
+
 template <int FMT>
-int launch_fmt(const qwc_hal* hal, cudaStream_t st, GemvParams p, int64_t m, bool stream_ok) {
+int launch_fmt(const qwc_hal* hal, cudaStream_t st, GemvParams p, int64_t m, bool stream_ok, int total_units,
+               float* workspace) {
     const char* xb = reinterpret_cast<const char*>(p.x);
     char* yb = static_cast<char*>(p.y);
     const int64_t ysz = p.y_f16 ? 2 : 4;
@@ -517,6 +695,7 @@ int launch_fmt(const qwc_hal* hal, cudaStream_t st, GemvParams p, int64_t m, boo
         if (p.epilogue == QWC_EPI_SILU_PAIR_FWHT)
             return qwc_fail(QWC_ERR_BAD_GEOMETRY, "fused FWHT epilogue needs 16-byte aligned rows (K %% 128 == 0)");
         p.m = static_cast<int>(m);
+        p.units = total_units;
         const int64_t items = static_cast<int64_t>(p.n_out) * m;
         int64_t grid = (items + 7) / 8;
         if (grid > hal->sm_count * 8) grid = hal->sm_count * 8;
@@ -531,7 +710,8 @@ int launch_fmt(const qwc_hal* hal, cudaStream_t st, GemvParams p, int64_t m, boo
         q.m = static_cast<int>(m - m0 < 16 ? m - m0 : 16);
         q.x = reinterpret_cast<const __half*>(xb + m0 * p.ldx * 2);
         q.y = yb + m0 * p.ldy * ysz;
-        const int rc = q.m <= 8 ? launch_stream<FMT, 1>(hal, st, q) : launch_stream<FMT, 2>(hal, st, q);
+        const int rc = q.m <= 8 ? launch_stream<FMT, 1>(hal, st, q, total_units, workspace)
+                                : launch_stream<FMT, 2>(hal, st, q, total_units, workspace);
         if (rc) return rc;
     }
     return QWC_OK;
@@ -539,9 +719,21 @@ int launch_fmt(const qwc_hal* hal, cudaStream_t st, GemvParams p, int64_t m, boo
 
 }  // namespace
 
+// Bytes of f32 scratch a call needs: non-zero only when the staged activations of up to 16 tokens exceed their
+// shared-memory share, so that K is processed in slices whose raw sums are carried in the workspace.
+size_t qwc_gemv_workspace_bytes(const qwc_weight_view* w, int64_t m) {
+    const int64_t mm = m < 16 ? m : 16;
+    if (mm <= 0) return 0;
+    const int64_t row_bytes = (w->k / w->group) * qwc_block_bytes(w->kind, w->bits, w->group);
+    if (row_bytes % 16 != 0) return 0;  // row-wise kernel: no scratch
+    const int64_t x_cap_units = kXCapBytes / (mm * 64);
+    return (w->k / 32) > x_cap_units ? static_cast<size_t>(mm) * static_cast<size_t>(w->n) * 4 : 0;
+}
+
 // Host entry used by qwc_gemm.  All arguments were validated by the caller.
 int qwc_launch_gemv(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
-                    void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, bool allow_stream) {
+                    void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace,
+                    size_t workspace_bytes) {
     GemvParams p{};
     const int fmt = qwc_fmt_of(*w);
     const int64_t bb = qwc_block_bytes(w->kind, w->bits, w->group);
@@ -553,18 +745,27 @@ int qwc_launch_gemv(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* 
     p.y = y;
     p.ldy = ldy;
     p.status = hal->status;
+    p.n = static_cast<int>(w->n);
     p.n_out = static_cast<int>(epilogue == QWC_EPI_NONE ? w->n : w->n / 2);
-    p.units = static_cast<int>(w->k / 32);
     p.y_f16 = y_dtype == QWC_F16;
     p.epilogue = epilogue;
     p.x_is_rotated = x_is_rotated;
     p.row_quantum = epilogue == QWC_EPI_SILU_PAIR_FWHT ? 32 : 1;
-    const bool stream_ok = allow_stream && (p.row_bytes % 16 == 0) && (reinterpret_cast<uintptr_t>(w->blocks) % 16 == 0) &&
-                           (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0);
+    p.sh4 = 1u << 28;
+    p.sh8 = 1u << 24;
+    p.sh12 = 1u << 20;
+    const int total_units = static_cast<int>(w->k / 32);
+    const bool stream_ok = (p.row_bytes % 16 == 0) && (reinterpret_cast<uintptr_t>(w->blocks) % 16 == 0);
+    const size_t need = stream_ok ? qwc_gemv_workspace_bytes(w, m) : 0;
+    if (need > 0 && (workspace == nullptr || workspace_bytes < need))
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace of %zu bytes needed (qwc_gemm_workspace_bytes), got %zu", need, workspace_bytes);
+    if (need > 0 && reinterpret_cast<uintptr_t>(workspace) % 4 != 0)
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace must be 4-byte aligned");
+    float* ws = need > 0 ? static_cast<float*>(workspace) : nullptr;
     switch (fmt) {
-        case FMT_HQ4_G32_M5: return launch_fmt<FMT_HQ4_G32_M5>(hal, st, p, m, stream_ok);
-        case FMT_HQ8_G32: return launch_fmt<FMT_HQ8_G32>(hal, st, p, m, stream_ok);
-        case FMT_HQ4_G64: return launch_fmt<FMT_HQ4_G64>(hal, st, p, m, stream_ok);
+        case FMT_HQ4_G32_M5: return launch_fmt<FMT_HQ4_G32_M5>(hal, st, p, m, stream_ok, total_units, ws);
+        case FMT_HQ8_G32: return launch_fmt<FMT_HQ8_G32>(hal, st, p, m, stream_ok, total_units, ws);
+        case FMT_HQ4_G64: return launch_fmt<FMT_HQ4_G64>(hal, st, p, m, stream_ok, total_units, ws);
         default: return qwc_fail(QWC_ERR_BAD_WEIGHTS, "unsupported container");
     }
 }

@@ -21,7 +21,10 @@ def _run(q, hal, view, x, epi=0, out_dtype=torch.float32, rotated=False):
     m = x.shape[0]
     n_out = view.n if epi == 0 else view.n // 2
     y = torch.full((m, n_out), float("nan"), dtype=out_dtype, device="cuda")
-    q.QWGemm.encode(hal, view, torch.from_numpy(np.ascontiguousarray(x)).cuda(), y, epi=epi, x_is_rotated=rotated)
+    nws = q.QWGemm.workspaceBytes(hal, view, m, epi, rotated)
+    ws = torch.empty(nws, dtype=torch.uint8, device="cuda") if nws else None
+    q.QWGemm.encode(hal, view, torch.from_numpy(np.ascontiguousarray(x)).cuda(), y, epi=epi, x_is_rotated=rotated,
+                    workspace=ws)
     return y.float().cpu().numpy()
 
 
@@ -190,3 +193,27 @@ def test_decode_gemv_bench_shape_properties(hal, oracle):
     ys = _run(q, hal, view, s, rotated=True)
     ya = _run(q, hal, view, xa)
     assert np.abs(ys - (y + ya)).max() <= 4e-3 * np.abs(ys).max()
+
+
+def test_k_sliced_call_needs_and_uses_the_workspace(hal, oracle):
+    # 16 tokens x K = 5120: the staged activations exceed their shared-memory share, K is processed in slices
+    # and the raw sums travel through the caller's workspace.
+    import qwegn_b200 as q
+    n, k, m = 200, 5120, 16
+    fmt = oracle.HQ4_G32
+    rng = np.random.default_rng(8)
+    blocks = oracle.quantize(rng.normal(0.0, 0.02, (n, k)).astype(np.float32), fmt)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    view = _bank(q, blocks, "HQ4_G32")
+    assert q.QWGemm.workspaceBytes(hal, view, m) == m * n * 4
+    assert q.QWGemm.workspaceBytes(hal, view, 1) == 0
+    xd = torch.from_numpy(x).cuda()
+    y = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    with pytest.raises(q.QWGemmError) as e:
+        q.QWGemm.encode(hal, view, xd, y)
+    assert e.value.case == "badShape"
+    assert_matmul_close(_run(q, hal, view, x), oracle.matmul(blocks, fmt, x))
+    gu = oracle.quantize(rng.normal(0.0, 0.03, (128, k)).astype(np.float32), fmt)
+    href = oracle.swiglu_f16(oracle.matmul(gu, fmt, x), rotate=True).astype(np.float32)
+    assert_matmul_close(_run(q, hal, _bank(q, gu, "HQ4_G32"), x, epi=q.EPI_SILU_PAIR_FWHT, out_dtype=torch.float16),
+                        href, tight=4e-3)
