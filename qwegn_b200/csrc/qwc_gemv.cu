@@ -68,6 +68,7 @@ struct GemvParams {
     int x_bytes;      // smem bytes of the activation region
     int red_bytes;    // smem bytes of the team reduction region
     uint32_t sh4, sh8, sh12;  // 2^28, 2^24, 2^20: mul.hi by these is a right shift by 4, 8, 12
+    int dbg_skip;     // experiment: consumers skip the math
     int use_tmap;     // full 16-row tiles arrive by one 2-D tensor copy instead of 16 row copies
 };
 
@@ -92,6 +93,12 @@ __device__ __forceinline__ uint32_t hsub2_1024(uint32_t a) {
 // as mul.hi(v, 2^28 / 2^24 / 2^20) on the FMA pipe; sh = {2^28, 2^24, 2^20} arrives as kernel parameters so the
 // compiler cannot turn the multiplies back into shifts.
 __device__ __forceinline__ uint32_t shr_fma(uint32_t v, uint32_t pow2) { return __umulhi(v, pow2); }
+// (v & 0x000F000F) | 0x64006400 as one three-input logic op: two nibbles -> the f16 pair (1024 + q, 1024 + q').
+__device__ __forceinline__ uint32_t nib2_f16x2(uint32_t v) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(v), "r"(0x000F000Fu), "r"(0x64006400u));
+    return d;
+}
 
 template <int FMT>
 __device__ __forceinline__ void decode_unit(const uint8_t* ublk, int wofs, const uint32_t sh[3], uint32_t a[16]) {
@@ -102,10 +109,10 @@ __device__ __forceinline__ void decode_unit(const uint8_t* ublk, int wofs, const
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const uint32_t v = lds32(ublk + wofs + 4 * w);
-            a[4 * w] = hfma2_u32((v & 0x000F000Fu) | 0x64006400u, s2, b2);
+            a[4 * w] = hfma2_u32(nib2_f16x2(v), s2, b2);
 #pragma unroll
             for (int i = 1; i < 4; ++i)
-                a[4 * w + i] = hfma2_u32((shr_fma(v, sh[i - 1]) & 0x000F000Fu) | 0x64006400u, s2, b2);
+                a[4 * w + i] = hfma2_u32(nib2_f16x2(v >> (4 * i)), s2, b2);
         }
     } else if (FMT == FMT_HQ8_G32) {
 #pragma unroll
@@ -118,10 +125,10 @@ __device__ __forceinline__ void decode_unit(const uint8_t* ublk, int wofs, const
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const uint32_t v = lds32(ublk + wofs + 4 * w);
-            a[4 * w] = hfma2_u32(hsub2_1024((v & 0x000F000Fu) | 0x64006400u), s2, b2);
+            a[4 * w] = hfma2_u32(hsub2_1024(nib2_f16x2(v)), s2, b2);
 #pragma unroll
             for (int i = 1; i < 4; ++i)
-                a[4 * w + i] = hfma2_u32(hsub2_1024((shr_fma(v, sh[i - 1]) & 0x000F000Fu) | 0x64006400u), s2, b2);
+                a[4 * w + i] = hfma2_u32(hsub2_1024(nib2_f16x2(v >> (4 * i))), s2, b2);
         }
     }
 }
@@ -202,6 +209,8 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     if (warp == kConsumerWarps) {
         // ------------------------------ producer warp ------------------------------
         uint32_t q = 0;
+        int pslot = 0;
+        uint32_t pparity = 0;  // phase parity of fill q in its slot
         bool ok = true;
         for (int r = 0; r < rounds && ok; ++r) {
             const int tl = min(T, njobs - r * T);
@@ -210,9 +219,14 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                 const int u0 = c * p.chunk_units;
                 const uint32_t cbytes = static_cast<uint32_t>(min(p.chunk_units, p.units - u0)) * C::kUnitBytes;
                 for (int tau = 0; tau < tl; ++tau, ++q) {
-                    const int slot = q % p.stages;
+                    const int slot = pslot;
+                    const uint32_t wait_parity = pparity ^ 1u;  // phase of the previous use of this slot
+                    if (++pslot == p.stages) {
+                        pslot = 0;
+                        pparity ^= 1u;
+                    }
                     if (q >= static_cast<uint32_t>(p.stages)) {
-                        if (*abort_flag || !mbar_wait(&empty[slot], ((q / p.stages) - 1) & 1)) {
+                        if (*abort_flag || !mbar_wait(&empty[slot], wait_parity)) {
                             if (!*abort_flag && lane == 0) atomicCAS(p.status, 0, QWC_DEV_WAIT_EMPTY_TIMEOUT);
                             *abort_flag = 1;
                             ok = false;
@@ -350,13 +364,34 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 #pragma unroll
                     for (int i = 0; i < 4; ++i) d[s][nt][h][i] = 0.0f;
 
+        // Ring position of this team's first fill of the job; it advances by tl (the teams active in this round)
+        // per fill, so slot and phase parity are kept incrementally (no division in the loop).
+        const uint32_t q0 = static_cast<uint32_t>(r) * E * T + team;
+        int slot = q0 % p.stages;
+        uint32_t parity = (q0 / p.stages) & 1;
+        // this lane's unit inside a chunk for group wj (advances by W groups), as byte offsets into the row / x
+        int hofs0, wofs, xofs0;
+        if (FMT == FMT_HQ4_G64) {
+            const int ul = 8 * (wj >> 1) + (wj & 1) + 2 * t;  // even units, then odd units, of an 8-unit span
+            hofs0 = (ul >> 1) * 36;
+            wofs = 4 + 16 * (ul & 1);
+            xofs0 = ul * 64;
+        } else {
+            const int ul = 4 * wj + t;
+            hofs0 = ul * C::kUnitBytes;
+            wofs = 4;
+            xofs0 = ul * 64;
+        }
+        // HQ4_G64 with odd W would alternate the unit parity between steps; the host only picks W = 1 there when
+        // forced, and the general form below handles it by recomputing the offsets per group.
+        const bool g64_recompute = FMT == FMT_HQ4_G64 && (W & 1);
+        const int hstep = FMT == FMT_HQ4_G64 ? (W >> 1) * 4 * 36 : W * 4 * C::kUnitBytes;  // W groups further along the row
+        const int xstep = W * 4 * 64;
 #pragma unroll
         for (int sub = 0; sub < SUB; ++sub) {
             for (int c = 0; c < p.nchunks; ++c) {
-                const uint32_t q = static_cast<uint32_t>(r) * E * T + static_cast<uint32_t>(sub * p.nchunks + c) * tl + team;
-                const int slot = q % p.stages;
-                if (ok && !*abort_flag) {
-                    ok = mbar_wait(&full[slot], (q / p.stages) & 1);
+                if (ok) {
+                    ok = mbar_wait(&full[slot], parity);
                     if (!ok) {
                         *abort_flag = 1;
                         if (lane == 0) atomicCAS(p.status, 0, QWC_DEV_WAIT_FULL_TIMEOUT);
@@ -364,41 +399,49 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                 }
                 const int u0 = c * p.chunk_units;
                 const int cu = min(p.chunk_units, p.units - u0);
-                if (ok && !*abort_flag) {
-                    const uint8_t* row_lo = stage0 + slot * stage_bytes + gid * p.stride;
+                if (ok && !p.dbg_skip) {
+                    const uint8_t* row_lo = stage0 + slot * stage_bytes + gid * p.stride + hofs0;
                     const uint8_t* row_hi = row_lo + 8 * p.stride;
+                    const uint8_t* xu[NT];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) xu[nt] = xtok[nt] + u0 * 64 + xofs0;
                     const int ngroups = cu / C::kGroupUnits;
                     for (int g = wj; g < ngroups; g += W) {
-                        // this lane's unit inside the chunk, and where its header / payload sit in the row
-                        int ul, hofs, wofs;
-                        if (FMT == FMT_HQ4_G64) {
-                            ul = 8 * (g >> 1) + (g & 1) + 2 * t;   // even units, then odd units, of an 8-unit span
-                            hofs = (ul >> 1) * 36;
-                            wofs = 4 + 16 * (ul & 1);
-                        } else {
-                            ul = 4 * g + t;
-                            hofs = ul * C::kUnitBytes;
-                            wofs = 4;
+                        int wo = wofs;
+                        if (g64_recompute) {
+                            const int ul = 8 * (g >> 1) + (g & 1) + 2 * t;
+                            row_lo = stage0 + slot * stage_bytes + gid * p.stride + (ul >> 1) * 36;
+                            row_hi = row_lo + 8 * p.stride;
+                            wo = 4 + 16 * (ul & 1);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) xu[nt] = xtok[nt] + (u0 + ul) * 64;
                         }
                         uint32_t alo[16], ahi[16];
-                        decode_unit<FMT>(row_lo + hofs, wofs, sh, alo);
-                        decode_unit<FMT>(row_hi + hofs, wofs, sh, ahi);
+                        decode_unit<FMT>(row_lo, wo, sh, alo);
+                        decode_unit<FMT>(row_hi, wo, sh, ahi);
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) {
-                            const uint8_t* xu = xtok[nt] + (u0 + ul) * 64;
                             uint4 xv[4];
 #pragma unroll
-                            for (int cc = 0; cc < 4; ++cc) xv[cc] = *reinterpret_cast<const uint4*>(xu + xsw[nt][cc]);
+                            for (int cc = 0; cc < 4; ++cc) xv[cc] = *reinterpret_cast<const uint4*>(xu[nt] + xsw[nt][cc]);
                             const uint32_t* xp = reinterpret_cast<const uint32_t*>(xv);
 #pragma unroll
                             for (int s = 0; s < 8; ++s)
                                 mma_16816(d[sub][nt][s & 1], alo[2 * s], ahi[2 * s], alo[2 * s + 1], ahi[2 * s + 1],
                                           xp[2 * s], xp[2 * s + 1]);
+                            xu[nt] += xstep;
                         }
+                        row_lo += hstep;
+                        row_hi += hstep;
                     }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[slot]);
+                slot += tl;
+                if (slot >= p.stages) {
+                    slot -= p.stages;
+                    parity ^= 1u;
+                }
             }
         }
 
@@ -751,6 +794,7 @@ int qwc_launch_gemv(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* 
     p.epilogue = epilogue;
     p.x_is_rotated = x_is_rotated;
     p.row_quantum = epilogue == QWC_EPI_SILU_PAIR_FWHT ? 32 : 1;
+    p.dbg_skip = getenv("QWC_DBG_SKIP") != nullptr;
     p.sh4 = 1u << 28;
     p.sh8 = 1u << 24;
     p.sh12 = 1u << 20;
