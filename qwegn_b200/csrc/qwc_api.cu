@@ -15,6 +15,10 @@ int qwc_launch_quantize(const qwc_hal*, cudaStream_t, const float*, int64_t, int
 int qwc_launch_gemv(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int,
                     int64_t, int, int, void*, size_t);
 size_t qwc_gemv_workspace_bytes(const qwc_weight_view*, int64_t);
+bool qwc_gemm_tc_supported(const qwc_hal*, const qwc_weight_view*, int64_t, int);
+size_t qwc_gemm_tc_workspace_bytes(const qwc_weight_view*, int64_t, int);
+int qwc_launch_gemm_tc(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int, int64_t,
+                       int, void*, size_t);
 
 static thread_local char g_err[512] = "";
 
@@ -149,9 +153,13 @@ int qwc_gemm_plan(int64_t m, int64_t n, int64_t k, int32_t kind, int32_t bits, i
         out->backend = QWC_BACKEND_ROWWISE;
         out->threads_per_cta = 256;
         snprintf(out->kernel, sizeof(out->kernel), "qwc_gemv_rowwise_%s", fname);
+    } else if (m > 16 && epilogue == QWC_EPI_NONE && (fmt == FMT_HQ4_G32_M5 || fmt == FMT_HQ8_G32) && k % 128 == 0) {
+        out->backend = QWC_BACKEND_TCGEN05;
+        out->threads_per_cta = 14 * 32;
+        snprintf(out->kernel, sizeof(out->kernel), "qwc_gemm_tc_%s_128x256x64", fname);
     } else {
         out->backend = QWC_BACKEND_STREAM_MMA;
-        out->threads_per_cta = 16 * 32;
+        out->threads_per_cta = 17 * 32;
         snprintf(out->kernel, sizeof(out->kernel), "qwc_gemv_stream_%s_m%d", fname, m <= 8 ? 8 : 16);
     }
     return QWC_OK;
@@ -198,8 +206,10 @@ int qwc_quantize(qwc_hal* hal, qwc_stream stream, const float* w_f32, int64_t n,
     return qwc_launch_quantize(hal, static_cast<cudaStream_t>(stream), w_f32, n, k, qwc_fmt_of(v), blocks_out);
 }
 
-size_t qwc_gemm_workspace_bytes(const qwc_hal*, const qwc_weight_view* w, int64_t m, int32_t, int32_t) {
-    if (!w || w->k <= 0 || w->group <= 0 || qwc_fmt_of(*w) == FMT_UNSUPPORTED) return 0;
+size_t qwc_gemm_workspace_bytes(const qwc_hal* hal, const qwc_weight_view* w, int64_t m, int32_t epilogue,
+                                int32_t x_is_rotated) {
+    if (!hal || !w || w->k <= 0 || w->group <= 0 || qwc_fmt_of(*w) == FMT_UNSUPPORTED) return 0;
+    if (qwc_gemm_tc_supported(hal, w, m, epilogue)) return qwc_gemm_tc_workspace_bytes(w, m, x_is_rotated);
     return qwc_gemv_workspace_bytes(w, m);
 }
 
@@ -225,6 +235,9 @@ int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const vo
     if (ldx < w->k) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldx=%lld < k=%lld", (long long)ldx, (long long)w->k);
     if (ldy < n_out) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldy=%lld < output width %lld", (long long)ldy, (long long)n_out);
     if (reinterpret_cast<uintptr_t>(x_f16) % 2 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "x must be 2-byte aligned");
+    if (qwc_gemm_tc_supported(hal, w, m, epilogue))
+        return qwc_launch_gemm_tc(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, x_is_rotated,
+                                  workspace, workspace_bytes);
     return qwc_launch_gemv(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, epilogue,
                            x_is_rotated, workspace, workspace_bytes);
 }

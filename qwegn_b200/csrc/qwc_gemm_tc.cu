@@ -1,0 +1,482 @@
+// Prefill GEMM over packed HQ blocks on the 5th-generation tensor cores: the CUDA twin of the reference's
+// qwg_gemm_q4g_h16 / qwg_gemm_q4g_nax_f32 / qwg_gemm_aq*_h16 kernels (Sources/QWMetal/gemm/qwgemm_batched.metal:24-36,
+// 266-277; tile loop Sources/QWMetal/include/qw_gemm_nax.metalh:153-423).
+//
+//   Y[m, n] = sum_k Xrot[m, k] * Wrot[n, k],   f16 operands, f32 accumulate in tensor memory.
+//
+// One persistent CTA per SM walks (weight tile, token tile) pairs.  Per 64-wide K tile:
+//   * a TMA warp brings the packed weight rows, unchanged, into shared memory (2-D tensor copy, 128 rows x one
+//     raw step of 128 k) and the rotated activations (256 tokens x 64 k, 128-byte swizzle);
+//   * eight converter warps decode the packed blocks to f16 in registers (magic-bias form, one f16 FMA with scale
+//     and bias: the reference's in-register decode, qw_gemm_nax.metalh:114-127) and store them as the K-major,
+//     128-byte-swizzled operand tile the tensor core reads;
+//   * one thread issues tcgen05.mma (M = 128 weight rows, N = 256 tokens, K = 16) into a TMEM accumulator;
+//     tcgen05.commit releases the stage, and after the last K tile hands the accumulator to the epilogue;
+//   * four epilogue warps read the accumulator with tcgen05.ld (lane = weight row), round to the output type and
+//     store; two accumulators alternate so the epilogue of one tile overlaps the main loop of the next.
+// Weights are the M operand so that 256 tokens share every decoded weight (one decode per 256 FMAs per weight).
+// Every mbarrier wait is bounded; a wait that gives up sets the device status word and the CTA winds down.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "qwc_common.cuh"
+
+namespace {
+
+constexpr int kBM = 128;        // weight rows per tile (UMMA M)
+constexpr int kBN = 256;        // tokens per tile (UMMA N)
+constexpr int kBK = 64;         // k per operand tile (one 128-byte swizzle atom of f16)
+constexpr int kRawK = 128;      // k per raw weight step (two operand tiles)
+constexpr int kConvWarps = 8;
+constexpr int kEpiWarps = 4;
+constexpr int kWarps = 2 + kConvWarps + kEpiWarps;
+constexpr int kTcThreads = kWarps * 32;
+constexpr int kWTileBytes = kBM * kBK * 2;   // 16 KB
+constexpr int kXTileBytes = kBN * kBK * 2;   // 32 KB
+constexpr int kMaxAB = 4, kMaxRaw = 3;
+
+struct TcParams {
+    void* y;
+    int64_t ldy;
+    int32_t* status;
+    int m, n, k;
+    int y_f16;
+    int ab_stages, raw_stages;
+    int raw_row_bytes;   // packed bytes of 128 k of one row: 80 (HQ4_G32_M5) or 144 (HQ8_G32)
+    int m_tiles, n_tiles;
+};
+
+__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// K-major, 128-byte-swizzled operand descriptor: start address, LBO = 1 (unused for swizzled K-major),
+// SBO = 1024 B (one 8-row atom), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, N = 256, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t nib2_f16x2(uint32_t v) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(v), "r"(0x000F000Fu), "r"(0x64006400u));
+    return d;
+}
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, __half2 s2, __half2 b2) {
+    const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), s2, b2);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t hsub2_1024(uint32_t a) {
+    const uint32_t k = 0x64006400u;
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&k));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// Decode one 32-element unit of one row into four 16-byte chunks (8 consecutive k each, natural order).
+template <int FMT>
+__device__ __forceinline__ void decode_unit_natural(const uint8_t* blk, uint4 out[4]) {
+    const uint32_t hdr = lds32(blk);
+    const __half2 h = *reinterpret_cast<const __half2*>(&hdr);
+    const __half2 s2 = __half2half2(__low2half(h)), b2 = __half2half2(__high2half(h));
+    if (FMT == FMT_HQ4_G32_M5) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t v = lds32(blk + 4 + 4 * w);
+            out[w].x = hfma2_u32(nib2_f16x2(v), s2, b2);
+            out[w].y = hfma2_u32(nib2_f16x2(v >> 4), s2, b2);
+            out[w].z = hfma2_u32(nib2_f16x2(v >> 8), s2, b2);
+            out[w].w = hfma2_u32(nib2_f16x2(v >> 12), s2, b2);
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t v0 = lds32(blk + 4 + 8 * c), v1 = lds32(blk + 8 + 8 * c);
+            out[c].x = hfma2_u32(hsub2_1024(__byte_perm(v0, 0x64646464u, 0x4140)), s2, b2);
+            out[c].y = hfma2_u32(hsub2_1024(__byte_perm(v0, 0x64646464u, 0x4342)), s2, b2);
+            out[c].z = hfma2_u32(hsub2_1024(__byte_perm(v1, 0x64646464u, 0x4140)), s2, b2);
+            out[c].w = hfma2_u32(hsub2_1024(__byte_perm(v1, 0x64646464u, 0x4342)), s2, b2);
+        }
+    }
+}
+
+struct Ring {
+    int slot;
+    uint32_t parity;
+    int depth;
+    __device__ __forceinline__ void advance() {
+        if (++slot == depth) {
+            slot = 0;
+            parity ^= 1u;
+        }
+    }
+};
+
+template <int FMT>
+__global__ void __launch_bounds__(kTcThreads, 1)
+qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // layout (1024-byte aligned base): [W tiles][X tiles][raw stages][barriers]
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* wt = smem;
+    uint8_t* xt = wt + p.ab_stages * kWTileBytes;
+    uint8_t* raw = xt + p.ab_stages * kXTileBytes;
+    const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + p.raw_stages * raw_stage_bytes);
+    uint64_t* x_full = bars;                  // [kMaxAB]
+    uint64_t* w_full = bars + kMaxAB;         // [kMaxAB]
+    uint64_t* ab_empty = bars + 2 * kMaxAB;   // [kMaxAB]
+    uint64_t* raw_full = bars + 3 * kMaxAB;   // [kMaxRaw]
+    uint64_t* raw_empty = raw_full + kMaxRaw; // [kMaxRaw]
+    uint64_t* acc_full = raw_empty + kMaxRaw; // [2]
+    uint64_t* acc_empty = acc_full + 2;       // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.ab_stages; ++s) {
+            mbar_init(&x_full[s], 1);
+            mbar_init(&w_full[s], kConvWarps);
+            mbar_init(&ab_empty[s], 1);
+        }
+        for (int s = 0; s < p.raw_stages; ++s) {
+            mbar_init(&raw_full[s], 1);
+            mbar_init(&raw_empty[s], kConvWarps);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], kEpiWarps);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        // 512 columns: two 128 x 256 f32 accumulators.  One CTA per SM, so the allocation cannot contend.
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int ktiles = p.k / kBK;
+    const int raw_steps = p.k / kRawK;
+
+    auto fail = [&](int code) {
+        if (!*abort_flag) atomicCAS(p.status, 0, code);
+        *abort_flag = 1;
+    };
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        if (lane == 0) {
+            Ring ab{0, 0, p.ab_stages}, rr{0, 0, p.raw_stages};
+            uint32_t ab_fills = 0, raw_fills = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+                for (int rs = 0; rs < raw_steps && ok; ++rs) {
+                    if (raw_fills >= static_cast<uint32_t>(p.raw_stages) && !mbar_wait(&raw_empty[rr.slot], rr.parity ^ 1u)) {
+                        fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&raw_full[rr.slot], static_cast<uint32_t>(kBM * p.raw_row_bytes));
+                    tma_load_2d(raw + rr.slot * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), nt * kBM, &raw_full[rr.slot]);
+                    rr.advance();
+                    ++raw_fills;
+                    for (int h = 0; h < kRawK / kBK && ok; ++h) {
+                        if (ab_fills >= static_cast<uint32_t>(p.ab_stages) && !mbar_wait(&ab_empty[ab.slot], ab.parity ^ 1u)) {
+                            fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(&x_full[ab.slot], kXTileBytes);
+                        tma_load_2d(xt + ab.slot * kXTileBytes, &xmap, (rs * (kRawK / kBK) + h) * kBK, mt * kBN, &x_full[ab.slot]);
+                        ab.advance();
+                        ++ab_fills;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer -------------------------------
+        if (lane == 0) {
+            Ring ab{0, 0, p.ab_stages};
+            uint32_t tiles_done = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tiles_done) {
+                const int as = tiles_done & 1;
+                if (tiles_done >= 2 && !mbar_wait(&acc_empty[as], ((tiles_done >> 1) - 1) & 1)) {
+                    fail(QWC_DEV_WAIT_TMEM_TIMEOUT);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * kBN);
+                for (int kt = 0; kt < ktiles; ++kt) {
+                    if (!mbar_wait(&x_full[ab.slot], ab.parity) || !mbar_wait(&w_full[ab.slot], ab.parity)) {
+                        fail(QWC_DEV_WAIT_FULL_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(wt + ab.slot * kWTileBytes), b_addr = smem_u32(xt + ab.slot * kXTileBytes);
+#pragma unroll
+                    for (int j = 0; j < kBK / 16; ++j)
+                        umma_f16(d_tmem, umma_desc_sw128(a_addr + j * 32), umma_desc_sw128(b_addr + j * 32), (kt > 0 || j > 0) ? 1u : 0u);
+                    umma_commit(&ab_empty[ab.slot]);  // frees the stage when these MMAs have read it
+                    ab.advance();
+                }
+                if (ok) umma_commit(&acc_full[as]);
+            }
+        }
+        __syncwarp();
+    } else if (warp < 2 + kConvWarps) {
+        // ------------------------------- converters -------------------------------
+        const int cw = warp - 2;
+        const int r8 = lane >> 2, u = lane & 3;   // 8 rows x 4 units per warp step
+        const int unit_bytes = p.raw_row_bytes / 4;
+        Ring ab{0, 0, p.ab_stages}, rr{0, 0, p.raw_stages};
+        uint32_t ab_uses = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int rs = 0; rs < raw_steps && ok; ++rs) {
+                // both operand stages of this raw step must have been read by the tensor core
+                Ring ab1 = ab;
+                ab1.advance();
+                if (!mbar_wait(&raw_full[rr.slot], rr.parity) ||
+                    (ab_uses >= static_cast<uint32_t>(p.ab_stages) && !mbar_wait(&ab_empty[ab.slot], ab.parity ^ 1u)) ||
+                    (ab_uses + 1 >= static_cast<uint32_t>(p.ab_stages) && !mbar_wait(&ab_empty[ab1.slot], ab1.parity ^ 1u))) {
+                    if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+                uint8_t* wdst = wt + ((u >> 1) ? ab1.slot : ab.slot) * kWTileBytes;
+                const uint8_t* rbase = raw + rr.slot * raw_stage_bytes;
+#pragma unroll
+                for (int it = 0; it < kBM / (kConvWarps * 8); ++it) {
+                    const int row = cw * (kBM / kConvWarps) + it * 8 + r8;
+                    uint4 ch[4];
+                    decode_unit_natural<FMT>(rbase + row * p.raw_row_bytes + u * unit_bytes, ch);
+                    uint8_t* rowp = wdst + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        *reinterpret_cast<uint4*>(rowp + ((((u & 1) * 4 + c) ^ (row & 7)) << 4)) = ch[c];
+                }
+                fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async-proxy reads
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&w_full[ab.slot]);
+                    mbar_arrive(&w_full[ab1.slot]);
+                    mbar_arrive(&raw_empty[rr.slot]);
+                }
+                ab = ab1;
+                ab.advance();
+                ab_uses += 2;
+                rr.advance();
+            }
+        }
+    } else {
+        // ------------------------------- epilogue -------------------------------
+        const int quarter = warp & 3;   // TMEM lanes [32 * quarter, 32 * quarter + 32)
+        uint32_t tiles_done = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tiles_done) {
+            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+            const int as = tiles_done & 1;
+            if (!mbar_wait(&acc_full[as], (tiles_done >> 1) & 1)) {
+                if (lane == 0) fail(QWC_DEV_WAIT_MMA_TIMEOUT);
+                break;
+            }
+            tc_fence_after();
+            const int n = nt * kBM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * kBN);
+#pragma unroll 1
+            for (int c = 0; c < kBN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c * 32, r);
+                tmem_ld_wait();
+                const int m0 = mt * kBN + c * 32;
+                if (n < p.n) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (m0 + j < p.m) {
+                            const int64_t o = static_cast<int64_t>(m0 + j) * p.ldy + n;
+                            if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(__uint_as_float(r[j]));
+                            else static_cast<float*>(p.y)[o] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[as]);
+        }
+    }
+
+    // teardown: everyone meets, then the allocating warp returns the tensor memory
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+}
+
+// Out-of-place activation rotation for the prefill path: rows of ldx -> dense rows of k.
+__global__ void __launch_bounds__(256) qwc_rotate_rows_kernel(const __half* __restrict__ x, int64_t ldx, __half* __restrict__ out,
+                                                              int64_t m, int64_t k) {
+    const int lane = threadIdx.x & 31;
+    const int64_t units = k / 32, total = m * units;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t it = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); it < total; it += warps) {
+        const int64_t r = it / units, u = it % units;
+        float v = __half2float(x[r * ldx + u * 32 + lane]);
+#pragma unroll
+        for (int h = 1; h < 32; h <<= 1) v = fwht_xor_stage(v, h, (lane & h) != 0);
+        out[r * k + u * 32 + lane] = __float2half_rn(__fmul_rn(v, qwc_inv_sqrt32()));
+    }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+template <int FMT>
+int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& xmap, int smem) {
+    static bool configured[64] = {};
+    if (!configured[hal->device & 63]) {
+        QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured[hal->device & 63] = true;
+    }
+    int grid = p.m_tiles * p.n_tiles;
+    if (grid > hal->sm_count) grid = hal->sm_count;
+    qwc_gemm_tc_kernel<FMT><<<grid, kTcThreads, smem, st>>>(p, wmap, xmap);
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
+
+}  // namespace
+
+// Can the tensor-core path take this call?  (HQ4_G32_M5 and HQ8_G32 banks, K % 128 == 0, 16-byte aligned rows.)
+bool qwc_gemm_tc_supported(const qwc_hal* hal, const qwc_weight_view* w, int64_t m, int epilogue) {
+    const int fmt = qwc_fmt_of(*w);
+    if (hal->encode_tiled == nullptr || epilogue != QWC_EPI_NONE) return false;
+    if (fmt != FMT_HQ4_G32_M5 && fmt != FMT_HQ8_G32) return false;
+    if (w->k % kRawK != 0 || m <= 16) return false;
+    if (reinterpret_cast<uintptr_t>(w->blocks) % 16 != 0) return false;
+    static const bool off = getenv("QWC_NO_TCGEN05") != nullptr;
+    return !off;
+}
+
+// Scratch for the rotated activations when the caller passes standard-basis x.
+size_t qwc_gemm_tc_workspace_bytes(const qwc_weight_view* w, int64_t m, int x_is_rotated) {
+    return x_is_rotated ? 0 : static_cast<size_t>(m) * static_cast<size_t>(w->k) * 2;
+}
+
+int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
+                       void* y, int y_dtype, int64_t ldy, int x_is_rotated, void* workspace, size_t workspace_bytes) {
+    const int fmt = qwc_fmt_of(*w);
+    const __half* xr = static_cast<const __half*>(x);
+    int64_t ldxr = ldx;
+    if (!x_is_rotated) {
+        const size_t need = qwc_gemm_tc_workspace_bytes(w, m, 0);
+        if (workspace == nullptr || workspace_bytes < need)
+            return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace of %zu bytes needed (qwc_gemm_workspace_bytes), got %zu", need, workspace_bytes);
+        if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace must be 16-byte aligned");
+        int64_t blocks = (m * (w->k / 32) + 7) / 8;
+        if (blocks > hal->sm_count * 16) blocks = hal->sm_count * 16;
+        qwc_rotate_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(xr, ldx, static_cast<__half*>(workspace), m, w->k);
+        QWC_CUDA_TRY(cudaGetLastError());
+        xr = static_cast<const __half*>(workspace);
+        ldxr = w->k;
+    } else if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || ldx % 8 != 0) {
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "rotated activations must be 16-byte aligned with ldx %% 8 == 0 for the tensor-core path");
+    }
+    TcParams p{};
+    p.y = y;
+    p.ldy = ldy;
+    p.status = hal->status;
+    p.m = static_cast<int>(m);
+    p.n = static_cast<int>(w->n);
+    p.k = static_cast<int>(w->k);
+    p.y_f16 = y_dtype == QWC_F16;
+    p.raw_row_bytes = fmt == FMT_HQ4_G32_M5 ? 80 : 144;
+    p.m_tiles = static_cast<int>((m + kBN - 1) / kBN);
+    p.n_tiles = static_cast<int>((w->n + kBM - 1) / kBM);
+    const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
+    p.raw_stages = kMaxRaw;
+    p.ab_stages = kMaxAB;
+    auto smem_need = [&](int ab, int rs) { return 1024 + ab * (kWTileBytes + kXTileBytes) + rs * raw_stage_bytes + 512; };
+    while (smem_need(p.ab_stages, p.raw_stages) > 227 * 1024 && p.raw_stages > 2) --p.raw_stages;
+    while (smem_need(p.ab_stages, p.raw_stages) > 227 * 1024 && p.ab_stages > 2) --p.ab_stages;
+    const int smem = smem_need(p.ab_stages, p.raw_stages);
+
+    const EncodeFn enc = reinterpret_cast<EncodeFn>(hal->encode_tiled);
+    alignas(64) CUtensorMap wmap, xmap;
+    const int64_t row_bytes = (w->k / 32) * (fmt == FMT_HQ4_G32_M5 ? 20 : 36);
+    {
+        const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(row_bytes / 8), static_cast<cuuint64_t>(w->n)};
+        const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(row_bytes)};
+        const cuuint32_t box[2] = {static_cast<cuuint32_t>(p.raw_row_bytes / 8), static_cast<cuuint32_t>(kBM)};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w->blocks), gdim, gstride, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return qwc_fail(QWC_ERR_CUDA, "cuTensorMapEncodeTiled(weights) failed with %d", static_cast<int>(cr));
+    }
+    {
+        const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(w->k), static_cast<cuuint64_t>(m)};
+        const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ldxr * 2)};
+        const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(kBN)};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult cr = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(xr), gdim, gstride, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return qwc_fail(QWC_ERR_CUDA, "cuTensorMapEncodeTiled(activations) failed with %d", static_cast<int>(cr));
+    }
+    if (fmt == FMT_HQ4_G32_M5) return launch_tc<FMT_HQ4_G32_M5>(hal, st, p, wmap, xmap, smem);
+    return launch_tc<FMT_HQ8_G32>(hal, st, p, wmap, xmap, smem);
+}

@@ -1,0 +1,67 @@
+"""Prefill GEMM (tcgen05 path, M > 16) through the C ABI against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_matmul_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _bank(q, blocks, name):
+    n, nb, _ = blocks.shape
+    k = nb * q.CONTAINERS[name].group
+    return q.QWWeightView(torch.from_numpy(np.ascontiguousarray(blocks).reshape(-1)).cuda(), n, k, q.CONTAINERS[name])
+
+
+def _run(q, hal, view, x, out_dtype=torch.float16, rotated=False):
+    m = x.shape[0]
+    y = torch.full((m, view.n), float("nan"), dtype=out_dtype, device="cuda")
+    nws = q.QWGemm.workspaceBytes(hal, view, m, 0, rotated)
+    ws = torch.empty(nws, dtype=torch.uint8, device="cuda") if nws else None
+    q.QWGemm.encode(hal, view, torch.from_numpy(np.ascontiguousarray(x)).cuda(), y, x_is_rotated=rotated, workspace=ws)
+    return y.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("name", ["HQ4_G32", "HQ8_G32"])
+@pytest.mark.parametrize("shape", [(17, 128, 128), (64, 200, 512), (256, 128, 1024), (300, 1000, 640), (1024, 384, 2560)])
+def test_prefill_vs_oracle(hal, oracle, name, shape):
+    import qwegn_b200 as q
+    m, n, k = shape
+    assert q.QWGemm.plan(m, n, k, q.CONTAINERS[name]).backend == 2
+    fmt = oracle.FORMATS[name]
+    rng = np.random.default_rng(m + n + k)
+    blocks = oracle.quantize(rng.normal(0.0, 0.02, (n, k)).astype(np.float32), fmt)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    view = _bank(q, blocks, name)
+    yref = oracle.matmul(blocks, fmt, x)
+    assert_matmul_close(_run(q, hal, view, x, out_dtype=torch.float32), yref)
+    assert_matmul_close(_run(q, hal, view, x), yref, tight=3e-3)
+    xr = oracle.fwht32_f16(x)
+    assert_matmul_close(_run(q, hal, view, xr, rotated=True, out_dtype=torch.float32), yref)
+
+
+def test_prefill_matches_the_gemv_path_row_by_row(hal, oracle):
+    # Twin test (Tests/QWGEMMTests/QWBatchedGemmTests.swift:37-140: batched GEMM vs per-row GEMV, max |d| < 0.05).
+    import qwegn_b200 as q
+    m, n, k = 96, 512, 1024
+    rng = np.random.default_rng(12)
+    blocks = oracle.quantize(rng.normal(0.0, 0.02, (n, k)).astype(np.float32), oracle.HQ4_G32)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    view = _bank(q, blocks, "HQ4_G32")
+    y = _run(q, hal, view, x, out_dtype=torch.float32)
+    rows = np.concatenate([_run(q, hal, view, x[i:i + 8], out_dtype=torch.float32) for i in range(0, m, 8)])
+    assert np.abs(y - rows).max() < 1e-3
+
+
+def test_prefill_needs_workspace_for_plain_activations(hal, oracle):
+    import qwegn_b200 as q
+    m, n, k = 64, 128, 256
+    blocks = oracle.quantize(np.ones((n, k), dtype=np.float32), oracle.HQ4_G32)
+    view = _bank(q, blocks, "HQ4_G32")
+    assert q.QWGemm.workspaceBytes(hal, view, m, 0, False) == m * k * 2
+    assert q.QWGemm.workspaceBytes(hal, view, m, 0, True) == 0
+    x = torch.zeros((m, k), dtype=torch.float16, device="cuda")
+    y = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    with pytest.raises(q.QWGemmError):
+        q.QWGemm.encode(hal, view, x, y)
