@@ -129,6 +129,74 @@ int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const vo
 size_t qwc_gemm_workspace_bytes(const qwc_hal* hal, const qwc_weight_view* w, int64_t m, int32_t epilogue,
                                 int32_t x_is_rotated);
 
+/* ---- mixture of experts ---------------------------------------------------------------------------------------
+ * The operator chain of QWMoEOperator.encodeResident (Sources/Operators/QWGEMM/QWMoEOperator.swift:206-442), grouped
+ * path: route -> pair sort + tile plan -> gather -> grouped gate/up GEMM -> SwiGLU + FWHT -> grouped down GEMM ->
+ * weighted combine.  All scratch is caller-allocated (QWMoEOperator.Scratch, :131-192). */
+
+/* One tile of a grouped expert GEMM (the tile list of Sources/QWMetal/gemm/qwgemm_moe_group_f32.metal:82-115,
+ * with 128 expert weight rows x up to 256 expert-sorted activation rows per tile). */
+typedef struct {
+    int32_t w_row0; /* first weight row of the tile in the stacked expert bank */
+    int32_t w_rows; /* valid weight rows (<= 128) */
+    int32_t x_row0; /* first expert-sorted activation row */
+    int32_t x_rows; /* valid activation rows (<= 256) */
+    int32_t y_col0; /* output column of the tile's first weight row */
+    int32_t expert;
+    int32_t pad0, pad1;
+} qwc_moe_tile;
+
+/* QWGemm.encodeFnMoeRoute (Sources/Operators/QWGEMM/QWGemmMoERouter.swift:78-113; kernel qwg_moe_route,
+ * Sources/QWMetal/subsystems/qwrouter.metal:84-168): f32 softmax over all experts, top-k by repeated argmax (ties to
+ * the lower id, non-finite logits never chosen, idx = -1 when none is left), optional renormalisation over the k
+ * chosen, times routed_scale (<= 0 means 1).  logits f32 [t, e]; idx i32 [t, k]; wts f32 [t, k].  e <= 512, k <= 16. */
+int qwc_moe_route(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t t, int64_t e, int64_t k, int32_t norm_topk,
+                  float routed_scale, int32_t* idx, float* wts);
+
+/* QWGemm.encodeMoEGroupPairsF32 (Sources/Operators/QWGEMM/QWGemmMoE.swift:24-99; kernel qwg_moe_group_pairs_f32):
+ * counting sort of the t*k (token, route) pairs by expert, slot order inside an expert = ascending pair index.
+ * expert_off i32 [e + 1]; sorted_pair, sorted_tok, inv_perm i32 [pairs] (inv_perm = -1 for dropped pairs).  Also
+ * writes the tile lists of the two grouped GEMMs (gate/up with gu_rows = 2 * inter rows per expert, down with dn_rows
+ * = hidden rows per expert): tiles_gu / tiles_dn hold up to qwc_moe_max_tiles() entries, tile_counts i32 [2]. */
+int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int64_t pairs, int64_t e, int64_t k,
+                        int32_t* expert_off, int32_t* sorted_pair, int32_t* sorted_tok, int32_t* inv_perm,
+                        int64_t gu_rows, int64_t dn_rows, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
+                        int32_t* tile_counts);
+int64_t qwc_moe_max_tiles(int64_t pairs, int64_t e, int64_t rows_per_expert);
+
+/* Gather + rotate: xs[p, :] = f16(fwht32(x[sorted_tok[p], :])) for the sorted pairs (x_is_rotated != 0: plain copy).
+ * Stands where the gather-A of qwg_moe_nax_gemm (Sources/QWMetal/include/qw_gemm_nax.metalh:436-470) and the bridge
+ * (QWGemmMoE.swift:334-377) stand. */
+int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t ldx, int64_t h, const int32_t* sorted_tok,
+                   const int32_t* expert_off, int64_t e, int64_t pairs, int32_t x_is_rotated, void* xs_f16);
+
+/* QWGemm.encodeMoEGateUpNax / encodeMoENaxSplitF32 (QWGemmMoE.swift:201-296): grouped expert GEMM over the tile list.
+ * bank: stacked expert bank [e * rows_per_expert, k]; xs: expert-sorted rotated activations f16 [pairs, k];
+ * y: f16 or f32 [pairs, rows_per_expert]. */
+int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank, const void* xs_f16, int64_t pairs,
+                         const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, void* y, int32_t y_dtype,
+                         int64_t ldy);
+
+/* QWGemm.encodeSiluMulSplitF16 (Sources/Operators/QWGEMM/QWGemmF32.swift:96-105; kernels
+ * Sources/QWMetal/gemm/qwgemm_batched.metal:55-97): h[p, i] = fwht32(f16(silu(gu[p, i]) * gu[p, inter + i])). */
+int qwc_moe_silu_mul(qwc_hal* hal, qwc_stream stream, const void* gu_f16, int64_t rows, int64_t inter, int32_t rotate,
+                     void* h_f16);
+
+/* QWGemm.encodeMoEDownReduceCombineF32 (QWGemmMoE.swift:298-332; kernel qwg_moe_down_reduce_combine_f32):
+ * out[t, :] = sum_k wts[t, k] * dn[inv_perm[t * k_top + k], :] (dropped pairs skipped), f32 accumulate. */
+int qwc_moe_combine(qwc_hal* hal, qwc_stream stream, const void* dn, int32_t dn_dtype, const int32_t* inv_perm,
+                    const float* wts, int64_t t, int64_t k, int64_t h, void* out, int32_t out_dtype);
+
+/* QWMoEOperator.encodeResident (QWMoEOperator.swift:206-442), grouped path with no shared expert: the whole chain
+ * above on one stream.  x f16 [t, h] (standard basis unless x_is_rotated); logits f32 [t, e]; bank_gu = stacked
+ * [e * 2 * inter, h] gate||up banks, bank_dn = stacked [e * h, inter]; out f32 or f16 [t, h].  scratch must hold
+ * qwc_moe_scratch_bytes() bytes, 256-byte aligned. */
+int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank_gu, const qwc_weight_view* bank_dn,
+                    int64_t e, int64_t inter, const void* x_f16, int64_t t, int64_t ldx, int32_t x_is_rotated,
+                    const float* logits, int64_t k, int32_t norm_topk, float routed_scale, void* out, int32_t out_dtype,
+                    void* scratch, size_t scratch_bytes);
+size_t qwc_moe_scratch_bytes(int64_t t, int64_t e, int64_t k, int64_t h, int64_t inter);
+
 #ifdef __cplusplus
 }
 #endif

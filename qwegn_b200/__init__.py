@@ -7,9 +7,10 @@ from ._lib import (EPI_NONE, EPI_SILU_PAIR, EPI_SILU_PAIR_FWHT, F16, F32, KIND_H
                    LIB_PATH)
 from .gemm import (CONTAINERS, ContainerKind, QWGemm, QWGemmError, QWGemmPlan, QWHal, QWWeightView,
                    incumbentHQ4G32, rotatedHQ)
+from .moe import QWGemmMoE, QWMoEOperator
 
 __all__ = [
     "EPI_NONE", "EPI_SILU_PAIR", "EPI_SILU_PAIR_FWHT", "F16", "F32", "KIND_HQ4_G32_M5", "KIND_ROTATED_HQ",
     "LIB_PATH", "CONTAINERS", "ContainerKind", "QWGemm", "QWGemmError", "QWGemmPlan", "QWHal", "QWWeightView",
-    "incumbentHQ4G32", "rotatedHQ",
+    "incumbentHQ4G32", "rotatedHQ", "QWGemmMoE", "QWMoEOperator",
 ]

@@ -46,6 +46,18 @@ struct TcParams {
     int ab_stages, raw_stages;
     int raw_row_bytes;   // packed bytes of 128 k of one row: 80 (HQ4_G32_M5) or 144 (HQ8_G32)
     int m_tiles, n_tiles;
+    // grouped mode (MoE expert GEMMs): tiles come from a device-side list built by the pair sort
+    const qwc_moe_tile* tiles;   // null in dense mode
+    const int32_t* tile_count;   // device: number of valid entries of `tiles`
+};
+
+// One unit of work of the kernel: 128 weight rows x up to 256 activation rows.
+struct TileInfo {
+    int w_row0;     // first weight row (row coordinate of the weight tensor map)
+    int w_rows;     // valid weight rows in the tile (<= 128)
+    int x_row0;     // first activation row (row coordinate of the activation tensor map)
+    int x_rows;     // valid activation rows (<= 256)
+    int y_col0;     // output column of weight row 0 of the tile
 };
 
 __device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
@@ -70,14 +82,17 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     return d;
 }
 
-// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, N = 256, M = 128.
-constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, M = 128 weight rows, N = tokens of the
+// tile rounded up to a multiple of 16 (16..256).
+__device__ __forceinline__ uint32_t make_idesc(int n_tokens) {
+    return (1u << 4) | (static_cast<uint32_t>(n_tokens >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
 
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -202,7 +217,26 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int total_tiles = p.tiles != nullptr ? *p.tile_count : p.m_tiles * p.n_tiles;
+    auto get_tile = [&](int tile) {
+        TileInfo t;
+        if (p.tiles != nullptr) {
+            const qwc_moe_tile g = p.tiles[tile];
+            t.w_row0 = g.w_row0;
+            t.w_rows = g.w_rows;
+            t.x_row0 = g.x_row0;
+            t.x_rows = g.x_rows;
+            t.y_col0 = g.y_col0;
+        } else {
+            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;   // token tiles fastest: CTAs share weight rows in L2
+            t.w_row0 = nt * kBM;
+            t.w_rows = min(kBM, p.n - t.w_row0);
+            t.x_row0 = mt * kBN;
+            t.x_rows = min(kBN, p.m - t.x_row0);
+            t.y_col0 = t.w_row0;
+        }
+        return t;
+    };
     const int ktiles = p.k / kBK;
     const int raw_steps = p.k / kRawK;
 
@@ -218,7 +252,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
             uint32_t ab_fills = 0, raw_fills = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+                const TileInfo ti = get_tile(tile);
                 for (int rs = 0; rs < raw_steps && ok; ++rs) {
                     if (raw_fills >= static_cast<uint32_t>(p.raw_stages) && !mbar_wait(&raw_empty[rr.slot], rr.parity ^ 1u)) {
                         fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
@@ -226,7 +260,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                         break;
                     }
                     mbar_arrive_expect_tx(&raw_full[rr.slot], static_cast<uint32_t>(kBM * p.raw_row_bytes));
-                    tma_load_2d(raw + rr.slot * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), nt * kBM, &raw_full[rr.slot]);
+                    tma_load_2d(raw + rr.slot * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[rr.slot]);
                     rr.advance();
                     ++raw_fills;
                     for (int h = 0; h < kRawK / kBK && ok; ++h) {
@@ -236,7 +270,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                             break;
                         }
                         mbar_arrive_expect_tx(&x_full[ab.slot], kXTileBytes);
-                        tma_load_2d(xt + ab.slot * kXTileBytes, &xmap, (rs * (kRawK / kBK) + h) * kBK, mt * kBN, &x_full[ab.slot]);
+                        tma_load_2d(xt + ab.slot * kXTileBytes, &xmap, (rs * (kRawK / kBK) + h) * kBK, ti.x_row0, &x_full[ab.slot]);
                         ab.advance();
                         ++ab_fills;
                     }
@@ -258,6 +292,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * kBN);
+                const uint32_t idesc = make_idesc(min(kBN, (get_tile(tile).x_rows + 15) & ~15));
                 for (int kt = 0; kt < ktiles; ++kt) {
                     if (!mbar_wait(&x_full[ab.slot], ab.parity) || !mbar_wait(&w_full[ab.slot], ab.parity)) {
                         fail(QWC_DEV_WAIT_FULL_TIMEOUT);
@@ -268,7 +303,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                     const uint32_t a_addr = smem_u32(wt + ab.slot * kWTileBytes), b_addr = smem_u32(xt + ab.slot * kXTileBytes);
 #pragma unroll
                     for (int j = 0; j < kBK / 16; ++j)
-                        umma_f16(d_tmem, umma_desc_sw128(a_addr + j * 32), umma_desc_sw128(b_addr + j * 32), (kt > 0 || j > 0) ? 1u : 0u);
+                        umma_f16(d_tmem, umma_desc_sw128(a_addr + j * 32), umma_desc_sw128(b_addr + j * 32), idesc, (kt > 0 || j > 0) ? 1u : 0u);
                     umma_commit(&ab_empty[ab.slot]);  // frees the stage when these MMAs have read it
                     ab.advance();
                 }
@@ -326,26 +361,27 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         const int quarter = warp & 3;   // TMEM lanes [32 * quarter, 32 * quarter + 32)
         uint32_t tiles_done = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tiles_done) {
-            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+            const TileInfo ti = get_tile(tile);
             const int as = tiles_done & 1;
             if (!mbar_wait(&acc_full[as], (tiles_done >> 1) & 1)) {
                 if (lane == 0) fail(QWC_DEV_WAIT_MMA_TIMEOUT);
                 break;
             }
             tc_fence_after();
-            const int n = nt * kBM + quarter * 32 + lane;
+            const int wr = quarter * 32 + lane;          // weight row inside the tile
+            const int64_t ycol = ti.y_col0 + wr;
+            const int chunks = (ti.x_rows + 31) / 32;    // only the token columns the MMA wrote
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * kBN);
 #pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
+            for (int c = 0; c < chunks; ++c) {
                 uint32_t r[32];
                 tmem_ld32(taddr + c * 32, r);
                 tmem_ld_wait();
-                const int m0 = mt * kBN + c * 32;
-                if (n < p.n) {
+                if (wr < ti.w_rows) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        if (m0 + j < p.m) {
-                            const int64_t o = static_cast<int64_t>(m0 + j) * p.ldy + n;
+                        if (c * 32 + j < ti.x_rows) {
+                            const int64_t o = static_cast<int64_t>(ti.x_row0 + c * 32 + j) * p.ldy + ycol;
                             if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(__uint_as_float(r[j]));
                             else static_cast<float*>(p.y)[o] = __uint_as_float(r[j]);
                         }
@@ -385,14 +421,13 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 template <int FMT>
-int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& xmap, int smem) {
+int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& xmap, int smem,
+              int grid) {
     static bool configured[64] = {};
     if (!configured[hal->device & 63]) {
         QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured[hal->device & 63] = true;
     }
-    int grid = p.m_tiles * p.n_tiles;
-    if (grid > hal->sm_count) grid = hal->sm_count;
     qwc_gemm_tc_kernel<FMT><<<grid, kTcThreads, smem, st>>>(p, wmap, xmap);
     QWC_CUDA_TRY(cudaGetLastError());
     return QWC_OK;
@@ -416,26 +451,13 @@ size_t qwc_gemm_tc_workspace_bytes(const qwc_weight_view* w, int64_t m, int x_is
     return x_is_rotated ? 0 : static_cast<size_t>(m) * static_cast<size_t>(w->k) * 2;
 }
 
-int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
-                       void* y, int y_dtype, int64_t ldy, int x_is_rotated, void* workspace, size_t workspace_bytes) {
+// Shared by the dense door and the grouped (MoE) door: tensor maps, shared-memory budget, launch.
+static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const __half* xr, int64_t ldxr, int64_t m,
+                  void* y, int y_dtype, int64_t ldy, const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles) {
     const int fmt = qwc_fmt_of(*w);
-    const __half* xr = static_cast<const __half*>(x);
-    int64_t ldxr = ldx;
-    if (!x_is_rotated) {
-        const size_t need = qwc_gemm_tc_workspace_bytes(w, m, 0);
-        if (workspace == nullptr || workspace_bytes < need)
-            return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace of %zu bytes needed (qwc_gemm_workspace_bytes), got %zu", need, workspace_bytes);
-        if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace must be 16-byte aligned");
-        int64_t blocks = (m * (w->k / 32) + 7) / 8;
-        if (blocks > hal->sm_count * 16) blocks = hal->sm_count * 16;
-        qwc_rotate_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(xr, ldx, static_cast<__half*>(workspace), m, w->k);
-        QWC_CUDA_TRY(cudaGetLastError());
-        xr = static_cast<const __half*>(workspace);
-        ldxr = w->k;
-    } else if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || ldx % 8 != 0) {
-        return qwc_fail(QWC_ERR_BAD_SHAPE, "rotated activations must be 16-byte aligned with ldx %% 8 == 0 for the tensor-core path");
-    }
     TcParams p{};
+    p.tiles = tiles;
+    p.tile_count = tile_count;
     p.y = y;
     p.ldy = ldy;
     p.status = hal->status;
@@ -477,6 +499,36 @@ int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_vie
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return qwc_fail(QWC_ERR_CUDA, "cuTensorMapEncodeTiled(activations) failed with %d", static_cast<int>(cr));
     }
-    if (fmt == FMT_HQ4_G32_M5) return launch_tc<FMT_HQ4_G32_M5>(hal, st, p, wmap, xmap, smem);
-    return launch_tc<FMT_HQ8_G32>(hal, st, p, wmap, xmap, smem);
+    const int64_t ntiles = tiles != nullptr ? max_tiles : static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+    const int grid = static_cast<int>(ntiles < hal->sm_count ? (ntiles < 1 ? 1 : ntiles) : hal->sm_count);
+    if (fmt == FMT_HQ4_G32_M5) return launch_tc<FMT_HQ4_G32_M5>(hal, st, p, wmap, xmap, smem, grid);
+    return launch_tc<FMT_HQ8_G32>(hal, st, p, wmap, xmap, smem, grid);
+}
+
+int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
+                       void* y, int y_dtype, int64_t ldy, int x_is_rotated, void* workspace, size_t workspace_bytes) {
+    const __half* xr = static_cast<const __half*>(x);
+    int64_t ldxr = ldx;
+    if (!x_is_rotated) {
+        const size_t need = qwc_gemm_tc_workspace_bytes(w, m, 0);
+        if (workspace == nullptr || workspace_bytes < need)
+            return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace of %zu bytes needed (qwc_gemm_workspace_bytes), got %zu", need, workspace_bytes);
+        if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace must be 16-byte aligned");
+        int64_t blocks = (m * (w->k / 32) + 7) / 8;
+        if (blocks > hal->sm_count * 16) blocks = hal->sm_count * 16;
+        qwc_rotate_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(xr, ldx, static_cast<__half*>(workspace), m, w->k);
+        QWC_CUDA_TRY(cudaGetLastError());
+        xr = static_cast<const __half*>(workspace);
+        ldxr = w->k;
+    } else if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || ldx % 8 != 0) {
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "rotated activations must be 16-byte aligned with ldx %% 8 == 0 for the tensor-core path");
+    }
+    return tc_run(hal, st, w, xr, ldxr, m, y, y_dtype, ldy, nullptr, nullptr, 0);
+}
+
+// Grouped expert GEMM: the same kernel over a device-side tile list (see qwc_moe_group_pairs).
+int qwc_launch_gemm_tc_grouped(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* bank, const void* xs, int64_t pairs,
+                               const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, void* y, int y_dtype,
+                               int64_t ldy) {
+    return tc_run(hal, st, bank, static_cast<const __half*>(xs), bank->k, pairs, y, y_dtype, ldy, tiles, tile_count, max_tiles);
 }

@@ -1,0 +1,488 @@
+// Mixture-of-experts operator chain: the CUDA twins of the reference's router, pair sort, SwiGLU and combine
+// kernels and the host orchestration of QWMoEOperator.encodeResident
+// (Sources/Operators/QWGEMM/QWMoEOperator.swift:206-442, grouped path, T > 8).
+//   qwg_moe_route                      Sources/QWMetal/subsystems/qwrouter.metal:84-168
+//   qwg_moe_group_pairs_f32            Sources/QWMetal/gemm/qwgemm_moe_group_f32.metal:10-148
+//   qwg_silu_mul_split_f16             Sources/QWMetal/gemm/qwgemm_batched.metal:55-97
+//   qwg_moe_down_reduce_combine_f32    Sources/QWMetal/gemm/qwgemm_moe_nax_f16.metal:7-126
+// The grouped expert GEMMs run on the tensor-core kernel of qwc_gemm_tc.cu over the tile list built here.
+#include "qwc_common.cuh"
+
+int qwc_launch_gemm_tc_grouped(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, const qwc_moe_tile*,
+                               const int32_t*, int64_t, void*, int, int64_t);
+bool qwc_gemm_tc_supported(const qwc_hal*, const qwc_weight_view*, int64_t, int);
+
+namespace {
+
+constexpr int kTileW = 128;  // weight rows per grouped-GEMM tile
+constexpr int kTileX = 256;  // activation rows per grouped-GEMM tile
+
+__device__ __forceinline__ bool finite_bits(float v) { return (__float_as_uint(v) & 0x7F800000u) != 0x7F800000u; }
+
+// One warp routes one token.  Lane l holds experts l, l + 32, ... (e <= 512 -> at most 16 per lane).
+__global__ void __launch_bounds__(128) qwc_moe_route_kernel(const float* __restrict__ logits, int t_rows, int e, int k,
+                                                            int norm_topk, float routed_scale, int32_t* __restrict__ idx,
+                                                            float* __restrict__ wts) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= t_rows) return;
+    constexpr int kMaxPer = 16;
+    float pv[kMaxPer];
+    bool valid[kMaxPer];
+    const int per = (e + 31) / 32;
+    float mx = -3.4e38f;
+    bool any = false;
+#pragma unroll
+    for (int j = 0; j < kMaxPer; ++j) {
+        const int id = lane + 32 * j;
+        pv[j] = (j < per && id < e) ? logits[static_cast<int64_t>(t) * e + id] : 0.0f;
+        valid[j] = j < per && id < e && finite_bits(pv[j]);
+        if (valid[j]) {
+            mx = any ? fmaxf(mx, pv[j]) : pv[j];
+            any = true;
+        }
+    }
+    const bool any_finite = __any_sync(0xFFFFFFFFu, any);
+    float wmx = any ? mx : -3.4e38f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wmx = fmaxf(wmx, __shfl_xor_sync(0xFFFFFFFFu, wmx, o));
+    const float max_logit = any_finite ? wmx : 0.0f;
+    // total = sum over experts in index order groups (lane-major partial sums, then a warp sum): f32, like the
+    // reference's simd_sum per 32-wide slice accumulated over slices
+    float total = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kMaxPer; ++j) {
+        float ex = valid[j] ? expf(pv[j] - max_logit) : 0.0f;
+        pv[j] = ex;
+        float s = ex;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+        total += s;
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxPer; ++j) {
+        valid[j] = valid[j] && total > 0.0f;
+        pv[j] = valid[j] ? pv[j] / total : -1e30f;
+    }
+    float sel_w = 0.0f;   // lane r keeps the weight of the r-th choice
+    int sel_i = -1;
+    float acc = 0.0f;
+    for (int r = 0; r < k; ++r) {
+        float bv = -3.4e38f;
+        int bi = 0x7FFFFFFF;
+#pragma unroll
+        for (int j = 0; j < kMaxPer; ++j) {
+            const int id = lane + 32 * j;
+            if (valid[j] && (pv[j] > bv || (pv[j] == bv && id < bi))) {
+                bv = pv[j];
+                bi = id;
+            }
+        }
+        // warp argmax with ties to the lower id
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+            if (oi != 0x7FFFFFFF && (bi == 0x7FFFFFFF || ov > bv || (ov == bv && oi < bi))) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        const bool found = bi != 0x7FFFFFFF;
+        if (found && (bi & 31) == lane) {
+#pragma unroll
+            for (int j = 0; j < kMaxPer; ++j)
+                if (j == (bi >> 5)) valid[j] = false;
+        }
+        if (lane == r) {
+            sel_w = found ? bv : 0.0f;
+            sel_i = found ? bi : -1;
+        }
+        acc += found ? bv : 0.0f;   // same order on every lane: sum of the chosen weights in rank order
+    }
+    if (lane < k) {
+        const float rs = routed_scale > 0.0f ? routed_scale : 1.0f;
+        const float nw = norm_topk ? (acc > 0.0f ? sel_w / acc : 0.0f) : sel_w;
+        idx[static_cast<int64_t>(t) * k + lane] = sel_i;
+        wts[static_cast<int64_t>(t) * k + lane] = nw * rs;
+    }
+}
+
+// Pass 1 of the pair sort: one warp per expert counts its pairs; warp `e` (one past the last expert) marks the
+// dropped pairs (idx < 0 or >= e) in inv_perm.
+__global__ void __launch_bounds__(256) qwc_moe_count_kernel(const int32_t* __restrict__ idx, int pairs, int e,
+                                                            int32_t* __restrict__ counts, int32_t* __restrict__ inv_perm) {
+    const int lane = threadIdx.x & 31;
+    const int ex = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (ex > e) return;
+    int c = 0;
+    for (int i0 = 0; i0 < pairs; i0 += 32) {
+        const int i = i0 + lane;
+        const int v = i < pairs ? idx[i] : 0;
+        if (ex == e) {
+            if (i < pairs && (v < 0 || v >= e)) inv_perm[i] = -1;
+        } else {
+            c += __popc(__ballot_sync(0xFFFFFFFFu, i < pairs && v == ex));
+        }
+    }
+    if (ex < e && lane == 0) counts[ex] = c;
+}
+
+// Pass 2: exclusive prefix over the experts and the two tile lists (one CTA).
+__global__ void __launch_bounds__(512) qwc_moe_plan_kernel(const int32_t* counts, int e, int32_t* expert_off,
+                                                           int gu_rows, int dn_rows, qwc_moe_tile* __restrict__ tiles_gu,
+                                                           qwc_moe_tile* __restrict__ tiles_dn, int32_t* __restrict__ tile_counts) {
+    __shared__ int s_off[513];
+    __shared__ int s_tx[513];   // activation-tile prefix
+    if (threadIdx.x == 0) {
+        int run = 0, tx = 0;
+        for (int i = 0; i < e; ++i) {
+            s_off[i] = run;
+            s_tx[i] = tx;
+            run += counts[i];
+            tx += (counts[i] + kTileX - 1) / kTileX;
+        }
+        s_off[e] = run;
+        s_tx[e] = tx;
+        tile_counts[0] = tx * ((gu_rows + kTileW - 1) / kTileW);
+        tile_counts[1] = tx * ((dn_rows + kTileW - 1) / kTileW);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i <= e; i += blockDim.x) expert_off[i] = s_off[i];
+    for (int ex = threadIdx.x; ex < e; ex += blockDim.x) {
+        const int cnt = s_off[ex + 1] - s_off[ex];
+        const int ntx = s_tx[ex + 1] - s_tx[ex];
+        for (int which = 0; which < 2; ++which) {
+            const int rows = which == 0 ? gu_rows : dn_rows;
+            qwc_moe_tile* tiles = which == 0 ? tiles_gu : tiles_dn;
+            if (tiles == nullptr) continue;
+            const int ntw = (rows + kTileW - 1) / kTileW;
+            // weight tiles fastest inside an activation tile: consecutive tiles re-read the same activations
+            for (int mt = 0; mt < ntx; ++mt)
+                for (int j = 0; j < ntw; ++j) {
+                    qwc_moe_tile tl;
+                    tl.w_row0 = ex * rows + j * kTileW;
+                    tl.w_rows = min(kTileW, rows - j * kTileW);
+                    tl.x_row0 = s_off[ex] + mt * kTileX;
+                    tl.x_rows = min(kTileX, cnt - mt * kTileX);
+                    tl.y_col0 = j * kTileW;
+                    tl.expert = ex;
+                    tl.pad0 = tl.pad1 = 0;
+                    tiles[(s_tx[ex] + mt) * ntw + j] = tl;
+                }
+        }
+    }
+}
+
+// Pass 3: one warp per expert places its pairs in ascending pair order.
+__global__ void __launch_bounds__(256) qwc_moe_place_kernel(const int32_t* __restrict__ idx, int pairs, int e, int k,
+                                                            const int32_t* __restrict__ expert_off, int32_t* __restrict__ sorted_pair,
+                                                            int32_t* __restrict__ sorted_tok, int32_t* __restrict__ inv_perm) {
+    const int lane = threadIdx.x & 31;
+    const int ex = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (ex >= e) return;
+    int at = expert_off[ex];
+    for (int i0 = 0; i0 < pairs; i0 += 32) {
+        const int i = i0 + lane;
+        const bool hit = i < pairs && idx[i] == ex;
+        const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
+        if (hit) {
+            const int pos = at + __popc(m & ((1u << lane) - 1u));
+            sorted_pair[pos] = i;
+            sorted_tok[pos] = i / k;
+            inv_perm[i] = pos;
+        }
+        at += __popc(m);
+    }
+}
+
+// xs[p, :] = rot(x[sorted_tok[p], :]).  One warp per (sorted row, 32-element unit).
+__global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __restrict__ x, int64_t ldx, int h,
+                                                             const int32_t* __restrict__ sorted_tok,
+                                                             const int32_t* __restrict__ expert_off, int e, int rotate,
+                                                             __half* __restrict__ xs) {
+    const int lane = threadIdx.x & 31;
+    const int units = h / 32;
+    const int64_t valid = expert_off[e];
+    const int64_t total = valid * units;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t it = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); it < total; it += warps) {
+        const int64_t pr = it / units;
+        const int u = static_cast<int>(it % units);
+        const int tok = sorted_tok[pr];
+        float v = __half2float(x[static_cast<int64_t>(tok) * ldx + u * 32 + lane]);
+        if (rotate) {
+#pragma unroll
+            for (int s = 1; s < 32; s <<= 1) v = fwht_xor_stage(v, s, (lane & s) != 0);
+            v = __fmul_rn(v, qwc_inv_sqrt32());
+        }
+        xs[pr * h + u * 32 + lane] = __float2half_rn(v);
+    }
+}
+
+// h[p, i] = fwht32(f16(silu(g) * u)) over expert-sorted rows; one warp per (row, 32-wide slice of inter).
+__global__ void __launch_bounds__(256) qwc_moe_silu_mul_kernel(const __half* __restrict__ gu, const int32_t* __restrict__ row_count,
+                                                               int64_t rows_cap, int inter, int rotate, __half* __restrict__ hout) {
+    const int lane = threadIdx.x & 31;
+    const int units = inter / 32;
+    const int64_t rows = row_count != nullptr ? static_cast<int64_t>(*row_count) : rows_cap;
+    const int64_t total = rows * units;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t it = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); it < total; it += warps) {
+        const int64_t r = it / units;
+        const int c = static_cast<int>(it % units) * 32 + lane;
+        const float g = __half2float(gu[r * 2 * inter + c]);
+        const float u = __half2float(gu[r * 2 * inter + inter + c]);
+        float v = __half2float(__float2half_rn((g / (1.0f + expf(-g))) * u));
+        if (rotate) {
+#pragma unroll
+            for (int s = 1; s < 32; s <<= 1) v = fwht_xor_stage(v, s, (lane & s) != 0);
+            v = __fmul_rn(v, qwc_inv_sqrt32());
+        }
+        hout[r * inter + c] = __float2half_rn(v);
+    }
+}
+
+// out[t, :] = sum_k wts[t, k] * dn[inv_perm[t, k], :]; one thread per (token, 2 columns), f32 accumulate in k order.
+template <typename DnT, typename OutT>
+__global__ void __launch_bounds__(256) qwc_moe_combine_kernel(const DnT* __restrict__ dn, const int32_t* __restrict__ inv_perm,
+                                                              const float* __restrict__ wts, int t_rows, int k, int h,
+                                                              OutT* __restrict__ out) {
+    const int64_t total = static_cast<int64_t>(t_rows) * (h / 2);
+    for (int64_t it = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; it < total;
+         it += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(it / (h / 2));
+        const int c = static_cast<int>(it % (h / 2)) * 2;
+        float a0 = 0.0f, a1 = 0.0f;
+        for (int j = 0; j < k; ++j) {
+            const int pos = inv_perm[static_cast<int64_t>(t) * k + j];
+            if (pos < 0) continue;
+            const float w = wts[static_cast<int64_t>(t) * k + j];
+            if (sizeof(DnT) == 2) {
+                const __half2 v = *reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(dn) + static_cast<int64_t>(pos) * h + c);
+                a0 = fmaf(w, __low2float(v), a0);
+                a1 = fmaf(w, __high2float(v), a1);
+            } else {
+                const float2 v = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(dn) + static_cast<int64_t>(pos) * h + c);
+                a0 = fmaf(w, v.x, a0);
+                a1 = fmaf(w, v.y, a1);
+            }
+        }
+        if (sizeof(OutT) == 2) {
+            *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(out) + static_cast<int64_t>(t) * h + c) = __floats2half2_rn(a0, a1);
+        } else {
+            *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + static_cast<int64_t>(t) * h + c) = make_float2(a0, a1);
+        }
+    }
+}
+
+int grid_for(const qwc_hal* hal, int64_t items, int per_block, int waves) {
+    int64_t g = (items + per_block - 1) / per_block;
+    const int64_t cap = static_cast<int64_t>(hal->sm_count) * waves;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return static_cast<int>(g);
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Scratch layout of qwc_moe_forward (every region 256-byte aligned).
+struct MoeScratch {
+    size_t idx, wts, counts, expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn, tile_counts, xs, gu, hs, dn, total;
+};
+
+MoeScratch moe_layout(int64_t t, int64_t e, int64_t k, int64_t h, int64_t inter) {
+    MoeScratch s{};
+    const int64_t pairs = t * k;
+    size_t at = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = at;
+        at = align_up(at + bytes, 256);
+        return o;
+    };
+    s.idx = take(pairs * 4);
+    s.wts = take(pairs * 4);
+    s.counts = take((e + 1) * 4);
+    s.expert_off = take((e + 1) * 4);
+    s.sorted_pair = take(pairs * 4);
+    s.sorted_tok = take(pairs * 4);
+    s.inv_perm = take(pairs * 4);
+    s.tiles_gu = take(qwc_moe_max_tiles(pairs, e, 2 * inter) * sizeof(qwc_moe_tile));
+    s.tiles_dn = take(qwc_moe_max_tiles(pairs, e, h) * sizeof(qwc_moe_tile));
+    s.tile_counts = take(16);
+    s.xs = take(pairs * h * 2);
+    s.gu = take(pairs * 2 * inter * 2);
+    s.hs = take(pairs * inter * 2);
+    s.dn = take(pairs * h * 2);
+    s.total = at;
+    return s;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t qwc_moe_max_tiles(int64_t pairs, int64_t e, int64_t rows_per_expert) {
+    // sum over experts of ceil(cnt / 256) <= min(pairs, e + pairs / 256)
+    int64_t tx = e + pairs / kTileX;
+    if (tx > pairs) tx = pairs;
+    return tx * ((rows_per_expert + kTileW - 1) / kTileW);
+}
+
+int qwc_moe_route(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t t, int64_t e, int64_t k, int32_t norm_topk,
+                  float routed_scale, int32_t* idx, float* wts) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    // the reference's limits (QWGemmMoERouter.swift:22): e <= 512, k <= 16
+    if (e <= 0 || e > 512) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "experts=%lld must be in 1..512", (long long)e);
+    if (k <= 0 || k > 16 || k > e) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "top-k=%lld must be in 1..16 and <= experts", (long long)k);
+    if (t < 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "t is negative");
+    if (t == 0) return QWC_OK;
+    if (!logits || !idx || !wts) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    const int blocks = static_cast<int>((t + 3) / 4);
+    qwc_moe_route_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, static_cast<int>(t), static_cast<int>(e),
+                                                                               static_cast<int>(k), norm_topk, routed_scale, idx, wts);
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
+
+int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int64_t pairs, int64_t e, int64_t k,
+                        int32_t* expert_off, int32_t* sorted_pair, int32_t* sorted_tok, int32_t* inv_perm,
+                        int64_t gu_rows, int64_t dn_rows, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
+                        int32_t* tile_counts) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (e <= 0 || e > 512) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "experts=%lld must be in 1..512", (long long)e);
+    if (k <= 0 || pairs < 0 || pairs % k != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "pairs=%lld is not a multiple of k=%lld", (long long)pairs, (long long)k);
+    if (pairs >= (int64_t(1) << 30)) return qwc_fail(QWC_ERR_BAD_SHAPE, "too many pairs");
+    if (!idx || !expert_off || !sorted_pair || !sorted_tok || !inv_perm || !tile_counts) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // expert_off doubles as the count buffer of pass 1; the plan kernel reads all counts before it writes offsets
+    const int warps = static_cast<int>(e) + 1;
+    qwc_moe_count_kernel<<<(warps + 7) / 8, 256, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e), expert_off, inv_perm);
+    QWC_CUDA_TRY(cudaGetLastError());
+    qwc_moe_plan_kernel<<<1, 512, 0, st>>>(expert_off, static_cast<int>(e), expert_off, static_cast<int>(gu_rows),
+                                           static_cast<int>(dn_rows), tiles_gu, tiles_dn, tile_counts);
+    QWC_CUDA_TRY(cudaGetLastError());
+    qwc_moe_place_kernel<<<(static_cast<int>(e) + 7) / 8, 256, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e),
+                                                                       static_cast<int>(k), expert_off, sorted_pair, sorted_tok, inv_perm);
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
+
+int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t ldx, int64_t h, const int32_t* sorted_tok,
+                   const int32_t* expert_off, int64_t e, int64_t pairs, int32_t x_is_rotated, void* xs_f16) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (h <= 0 || h % 32 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "hidden=%lld must be a positive multiple of 32", (long long)h);
+    if (ldx < h) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldx < hidden");
+    if (pairs == 0) return QWC_OK;
+    if (!x_f16 || !sorted_tok || !expert_off || !xs_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    qwc_moe_gather_kernel<<<grid_for(hal, pairs * (h / 32), 8, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), sorted_tok, expert_off, static_cast<int>(e), !x_is_rotated,
+        static_cast<__half*>(xs_f16));
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
+
+int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank, const void* xs_f16, int64_t pairs,
+                         const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, void* y, int32_t y_dtype,
+                         int64_t ldy) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (!bank || !bank->blocks) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "bank is null");
+    if (pairs <= 0 || max_tiles <= 0) return QWC_OK;
+    if (!xs_f16 || !tiles || !tile_count || !y) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    if (y_dtype != QWC_F16 && y_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "y dtype must be f16 or f32");
+    // The grouped door uses the tensor-core kernel only: K % 128 == 0, HQ4_G32_M5 or HQ8_G32, 16-byte aligned bank.
+    if (!qwc_gemm_tc_supported(hal, bank, 17, QWC_EPI_NONE))
+        return qwc_fail(QWC_ERR_BLOCKED, "grouped expert GEMM needs an HQ4_G32_M5 / HQ8_G32 bank with k %% 128 == 0, 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(xs_f16) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "xs must be 16-byte aligned");
+    return qwc_launch_gemm_tc_grouped(hal, static_cast<cudaStream_t>(stream), bank, xs_f16, pairs, tiles, tile_count, max_tiles, y,
+                                      y_dtype, ldy);
+}
+
+int qwc_moe_silu_mul(qwc_hal* hal, qwc_stream stream, const void* gu_f16, int64_t rows, int64_t inter, int32_t rotate,
+                     void* h_f16) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (inter <= 0 || inter % 32 != 0) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "inter=%lld must be a positive multiple of 32", (long long)inter);
+    if (rows <= 0) return QWC_OK;
+    if (!gu_f16 || !h_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    qwc_moe_silu_mul_kernel<<<grid_for(hal, rows * (inter / 32), 8, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(gu_f16), nullptr, rows, static_cast<int>(inter), rotate, static_cast<__half*>(h_f16));
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
+
+int qwc_moe_combine(qwc_hal* hal, qwc_stream stream, const void* dn, int32_t dn_dtype, const int32_t* inv_perm,
+                    const float* wts, int64_t t, int64_t k, int64_t h, void* out, int32_t out_dtype) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (h <= 0 || h % 2 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "hidden must be even");
+    if (t <= 0) return QWC_OK;
+    if (!dn || !inv_perm || !wts || !out) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = grid_for(hal, t * (h / 2), 256, 16);
+    const int ti = static_cast<int>(t), ki = static_cast<int>(k), hi = static_cast<int>(h);
+    if (dn_dtype == QWC_F16 && out_dtype == QWC_F32)
+        qwc_moe_combine_kernel<__half, float><<<grid, 256, 0, st>>>(static_cast<const __half*>(dn), inv_perm, wts, ti, ki, hi, static_cast<float*>(out));
+    else if (dn_dtype == QWC_F16 && out_dtype == QWC_F16)
+        qwc_moe_combine_kernel<__half, __half><<<grid, 256, 0, st>>>(static_cast<const __half*>(dn), inv_perm, wts, ti, ki, hi, static_cast<__half*>(out));
+    else if (dn_dtype == QWC_F32 && out_dtype == QWC_F32)
+        qwc_moe_combine_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(dn), inv_perm, wts, ti, ki, hi, static_cast<float*>(out));
+    else if (dn_dtype == QWC_F32 && out_dtype == QWC_F16)
+        qwc_moe_combine_kernel<float, __half><<<grid, 256, 0, st>>>(static_cast<const float*>(dn), inv_perm, wts, ti, ki, hi, static_cast<__half*>(out));
+    else
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "dtypes must be f16 or f32");
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
+
+size_t qwc_moe_scratch_bytes(int64_t t, int64_t e, int64_t k, int64_t h, int64_t inter) {
+    if (t <= 0 || e <= 0 || k <= 0 || h <= 0 || inter <= 0) return 0;
+    return moe_layout(t, e, k, h, inter).total;
+}
+
+int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank_gu, const qwc_weight_view* bank_dn,
+                    int64_t e, int64_t inter, const void* x_f16, int64_t t, int64_t ldx, int32_t x_is_rotated,
+                    const float* logits, int64_t k, int32_t norm_topk, float routed_scale, void* out, int32_t out_dtype,
+                    void* scratch, size_t scratch_bytes) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (!bank_gu || !bank_dn) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "expert banks are null");
+    const int64_t h = bank_gu->k;
+    // Bank geometry (QWMoEOperator.Weights, QWMoEOperator.swift:10-130): gate||up is [e * 2 * inter, h], down is [e * h, inter].
+    if (bank_gu->n != e * 2 * inter) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "gate/up bank has %lld rows, expected e * 2 * inter = %lld", (long long)bank_gu->n, (long long)(e * 2 * inter));
+    if (bank_dn->n != e * h || bank_dn->k != inter) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "down bank must be [e * hidden, inter] = [%lld, %lld]", (long long)(e * h), (long long)inter);
+    if (t < 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "t is negative");
+    if (t == 0) return QWC_OK;
+    if (!x_f16 || !logits || !out) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    const MoeScratch L = moe_layout(t, e, k, h, inter);
+    if (!scratch || scratch_bytes < L.total) return qwc_fail(QWC_ERR_BAD_SHAPE, "scratch of %zu bytes needed (qwc_moe_scratch_bytes), got %zu", L.total, scratch_bytes);
+    if (reinterpret_cast<uintptr_t>(scratch) % 256 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "scratch must be 256-byte aligned");
+    uint8_t* sc = static_cast<uint8_t*>(scratch);
+    const int64_t pairs = t * k;
+    int32_t* idx = reinterpret_cast<int32_t*>(sc + L.idx);
+    float* wts = reinterpret_cast<float*>(sc + L.wts);
+    int32_t* expert_off = reinterpret_cast<int32_t*>(sc + L.expert_off);
+    int32_t* sorted_pair = reinterpret_cast<int32_t*>(sc + L.sorted_pair);
+    int32_t* sorted_tok = reinterpret_cast<int32_t*>(sc + L.sorted_tok);
+    int32_t* inv_perm = reinterpret_cast<int32_t*>(sc + L.inv_perm);
+    qwc_moe_tile* tiles_gu = reinterpret_cast<qwc_moe_tile*>(sc + L.tiles_gu);
+    qwc_moe_tile* tiles_dn = reinterpret_cast<qwc_moe_tile*>(sc + L.tiles_dn);
+    int32_t* tile_counts = reinterpret_cast<int32_t*>(sc + L.tile_counts);
+    int rc;
+    if ((rc = qwc_moe_route(hal, stream, logits, t, e, k, norm_topk, routed_scale, idx, wts))) return rc;
+    if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h,
+                                  tiles_gu, tiles_dn, tile_counts))) return rc;
+    if ((rc = qwc_moe_gather(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs))) return rc;
+    if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_gu, sc + L.xs, pairs, tiles_gu, tile_counts, qwc_moe_max_tiles(pairs, e, 2 * inter),
+                                   sc + L.gu, QWC_F16, 2 * inter))) return rc;
+    if ((rc = qwc_moe_silu_mul(hal, stream, sc + L.gu, pairs, inter, 1, sc + L.hs))) return rc;
+    if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_dn, sc + L.hs, pairs, tiles_dn, tile_counts + 1, qwc_moe_max_tiles(pairs, e, h),
+                                   sc + L.dn, QWC_F16, h))) return rc;
+    return qwc_moe_combine(hal, stream, sc + L.dn, QWC_F16, inv_perm, wts, t, k, h, out, out_dtype);
+}
+
+}  // extern "C"

@@ -1,0 +1,116 @@
+"""MoE operator chain through the C ABI against the oracle (router, pair sort, grouped GEMMs, combine)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_matmul_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _expert_banks(oracle, fmt, experts, hidden, inter, rng):
+    gu = oracle.quantize(rng.normal(0.0, 0.05, (experts * 2 * inter, hidden)).astype(np.float32), fmt)
+    dn = oracle.quantize(rng.normal(0.0, 0.05, (experts * hidden, inter)).astype(np.float32), fmt)
+    return gu, dn
+
+
+@pytest.mark.parametrize("t,e,k", [(5, 8, 2), (257, 64, 8), (2048, 256, 8)])
+def test_route_matches_the_oracle(hal, oracle, t, e, k):
+    import qwegn_b200 as q
+    rng = np.random.default_rng(t + e)
+    lg = rng.standard_normal((t, e)).astype(np.float32)
+    lg[0, :3] = lg[0, 3]            # a tie: lower id first
+    if t > 4:
+        lg[4, 1] = np.inf
+        lg[4, 2] = np.nan
+    idx = torch.empty((t, k), dtype=torch.int32, device="cuda")
+    wts = torch.empty((t, k), dtype=torch.float32, device="cuda")
+    q.QWGemmMoE.encodeFnMoeRoute(hal, torch.from_numpy(lg).cuda(), k, idx, wts, norm_topk=True)
+    ridx, rwts = oracle.moe_route(lg, k, norm_topk=True)
+    assert np.array_equal(idx.cpu().numpy(), ridx)
+    np.testing.assert_allclose(wts.cpu().numpy(), rwts, rtol=2e-6, atol=1e-7)
+    q.QWGemmMoE.encodeFnMoeRoute(hal, torch.from_numpy(lg).cuda(), k, idx, wts, norm_topk=False, routed_scale=2.5)
+    ridx, rwts = oracle.moe_route(lg, k, norm_topk=False, routed_scale=2.5)
+    assert np.array_equal(idx.cpu().numpy(), ridx)
+    np.testing.assert_allclose(wts.cpu().numpy(), rwts, rtol=2e-6, atol=1e-7)
+
+
+def test_route_refusals(hal):
+    import qwegn_b200 as q
+    lg = torch.zeros((2, 600), dtype=torch.float32, device="cuda")
+    idx = torch.empty((2, 2), dtype=torch.int32, device="cuda")
+    wts = torch.empty((2, 2), dtype=torch.float32, device="cuda")
+    with pytest.raises(q.QWGemmError) as e:   # QWGemmMoERouter.swift:22: E <= 512
+        q.QWGemmMoE.encodeFnMoeRoute(hal, lg, 2, idx, wts)
+    assert e.value.case == "badGeometry"
+
+
+@pytest.mark.parametrize("t,e,k", [(37, 8, 4), (2048, 256, 8), (3, 16, 2)])
+def test_group_pairs_matches_the_oracle(hal, oracle, t, e, k):
+    import qwegn_b200 as q
+    rng = np.random.default_rng(t * 7 + e)
+    idx = rng.integers(-1, e, size=(t, k)).astype(np.int32)
+    off, sp, st, inv, tg, td, tc = q.QWGemmMoE.encodeMoEGroupPairs(hal, torch.from_numpy(idx).cuda(), e, 1024, 2048)
+    roff, rsp, rst, rinv = oracle.moe_group_pairs(idx, e)
+    valid = int(roff[-1])
+    assert np.array_equal(off.cpu().numpy(), roff)
+    assert np.array_equal(sp.cpu().numpy()[:valid], rsp[:valid])
+    assert np.array_equal(st.cpu().numpy()[:valid], rst[:valid])
+    assert np.array_equal(inv.cpu().numpy(), rinv)
+    # tile plan: every expert's rows are covered exactly once per 128-row weight tile
+    counts = tc.cpu().numpy()
+    tiles = tg.cpu().numpy()[: counts[0]]
+    assert counts[0] == sum(-(-int(c) // 256) for c in np.diff(roff)) * 8
+    cover = np.zeros(valid, dtype=np.int32)
+    for w0, wr, x0, xr, y0, ex, _, _ in tiles:
+        assert wr == 128 and w0 == ex * 1024 + y0 and roff[ex] <= x0 and x0 + xr <= roff[ex + 1]
+        if y0 == 0:
+            cover[x0:x0 + xr] += 1
+    assert (cover == 1).all()
+    assert counts[1] == counts[0] * 2
+
+
+@pytest.mark.parametrize("cfg", [(64, 8, 2, 256, 128), (300, 32, 4, 512, 256), (40, 16, 8, 128, 128)])
+@pytest.mark.parametrize("name", ["HQ4_G32", "HQ8_G32"])
+def test_moe_forward_vs_oracle(hal, oracle, cfg, name):
+    import qwegn_b200 as q
+    t, e, k, hidden, inter = cfg
+    fmt = oracle.FORMATS[name]
+    rng = np.random.default_rng(sum(cfg))
+    gu, dn = _expert_banks(oracle, fmt, e, hidden, inter, rng)
+    x = rng.standard_normal((t, hidden)).astype(np.float16)
+    lg = rng.standard_normal((t, e)).astype(np.float32)
+    cont = q.CONTAINERS[name]
+    bank_gu = q.QWWeightView(torch.from_numpy(gu.reshape(-1)).cuda(), e * 2 * inter, hidden, cont)
+    bank_dn = q.QWWeightView(torch.from_numpy(dn.reshape(-1)).cuda(), e * hidden, inter, cont)
+    op = q.QWMoEOperator(hal, bank_gu, bank_dn, e, inter, k, norm_topk=True)
+    scratch = torch.empty(op.scratchBytes(t), dtype=torch.uint8, device="cuda")
+    out = torch.full((t, hidden), float("nan"), dtype=torch.float32, device="cuda")
+    op.encodeResident(torch.from_numpy(x).cuda(), torch.from_numpy(lg).cuda(), out, scratch)
+    ridx, rwts = oracle.moe_route(lg, k, norm_topk=True)
+    ref = oracle.moe_forward(gu, dn, fmt, e, hidden, inter, x, ridx, rwts)
+    # gate/up and the down result are stored as f16 between the kernels (the reference's numeric class,
+    # Sources/QWMetal/include/qw_gemm_nax_swiglu.metalh:132); the oracle keeps them in f32
+    assert_matmul_close(out.cpu().numpy(), ref, tight=6e-3)
+    out16 = torch.empty((t, hidden), dtype=torch.float16, device="cuda")
+    op.encodeResident(torch.from_numpy(x).cuda(), torch.from_numpy(lg).cuda(), out16, scratch)
+    assert_matmul_close(out16.float().cpu().numpy(), ref, tight=8e-3)
+
+
+def test_moe_forward_refusals(hal, oracle):
+    import qwegn_b200 as q
+    rng = np.random.default_rng(1)
+    gu, dn = _expert_banks(oracle, oracle.HQ4_G32, 4, 128, 128, rng)
+    bank_gu = q.QWWeightView(torch.from_numpy(gu.reshape(-1)).cuda(), 4 * 256, 128)
+    bank_dn = q.QWWeightView(torch.from_numpy(dn.reshape(-1)).cuda(), 4 * 128, 128)
+    op = q.QWMoEOperator(hal, bank_gu, bank_dn, 4, 128, 2)
+    x = torch.zeros((3, 128), dtype=torch.float16, device="cuda")
+    lg = torch.zeros((3, 4), dtype=torch.float32, device="cuda")
+    out = torch.zeros((3, 128), dtype=torch.float32, device="cuda")
+    with pytest.raises(q.QWGemmError):   # scratch too small
+        op.encodeResident(x, lg, out, torch.empty(16, dtype=torch.uint8, device="cuda"))
+    bad = q.QWMoEOperator(hal, bank_gu, bank_dn, 5, 128, 2)   # bank rows do not match the expert count
+    with pytest.raises(q.QWGemmError) as e:
+        bad.encodeResident(x, torch.zeros((3, 5), dtype=torch.float32, device="cuda"), out,
+                           torch.empty(bad.scratchBytes(3), dtype=torch.uint8, device="cuda"))
+    assert e.value.case == "badWeights"
