@@ -1,0 +1,77 @@
+"""Tensor-parallel MLP and expert-parallel MoE on 2 GPUs (NCCL) against the single-device oracle.
+Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, results):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import qwegn_b200 as q
+        from qwegn_b200 import parallel as par
+        from oracle import qw_oracle as qo
+        hal = q.QWHal(rank)
+        fmt, cont = qo.HQ4_G32, q.CONTAINERS["HQ4_G32"]
+        rng = np.random.default_rng(9)   # identical data on every rank
+
+        # ---- tensor-parallel MLP: column-parallel gate||up (SwiGLU + FWHT fused), row-parallel down, all-reduce
+        hidden, inter = 512, 1024
+        gu = qo.quantize(rng.normal(0, 0.05, (2 * inter, hidden)).astype(np.float32), fmt)
+        dn = qo.quantize(rng.normal(0, 0.05, (hidden, inter)).astype(np.float32), fmt)
+        mlp = par.TPMlp(hal, torch.from_numpy(gu.reshape(-1)), torch.from_numpy(dn.reshape(-1)), hidden, inter, cont, rank, world)
+        for m in (1, 8):
+            x = rng.standard_normal((m, hidden)).astype(np.float16)
+            h_loc = torch.empty((m, mlp.inter_local), dtype=torch.float16, device="cuda")
+            y = torch.empty((m, hidden), dtype=torch.float32, device="cuda")
+            mlp.forward(torch.from_numpy(x).cuda(), h_loc, y)
+            ref = qo.matmul(dn, fmt, qo.swiglu_f16(qo.matmul(gu, fmt, x), rotate=True), x_is_rotated=True)
+            err = np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max()
+            assert err < 3e-3, ("tp mlp", m, err)
+
+        # ---- expert-parallel MoE: tokens sharded over ranks, experts sharded over ranks
+        e, k, hid, it, t_total = 16, 4, 256, 128, 96
+        bgu = qo.quantize(rng.normal(0, 0.05, (e * 2 * it, hid)).astype(np.float32), fmt)
+        bdn = qo.quantize(rng.normal(0, 0.05, (e * hid, it)).astype(np.float32), fmt)
+        xs = rng.standard_normal((t_total, hid)).astype(np.float16)
+        lg = rng.standard_normal((t_total, e)).astype(np.float32)
+        ep = par.EPMoE(hal, torch.from_numpy(bgu.reshape(-1)), torch.from_numpy(bdn.reshape(-1)), e, hid, it, k, cont, rank, world)
+        t0, t1 = t_total * rank // world, t_total * (rank + 1) // world
+        out = ep.forward(torch.from_numpy(xs[t0:t1]).cuda(), torch.from_numpy(lg[t0:t1]).cuda())
+        ridx, rwts = qo.moe_route(lg[t0:t1], k, norm_topk=True)
+        ref = qo.moe_forward(bgu, bdn, fmt, e, hid, it, xs[t0:t1], ridx, rwts)
+        err = np.abs(out.cpu().numpy() - ref).max() / np.abs(ref).max()
+        assert err < 8e-3, ("ep moe", err)
+        assert hal.device_status() == 0
+        results[rank] = True
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp_mlp_and_ep_moe_on_two_gpus():
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert all(results.get(r) for r in range(world))
