@@ -218,7 +218,7 @@ def run_ours(args):
     hal = q.QWHal(local_rank)
     peaks = measured_peaks()
     n, k, m = WORKLOAD["n"], WORKLOAD["k"], WORKLOAD["m"]
-    sections = set(args.sections.split(",")) if args.sections else {"sweep", "c1", "cpu"}
+    sections = set(args.sections.split(",")) if args.sections else {"sweep", "c1", "cpu", "prefill", "moe", "parallel"}
 
     # ---- headline: device-resident GEMV, weights rotating through > L2 of distinct banks -------------------
     sampler = ClockSampler(physical_gpu_index(local_rank))
@@ -300,8 +300,16 @@ def run_ours(args):
                     sweep[f"{cname}_M{mm}"] = {"GBps": round(b / (t * 1e-3) / 1e9, 1), "us": round(t * 1e3, 2)}
                     torch.cuda.empty_cache()
             extra["verify_sweep_N17408_K5120"] = sweep
+        if "prefill" in sections:
+            extra["prefill_M4096"] = bench_prefill(q, hal, peaks)
+        if "moe" in sections:
+            extra["moe_T2048_E256_top8"] = bench_moe(q, hal)
         if "cpu" in sections:
             line["cpu_baseline"] = cpu_baseline(q, hal, n, k, m)
+    if world > 1 and "parallel" in sections:
+        par = bench_parallel(q, hal, rank, world, dist)
+        if rank == 0:
+            extra.update(par)
     if extra:
         line["extra"] = extra
     if rank == 0:
@@ -309,6 +317,111 @@ def run_ours(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def _time_call(fn, iters, warm=3):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def bench_prefill(q, hal, peaks):
+    """Prefill GEMMs of one layer of the 27B-shaped dense transformer: M = 4096, hidden 5120, intermediate 17408,
+    QKV width 7168; HQ4_G32; rotated f16 activations resident; f16 out.  TFLOP/s = 2 M N K / time."""
+    import torch
+    out = {}
+    m = 4096
+    cont = q.CONTAINERS["HQ4_G32"]
+    for name, (n, k) in {"gate_up_N34816_K5120": (34816, 5120), "down_N5120_K17408": (5120, 17408), "qkv_N7168_K5120": (7168, 5120)}.items():
+        w = torch.randn((n, k), device="cuda", dtype=torch.float32) * 0.02
+        view = q.QWWeightView(q.QWGemm.quantize(hal, w, cont), n, k, cont)
+        del w
+        x = torch.randn((m, k), device="cuda", dtype=torch.float32).to(torch.float16)
+        q.QWGemm.encodeFwht32(hal, x)
+        y = torch.empty((m, n), dtype=torch.float16, device="cuda")
+        ms = _time_call(lambda: q.QWGemm.encode(hal, view, x, y, x_is_rotated=True), 10)
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        out[name] = {"ms": round(ms, 4), "TFLOPs": round(tf, 1), "frac_of_burst_peak": round(tf / peaks["bf16_tflops"], 3),
+                     "frac_of_sustained_peak": round(tf / peaks["bf16_tflops_sustained"], 3)}
+        del view, x, y
+        torch.cuda.empty_cache()
+    return out
+
+
+def bench_moe(q, hal):
+    """The 35B-A3B-shaped sparse MoE block: 2048 tokens, 256 experts, top-8, hidden 2048, expert intermediate 512,
+    HQ4_G32; router logits N(0, 1); the whole operator chain (route .. combine) per step."""
+    import torch
+    t, e, k, h, inter = 2048, 256, 8, 2048, 512
+    cont = q.CONTAINERS["HQ4_G32"]
+    gu = q.QWGemm.quantize(hal, torch.randn((e * 2 * inter, h), device="cuda") * 0.02, cont)
+    dn = q.QWGemm.quantize(hal, torch.randn((e * h, inter), device="cuda") * 0.02, cont)
+    op = q.QWMoEOperator(hal, q.QWWeightView(gu, e * 2 * inter, h, cont), q.QWWeightView(dn, e * h, inter, cont), e, inter, k)
+    x = torch.randn((t, h), device="cuda").to(torch.float16)
+    lg = torch.randn((t, e), device="cuda")
+    outp = torch.empty((t, h), device="cuda")
+    sc = torch.empty(op.scratchBytes(t), dtype=torch.uint8, device="cuda")
+    ms = _time_call(lambda: op.encodeResident(x, lg, outp, sc), 20)
+    flops = 2.0 * t * k * (2 * inter * h + h * inter)
+    wbytes = e * (2 * inter * (h // 32) * 20 + h * (inter // 32) * 20)
+    return {"us": round(ms * 1e3, 1), "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 1), "weight_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1),
+            "bound": "decode rate of the converter warps (64 rows per expert): neither the HBM nor the tensor roof binds yet"}
+
+
+def bench_parallel(q, hal, rank, world, dist):
+    """Tensor-parallel MLP of a 70B-class layer (hidden 8192, intermediate 28672, HQ4_G32; column-parallel gate||up with
+    fused SwiGLU+FWHT, row-parallel down, one NCCL all-reduce) at M = 1, and the expert-parallel MoE block (2048
+    tokens sharded over the ranks, 256 experts sharded over the ranks, NCCL all-to-all).  Max over ranks."""
+    import torch
+    from qwegn_b200 import parallel as par
+    cont = q.CONTAINERS["HQ4_G32"]
+    out = {}
+
+    def tmax(ms):
+        tt = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    hidden, inter = 8192, 28672
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(77)   # the same bank on every rank; each keeps its shard
+    gu_plane = q.QWGemm.quantize(hal, torch.randn((2 * inter, hidden), generator=gen, device="cuda") * 0.02, cont)
+    dn_plane = q.QWGemm.quantize(hal, torch.randn((hidden, inter), generator=gen, device="cuda") * 0.02, cont)
+    mlp = par.TPMlp(hal, gu_plane, dn_plane, hidden, inter, cont, rank, world)
+    del gu_plane, dn_plane
+    torch.cuda.empty_cache()
+    x = torch.randn((1, hidden), generator=gen, device="cuda").to(torch.float16)
+    h_loc = torch.empty((1, mlp.inter_local), dtype=torch.float16, device="cuda")
+    y = torch.empty((1, hidden), dtype=torch.float32, device="cuda")
+    dist.barrier()
+    ms = tmax(_time_call(lambda: mlp.forward(x, h_loc, y), 50, warm=5))
+    wbytes = (2 * inter * (hidden // 32) + hidden * (inter // 32)) * 20
+    out[f"tp{world}_mlp_decode_M1_H8192_I28672"] = {"us": round(ms * 1e3, 1), "aggregate_weight_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1)}
+    del mlp
+    torch.cuda.empty_cache()
+
+    t, e, k, h, it = 2048, 256, 8, 2048, 512
+    gu = q.QWGemm.quantize(hal, torch.randn((e * 2 * it, h), generator=gen, device="cuda") * 0.02, cont)
+    dn = q.QWGemm.quantize(hal, torch.randn((e * h, it), generator=gen, device="cuda") * 0.02, cont)
+    ep = par.EPMoE(hal, gu, dn, e, h, it, k, cont, rank, world)
+    del gu, dn
+    torch.cuda.empty_cache()
+    t0, t1 = t * rank // world, t * (rank + 1) // world
+    xs = torch.randn((t, h), generator=gen, device="cuda").to(torch.float16)[t0:t1].contiguous()
+    lg = torch.randn((t, e), generator=gen, device="cuda")[t0:t1].contiguous()
+    dist.barrier()
+    ms = tmax(_time_call(lambda: ep.forward(xs, lg), 10, warm=3))
+    flops = 2.0 * t * k * (2 * it * h + h * it)
+    out[f"ep{world}_moe_T2048_E256_top8"] = {"us": round(ms * 1e3, 1), "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 1)}
+    return out
 
 
 def cpu_baseline(q, hal, n, k, m):
