@@ -129,6 +129,18 @@ int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const vo
 size_t qwc_gemm_workspace_bytes(const qwc_hal* hal, const qwc_weight_view* w, int64_t m, int32_t epilogue,
                                 int32_t x_is_rotated);
 
+/* No counterpart in the reference.  The small-M matmul door (m <= 16, same arguments and results as qwc_gemm) for
+ * callers that cannot allocate device memory where they call it -- an operator inside an engine whose arena was
+ * frozen at load time, a thread that must not risk the device-wide synchronisation of cudaMalloc, a host running
+ * under a memory budget already handed out.  When the call needs scratch (9..16 tokens with K processed in slices)
+ * it comes from a fixed 2 MiB array inside the library's device image, held by every GPU that loads the library.
+ * Needs beyond qwc_static_scratch_capacity() are refused (QWC_ERR_BAD_SHAPE).  The first call on a device looks up
+ * the array's device address: make it before any stream capture, with that device current.  All calls share the
+ * array, so calls that could overlap on the GPU must be ordered by the caller.  Never allocates. */
+int qwc_gemm_static_scratch(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const void* x_f16, int64_t m,
+                            int64_t ldx, void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated);
+size_t qwc_static_scratch_capacity(void);
+
 /* ---- mixture of experts ---------------------------------------------------------------------------------------
  * The operator chain of QWMoEOperator.encodeResident (Sources/Operators/QWGEMM/QWMoEOperator.swift:206-442), grouped
  * path: route -> pair sort + tile plan -> gather -> grouped gate/up GEMM -> SwiGLU + FWHT -> grouped down GEMM ->

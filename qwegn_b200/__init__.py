@@ -8,6 +8,7 @@ from ._lib import (EPI_NONE, EPI_SILU_PAIR, EPI_SILU_PAIR_FWHT, F16, F32, KIND_H
 from .gemm import (CONTAINERS, ContainerKind, QWGemm, QWGemmError, QWGemmPlan, QWHal, QWWeightView,
                    incumbentHQ4G32, rotatedHQ)
 from .moe import QWGemmMoE, QWMoEOperator
+from . import noalloc  # noqa: F401  (registers qwc_gemm_static_scratch)
 
 __all__ = [
     "EPI_NONE", "EPI_SILU_PAIR", "EPI_SILU_PAIR_FWHT", "F16", "F32", "KIND_HQ4_G32_M5", "KIND_ROTATED_HQ",
