@@ -147,7 +147,7 @@ size_t qwc_static_scratch_capacity(void);
  * weighted combine.  All scratch is caller-allocated (QWMoEOperator.Scratch, :131-192). */
 
 /* One tile of a grouped expert GEMM (the tile list of Sources/QWMetal/gemm/qwgemm_moe_group_f32.metal:82-115,
- * with 128 expert weight rows x up to 256 expert-sorted activation rows per tile). */
+ * with 128 expert weight rows x up to qwc_moe_tile_rows() expert-sorted activation rows per tile). */
 typedef struct {
     int32_t w_row0; /* first weight row of the tile in the stacked expert bank */
     int32_t w_rows; /* valid weight rows (<= 128) */
@@ -175,6 +175,8 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
                         int64_t gu_rows, int64_t dn_rows, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
                         int32_t* tile_counts);
 int64_t qwc_moe_max_tiles(int64_t pairs, int64_t e, int64_t rows_per_expert);
+/* Activation rows per tile the plan uses for this problem size (192 today; the kernel also takes 64 and 256). */
+int32_t qwc_moe_tile_rows(int64_t pairs, int64_t e);
 
 /* Gather + rotate: xs[p, :] = f16(fwht32(x[sorted_tok[p], :])) for the sorted pairs (x_is_rotated != 0: plain copy).
  * Stands where the gather-A of qwg_moe_nax_gemm (Sources/QWMetal/include/qw_gemm_nax.metalh:436-470) and the bridge
@@ -184,10 +186,10 @@ int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t l
 
 /* QWGemm.encodeMoEGateUpNax / encodeMoENaxSplitF32 (QWGemmMoE.swift:201-296): grouped expert GEMM over the tile list.
  * bank: stacked expert bank [e * rows_per_expert, k]; xs: expert-sorted rotated activations f16 [pairs, k];
- * y: f16 or f32 [pairs, rows_per_expert]. */
+ * y: f16 or f32 [pairs, rows_per_expert].  x_tile_rows = qwc_moe_tile_rows() of the call that built the list. */
 int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank, const void* xs_f16, int64_t pairs,
-                         const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, void* y, int32_t y_dtype,
-                         int64_t ldy);
+                         const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, int32_t x_tile_rows, void* y,
+                         int32_t y_dtype, int64_t ldy);
 
 /* QWGemm.encodeSiluMulSplitF16 (Sources/Operators/QWGEMM/QWGemmF32.swift:96-105; kernels
  * Sources/QWMetal/gemm/qwgemm_batched.metal:55-97): h[p, i] = fwht32(f16(silu(gu[p, i]) * gu[p, inter + i])). */

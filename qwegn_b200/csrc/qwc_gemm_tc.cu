@@ -5,7 +5,7 @@
 //   Y[m, n] = sum_k Xrot[m, k] * Wrot[n, k],   f16 operands, f32 accumulate in tensor memory.
 //
 // One persistent CTA per SM walks (weight tile, token tile) pairs.  Per 64-wide K tile:
-//   * a TMA warp brings the packed weight rows, unchanged, into shared memory (2-D tensor copy, 128 rows x one
+//   * two TMA warps bring the packed weight rows, unchanged, into shared memory (2-D tensor copy, 128 rows x one
 //     raw step of 128 k) and the rotated activations (256 tokens x 64 k, 128-byte swizzle);
 //   * eight converter warps decode the packed blocks to f16 in registers (magic-bias form, one f16 FMA with scale
 //     and bias: the reference's in-register decode, qw_gemm_nax.metalh:114-127) and store them as the K-major,
@@ -29,13 +29,20 @@ constexpr int kBM = 128;        // weight rows per tile (UMMA M)
 constexpr int kBN = 256;        // tokens per tile (UMMA N)
 constexpr int kBK = 64;         // k per operand tile (one 128-byte swizzle atom of f16)
 constexpr int kRawK = 128;      // k per raw weight step (two operand tiles)
-constexpr int kConvWarps = 8;
+#ifndef QWC_TC_CONV_WARPS
+#define QWC_TC_CONV_WARPS 16
+#endif
+constexpr int kConvWarps = QWC_TC_CONV_WARPS;   // 8 rows x 4 units per warp step: 16 warps decode a raw step in one step
 constexpr int kEpiWarps = 4;
-constexpr int kWarps = 2 + kConvWarps + kEpiWarps;
+constexpr int kConvGroups = 2;                         // groups of converter warps that alternate raw steps
+constexpr int kGroupWarps = kConvWarps / kConvGroups;
+constexpr int kFirstConvWarp = 3;   // warps 0, 1, 2: activation TMA, MMA issue, weight TMA
+constexpr int kWarps = kFirstConvWarp + kConvWarps + kEpiWarps;
 constexpr int kTcThreads = kWarps * 32;
 constexpr int kWTileBytes = kBM * kBK * 2;   // 16 KB
 constexpr int kXTileBytes = kBN * kBK * 2;   // 32 KB
-constexpr int kMaxAB = 4, kMaxRaw = 3;
+constexpr int kStages = 4;    // operand stages (one decoded weight tile + one activation tile each)
+constexpr int kMaxRaw = 4;    // raw (packed weight) stages
 
 struct TcParams {
     void* y;
@@ -43,7 +50,9 @@ struct TcParams {
     int32_t* status;
     int m, n, k;
     int y_f16;
-    int ab_stages, raw_stages;
+    int raw_stages;
+    int x_tile_rows;     // activation rows per tile: 256 (192 for the 36-byte containers, to fit shared memory), 64 for small expert tiles
+    int x_slot_bytes;    // bytes of one activation stage: 256 rows x 128 B, or 64 x 128 B when every tile has <= 64 rows
     int raw_row_bytes;   // packed bytes of 128 k of one row: 80 (HQ4_G32_M5) or 144 (HQ8_G32)
     int m_tiles, n_tiles;
     // grouped mode (MoE expert GEMMs): tiles come from a device-side list built by the pair sort
@@ -156,49 +165,52 @@ __device__ __forceinline__ void decode_unit_natural(const uint8_t* blk, uint4 ou
     }
 }
 
-struct Ring {
-    int slot;
-    uint32_t parity;
-    int depth;
-    __device__ __forceinline__ void advance() {
-        if (++slot == depth) {
-            slot = 0;
-            parity ^= 1u;
-        }
+// Latency-critical wait of the MMA-issuing thread: a plain spin on try_wait (no suspend hint, no sleep); bounded.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 26); ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
     }
-};
+    return false;
+}
 
 template <int FMT>
 __global__ void __launch_bounds__(kTcThreads, 1)
-qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
+qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
+                   const __grid_constant__ CUtensorMap xmap128, const __grid_constant__ CUtensorMap xmap64) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // layout (1024-byte aligned base): [W tiles][X tiles][raw stages][barriers]
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* wt = smem;
-    uint8_t* xt = wt + p.ab_stages * kWTileBytes;
-    uint8_t* raw = xt + p.ab_stages * kXTileBytes;
+    uint8_t* xt = wt + kStages * kWTileBytes;
+    uint8_t* raw = xt + kStages * p.x_slot_bytes;
     const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
     uint64_t* bars = reinterpret_cast<uint64_t*>(raw + p.raw_stages * raw_stage_bytes);
-    uint64_t* x_full = bars;                  // [kMaxAB]
-    uint64_t* w_full = bars + kMaxAB;         // [kMaxAB]
-    uint64_t* ab_empty = bars + 2 * kMaxAB;   // [kMaxAB]
-    uint64_t* raw_full = bars + 3 * kMaxAB;   // [kMaxRaw]
-    uint64_t* raw_empty = raw_full + kMaxRaw; // [kMaxRaw]
-    uint64_t* acc_full = raw_empty + kMaxRaw; // [2]
-    uint64_t* acc_empty = acc_full + 2;       // [2]
+    uint64_t* full = bars;                       // [kStages]  activations landed (tx) + the group's converters arrived
+    uint64_t* empty = bars + kStages;            // [kStages]  tcgen05.commit: the MMAs have read both operand tiles
+    uint64_t* raw_full = bars + 2 * kStages;     // [kMaxRaw]
+    uint64_t* raw_empty = raw_full + kMaxRaw;    // [kMaxRaw]
+    uint64_t* acc_full = raw_empty + kMaxRaw;    // [2]
+    uint64_t* acc_empty = acc_full + 2;          // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.ab_stages; ++s) {
-            mbar_init(&x_full[s], 1);
-            mbar_init(&w_full[s], kConvWarps);
-            mbar_init(&ab_empty[s], 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1 + kGroupWarps);
+            mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < p.raw_stages; ++s) {
             mbar_init(&raw_full[s], 1);
-            mbar_init(&raw_empty[s], kConvWarps);
+            mbar_init(&raw_empty[s], kGroupWarps);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
@@ -231,8 +243,8 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
             const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;   // token tiles fastest: CTAs share weight rows in L2
             t.w_row0 = nt * kBM;
             t.w_rows = min(kBM, p.n - t.w_row0);
-            t.x_row0 = mt * kBN;
-            t.x_rows = min(kBN, p.m - t.x_row0);
+            t.x_row0 = mt * p.x_tile_rows;
+            t.x_rows = min(p.x_tile_rows, p.m - t.x_row0);
             t.y_col0 = t.w_row0;
         }
         return t;
@@ -245,35 +257,50 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         *abort_flag = 1;
     };
 
+    // K tile number j of the kernel (all tiles) uses stage j % kStages in phase (j / kStages) & 1; raw step r covers
+    // K tiles 2r and 2r + 1 and belongs to converter group r % kConvGroups, which therefore always owns the same two
+    // stages (kStages == 2 * kConvGroups).
     if (warp == 0) {
-        // ------------------------------- TMA producer -------------------------------
+        // ---------------- TMA producer: rotated activations (one tile per K tile) ----------------
         if (lane == 0) {
-            Ring ab{0, 0, p.ab_stages}, rr{0, 0, p.raw_stages};
-            uint32_t ab_fills = 0, raw_fills = 0;
+            uint32_t j = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const TileInfo ti = get_tile(tile);
-                for (int rs = 0; rs < raw_steps && ok; ++rs) {
-                    if (raw_fills >= static_cast<uint32_t>(p.raw_stages) && !mbar_wait(&raw_empty[rr.slot], rr.parity ^ 1u)) {
+                // the narrowest activation box that covers the tile's tokens
+                const CUtensorMap* xm = ti.x_rows <= 64 ? &xmap64 : (ti.x_rows <= 128 ? &xmap128 : &xmap);
+                const uint32_t xbytes = (ti.x_rows <= 64 ? 64u : (ti.x_rows <= 128 ? 128u : static_cast<uint32_t>(p.x_tile_rows))) * kBK * 2u;
+                for (int kt = 0; kt < ktiles; ++kt, ++j) {
+                    const uint32_t s = j % kStages;
+                    if (j >= kStages && !mbar_wait_relaxed(&empty[s], ((j / kStages) - 1) & 1u)) {
                         fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
                         ok = false;
                         break;
                     }
-                    mbar_arrive_expect_tx(&raw_full[rr.slot], static_cast<uint32_t>(kBM * p.raw_row_bytes));
-                    tma_load_2d(raw + rr.slot * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[rr.slot]);
-                    rr.advance();
-                    ++raw_fills;
-                    for (int h = 0; h < kRawK / kBK && ok; ++h) {
-                        if (ab_fills >= static_cast<uint32_t>(p.ab_stages) && !mbar_wait(&ab_empty[ab.slot], ab.parity ^ 1u)) {
-                            fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
-                            ok = false;
-                            break;
-                        }
-                        mbar_arrive_expect_tx(&x_full[ab.slot], kXTileBytes);
-                        tma_load_2d(xt + ab.slot * kXTileBytes, &xmap, (rs * (kRawK / kBK) + h) * kBK, ti.x_row0, &x_full[ab.slot]);
-                        ab.advance();
-                        ++ab_fills;
+                    mbar_arrive_expect_tx(&full[s], xbytes);
+                    tma_load_2d(xt + s * p.x_slot_bytes, xm, kt * kBK, ti.x_row0, &full[s]);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 2) {
+        // ---------------- TMA producer: packed weight rows (one raw step = two K tiles) ----------------
+        // A warp of its own so the weight stream runs ahead by the whole raw ring: the packed rows come from HBM / L2
+        // with the longest latency of the pipeline.
+        if (lane == 0) {
+            uint32_t r = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileInfo ti = get_tile(tile);
+                for (int rs = 0; rs < raw_steps; ++rs, ++r) {
+                    const uint32_t s = r % p.raw_stages;
+                    if (r >= static_cast<uint32_t>(p.raw_stages) && !mbar_wait_relaxed(&raw_empty[s], ((r / p.raw_stages) - 1) & 1u)) {
+                        fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
+                        ok = false;
+                        break;
                     }
+                    mbar_arrive_expect_tx(&raw_full[s], static_cast<uint32_t>(kBM * p.raw_row_bytes));
+                    tma_load_2d(raw + s * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[s]);
                 }
             }
         }
@@ -281,61 +308,62 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     } else if (warp == 1) {
         // ------------------------------- MMA issuer -------------------------------
         if (lane == 0) {
-            Ring ab{0, 0, p.ab_stages};
-            uint32_t tiles_done = 0;
+            uint32_t j = 0, tiles_done = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tiles_done) {
                 const int as = tiles_done & 1;
-                if (tiles_done >= 2 && !mbar_wait(&acc_empty[as], ((tiles_done >> 1) - 1) & 1)) {
+                if (tiles_done >= 2 && !mbar_wait_spin(&acc_empty[as], ((tiles_done >> 1) - 1) & 1)) {
                     fail(QWC_DEV_WAIT_TMEM_TIMEOUT);
                     break;
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * kBN);
                 const uint32_t idesc = make_idesc(min(kBN, (get_tile(tile).x_rows + 15) & ~15));
-                for (int kt = 0; kt < ktiles; ++kt) {
-                    if (!mbar_wait(&x_full[ab.slot], ab.parity) || !mbar_wait(&w_full[ab.slot], ab.parity)) {
+                for (int kt = 0; kt < ktiles; ++kt, ++j) {
+                    const uint32_t s = j % kStages;
+                    if (!mbar_wait_spin(&full[s], (j / kStages) & 1u)) {
                         fail(QWC_DEV_WAIT_FULL_TIMEOUT);
                         ok = false;
                         break;
                     }
-                    tc_fence_after();
-                    const uint32_t a_addr = smem_u32(wt + ab.slot * kWTileBytes), b_addr = smem_u32(xt + ab.slot * kXTileBytes);
+                    const uint32_t a_addr = smem_u32(wt + s * kWTileBytes), b_addr = smem_u32(xt + s * p.x_slot_bytes);
 #pragma unroll
-                    for (int j = 0; j < kBK / 16; ++j)
-                        umma_f16(d_tmem, umma_desc_sw128(a_addr + j * 32), umma_desc_sw128(b_addr + j * 32), idesc, (kt > 0 || j > 0) ? 1u : 0u);
-                    umma_commit(&ab_empty[ab.slot]);  // frees the stage when these MMAs have read it
-                    ab.advance();
+                    for (int q = 0; q < kBK / 16; ++q)
+                        umma_f16(d_tmem, umma_desc_sw128(a_addr + q * 32), umma_desc_sw128(b_addr + q * 32), idesc, (kt > 0 || q > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);   // the stage is free once these MMAs have read it
                 }
                 if (ok) umma_commit(&acc_full[as]);
             }
         }
         __syncwarp();
-    } else if (warp < 2 + kConvWarps) {
+    } else if (warp < kFirstConvWarp + kConvWarps) {
         // ------------------------------- converters -------------------------------
-        const int cw = warp - 2;
+        // The converter warps form kConvGroups groups that take the raw steps in turn.  A step costs a warp its decode
+        // plus a proxy fence of several hundred cycles; with every warp on the same step those latencies lie on the
+        // tensor core's critical path, with alternating groups they overlap with the other group's MMAs.
+        const int cw = warp - kFirstConvWarp;
+        const int grp = cw / kGroupWarps, cwl = cw % kGroupWarps;
         const int r8 = lane >> 2, u = lane & 3;   // 8 rows x 4 units per warp step
         const int unit_bytes = p.raw_row_bytes / 4;
-        Ring ab{0, 0, p.ab_stages}, rr{0, 0, p.raw_stages};
-        uint32_t ab_uses = 0;
+        const uint32_t s0 = 2 * grp, s1 = 2 * grp + 1;   // this group's operand stages
+        uint8_t* wdst = wt + ((u >> 1) ? s1 : s0) * kWTileBytes;
         bool ok = true;
+        uint32_t r = 0;   // raw steps since the kernel started (all tiles)
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            for (int rs = 0; rs < raw_steps && ok; ++rs) {
-                // both operand stages of this raw step must have been read by the tensor core
-                Ring ab1 = ab;
-                ab1.advance();
-                if (!mbar_wait(&raw_full[rr.slot], rr.parity) ||
-                    (ab_uses >= static_cast<uint32_t>(p.ab_stages) && !mbar_wait(&ab_empty[ab.slot], ab.parity ^ 1u)) ||
-                    (ab_uses + 1 >= static_cast<uint32_t>(p.ab_stages) && !mbar_wait(&ab_empty[ab1.slot], ab1.parity ^ 1u))) {
+            for (int rs = 0; rs < raw_steps; ++rs, ++r) {
+                if (static_cast<int>(r % kConvGroups) != grp) continue;
+                const uint32_t rslot = r % p.raw_stages, rpar = (r / p.raw_stages) & 1u;
+                const uint32_t use = r / kConvGroups;   // how often this group has filled its stages before
+                if (!mbar_wait(&raw_full[rslot], rpar) ||
+                    (use > 0 && (!mbar_wait(&empty[s0], (use - 1) & 1u) || !mbar_wait(&empty[s1], (use - 1) & 1u)))) {
                     if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
                     ok = false;
                     break;
                 }
-                uint8_t* wdst = wt + ((u >> 1) ? ab1.slot : ab.slot) * kWTileBytes;
-                const uint8_t* rbase = raw + rr.slot * raw_stage_bytes;
+                const uint8_t* rbase = raw + rslot * raw_stage_bytes;
 #pragma unroll
-                for (int it = 0; it < kBM / (kConvWarps * 8); ++it) {
-                    const int row = cw * (kBM / kConvWarps) + it * 8 + r8;
+                for (int it = 0; it < kBM / (kGroupWarps * 8); ++it) {
+                    const int row = cwl * (kBM / kGroupWarps) + it * 8 + r8;
                     uint4 ch[4];
                     decode_unit_natural<FMT>(rbase + row * p.raw_row_bytes + u * unit_bytes, ch);
                     uint8_t* rowp = wdst + (row >> 3) * 1024 + (row & 7) * 128;
@@ -346,14 +374,10 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                 fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async-proxy reads
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&w_full[ab.slot]);
-                    mbar_arrive(&w_full[ab1.slot]);
-                    mbar_arrive(&raw_empty[rr.slot]);
+                    mbar_arrive(&full[s0]);
+                    mbar_arrive(&full[s1]);
+                    mbar_arrive(&raw_empty[rslot]);
                 }
-                ab = ab1;
-                ab.advance();
-                ab_uses += 2;
-                rr.advance();
             }
         }
     } else {
@@ -363,7 +387,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tiles_done) {
             const TileInfo ti = get_tile(tile);
             const int as = tiles_done & 1;
-            if (!mbar_wait(&acc_full[as], (tiles_done >> 1) & 1)) {
+            if (!mbar_wait_relaxed(&acc_full[as], (tiles_done >> 1) & 1)) {
                 if (lane == 0) fail(QWC_DEV_WAIT_MMA_TIMEOUT);
                 break;
             }
@@ -374,16 +398,16 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * kBN);
 #pragma unroll 1
             for (int c = 0; c < chunks; ++c) {
-                uint32_t r[32];
-                tmem_ld32(taddr + c * 32, r);
+                uint32_t rr[32];
+                tmem_ld32(taddr + c * 32, rr);
                 tmem_ld_wait();
                 if (wr < ti.w_rows) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (c * 32 + j < ti.x_rows) {
-                            const int64_t o = static_cast<int64_t>(ti.x_row0 + c * 32 + j) * p.ldy + ycol;
-                            if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(__uint_as_float(r[j]));
-                            else static_cast<float*>(p.y)[o] = __uint_as_float(r[j]);
+                    for (int jj = 0; jj < 32; ++jj) {
+                        if (c * 32 + jj < ti.x_rows) {
+                            const int64_t o = static_cast<int64_t>(ti.x_row0 + c * 32 + jj) * p.ldy + ycol;
+                            if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(__uint_as_float(rr[jj]));
+                            else static_cast<float*>(p.y)[o] = __uint_as_float(rr[jj]);
                         }
                     }
                 }
@@ -421,14 +445,14 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 template <int FMT>
-int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& xmap, int smem,
+int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap* xmaps, int smem,
               int grid) {
     static bool configured[64] = {};
     if (!configured[hal->device & 63]) {
         QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured[hal->device & 63] = true;
     }
-    qwc_gemm_tc_kernel<FMT><<<grid, kTcThreads, smem, st>>>(p, wmap, xmap);
+    qwc_gemm_tc_kernel<FMT><<<grid, kTcThreads, smem, st>>>(p, wmap, xmaps[0], xmaps[1], xmaps[2]);
     QWC_CUDA_TRY(cudaGetLastError());
     return QWC_OK;
 }
@@ -453,7 +477,8 @@ size_t qwc_gemm_tc_workspace_bytes(const qwc_weight_view* w, int64_t m, int x_is
 
 // Shared by the dense door and the grouped (MoE) door: tensor maps, shared-memory budget, launch.
 static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const __half* xr, int64_t ldxr, int64_t m,
-                  void* y, int y_dtype, int64_t ldy, const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles) {
+                  void* y, int y_dtype, int64_t ldy, const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles,
+                  int x_tile_rows) {
     const int fmt = qwc_fmt_of(*w);
     TcParams p{};
     p.tiles = tiles;
@@ -466,18 +491,21 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     p.k = static_cast<int>(w->k);
     p.y_f16 = y_dtype == QWC_F16;
     p.raw_row_bytes = fmt == FMT_HQ4_G32_M5 ? 80 : 144;
-    p.m_tiles = static_cast<int>((m + kBN - 1) / kBN);
+    if (tiles == nullptr && fmt != FMT_HQ4_G32_M5) x_tile_rows = 192;   // 36-byte blocks: the raw stages are 1.8x larger
+    p.x_tile_rows = x_tile_rows;
+    p.m_tiles = static_cast<int>((m + x_tile_rows - 1) / x_tile_rows);
     p.n_tiles = static_cast<int>((w->n + kBM - 1) / kBM);
     const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
+    p.x_slot_bytes = x_tile_rows * kBK * 2;
     p.raw_stages = kMaxRaw;
-    p.ab_stages = kMaxAB;
-    auto smem_need = [&](int ab, int rs) { return 1024 + ab * (kWTileBytes + kXTileBytes) + rs * raw_stage_bytes + 512; };
-    while (smem_need(p.ab_stages, p.raw_stages) > 227 * 1024 && p.raw_stages > 2) --p.raw_stages;
-    while (smem_need(p.ab_stages, p.raw_stages) > 227 * 1024 && p.ab_stages > 2) --p.ab_stages;
-    const int smem = smem_need(p.ab_stages, p.raw_stages);
+    auto smem_need = [&](int rs) { return 1024 + kStages * (p.x_slot_bytes + kWTileBytes) + rs * raw_stage_bytes + 512; };
+    while (smem_need(p.raw_stages) > 227 * 1024 && p.raw_stages > 2) --p.raw_stages;
+    if (smem_need(p.raw_stages) > 227 * 1024) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "shared-memory budget exceeded");
+    const int smem = smem_need(p.raw_stages);
 
     const EncodeFn enc = reinterpret_cast<EncodeFn>(hal->encode_tiled);
-    alignas(64) CUtensorMap wmap, xmap;
+    alignas(64) CUtensorMap wmap;
+    alignas(64) CUtensorMap xmaps[3];   // activation boxes of 256, 128 and 64 rows
     const int64_t row_bytes = (w->k / 32) * (fmt == FMT_HQ4_G32_M5 ? 20 : 36);
     {
         const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(row_bytes / 8), static_cast<cuuint64_t>(w->n)};
@@ -489,20 +517,20 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return qwc_fail(QWC_ERR_CUDA, "cuTensorMapEncodeTiled(weights) failed with %d", static_cast<int>(cr));
     }
-    {
+    for (int i = 0; i < 3; ++i) {
         const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(w->k), static_cast<cuuint64_t>(m)};
         const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ldxr * 2)};
-        const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(kBN)};
+        const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(i == 0 ? x_tile_rows : (i == 1 ? 128 : 64))};
         const cuuint32_t estr[2] = {1, 1};
-        const CUresult cr = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(xr), gdim, gstride, box, estr,
+        const CUresult cr = enc(&xmaps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(xr), gdim, gstride, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return qwc_fail(QWC_ERR_CUDA, "cuTensorMapEncodeTiled(activations) failed with %d", static_cast<int>(cr));
     }
     const int64_t ntiles = tiles != nullptr ? max_tiles : static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     const int grid = static_cast<int>(ntiles < hal->sm_count ? (ntiles < 1 ? 1 : ntiles) : hal->sm_count);
-    if (fmt == FMT_HQ4_G32_M5) return launch_tc<FMT_HQ4_G32_M5>(hal, st, p, wmap, xmap, smem, grid);
-    return launch_tc<FMT_HQ8_G32>(hal, st, p, wmap, xmap, smem, grid);
+    if (fmt == FMT_HQ4_G32_M5) return launch_tc<FMT_HQ4_G32_M5>(hal, st, p, wmap, xmaps, smem, grid);
+    return launch_tc<FMT_HQ8_G32>(hal, st, p, wmap, xmaps, smem, grid);
 }
 
 int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
@@ -523,12 +551,13 @@ int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_vie
     } else if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || ldx % 8 != 0) {
         return qwc_fail(QWC_ERR_BAD_SHAPE, "rotated activations must be 16-byte aligned with ldx %% 8 == 0 for the tensor-core path");
     }
-    return tc_run(hal, st, w, xr, ldxr, m, y, y_dtype, ldy, nullptr, nullptr, 0);
+    return tc_run(hal, st, w, xr, ldxr, m, y, y_dtype, ldy, nullptr, nullptr, 0, kBN);
 }
 
 // Grouped expert GEMM: the same kernel over a device-side tile list (see qwc_moe_group_pairs).
 int qwc_launch_gemm_tc_grouped(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* bank, const void* xs, int64_t pairs,
                                const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, void* y, int y_dtype,
-                               int64_t ldy) {
-    return tc_run(hal, st, bank, static_cast<const __half*>(xs), bank->k, pairs, y, y_dtype, ldy, tiles, tile_count, max_tiles);
+                               int64_t ldy, int x_tile_rows) {
+    return tc_run(hal, st, bank, static_cast<const __half*>(xs), bank->k, pairs, y, y_dtype, ldy, tiles, tile_count, max_tiles,
+                  x_tile_rows);
 }

@@ -9,13 +9,17 @@
 #include "qwc_common.cuh"
 
 int qwc_launch_gemm_tc_grouped(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, const qwc_moe_tile*,
-                               const int32_t*, int64_t, void*, int, int64_t);
+                               const int32_t*, int64_t, void*, int, int64_t, int);
 bool qwc_gemm_tc_supported(const qwc_hal*, const qwc_weight_view*, int64_t, int);
 
 namespace {
 
 constexpr int kTileW = 128;  // weight rows per grouped-GEMM tile
-constexpr int kTileX = 256;  // activation rows per grouped-GEMM tile
+// Activation rows per grouped-GEMM tile.  The tensor-core kernel pays a fixed cost per K tile whatever the token
+// count, so fewer, taller tiles win (64-row tiles were measured 30 % slower at 64 rows per expert); 192 rows is the
+// tallest tile whose stages fit in shared memory for the 36-byte containers too.  The kernel still fetches only a
+// 64- or 128-row activation box when the tile is that small.
+__host__ __device__ inline int moe_tile_rows(int64_t pairs, int64_t e) { return (pairs >= 0 && e > 0) ? 192 : 192; }
 
 __device__ __forceinline__ bool finite_bits(float v) { return (__float_as_uint(v) & 0x7F800000u) != 0x7F800000u; }
 
@@ -109,27 +113,37 @@ __global__ void __launch_bounds__(128) qwc_moe_route_kernel(const float* __restr
 }
 
 // Pass 1 of the pair sort: one warp per expert counts its pairs; warp `e` (one past the last expert) marks the
-// dropped pairs (idx < 0 or >= e) in inv_perm.
-__global__ void __launch_bounds__(256) qwc_moe_count_kernel(const int32_t* __restrict__ idx, int pairs, int e,
+// dropped pairs (idx < 0 or >= e) in inv_perm.  The CTA stages the pair list through shared memory in chunks so the
+// per-warp scans run at shared-memory latency instead of one L2 round trip per 32 pairs.
+constexpr int kSortChunk = 8192;
+
+__global__ void __launch_bounds__(512) qwc_moe_count_kernel(const int32_t* __restrict__ idx, int pairs, int e,
                                                             int32_t* __restrict__ counts, int32_t* __restrict__ inv_perm) {
+    __shared__ int s_idx[kSortChunk];
     const int lane = threadIdx.x & 31;
     const int ex = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (ex > e) return;
     int c = 0;
-    for (int i0 = 0; i0 < pairs; i0 += 32) {
-        const int i = i0 + lane;
-        const int v = i < pairs ? idx[i] : 0;
-        if (ex == e) {
-            if (i < pairs && (v < 0 || v >= e)) inv_perm[i] = -1;
-        } else {
-            c += __popc(__ballot_sync(0xFFFFFFFFu, i < pairs && v == ex));
+    for (int base = 0; base < pairs; base += kSortChunk) {
+        const int n = min(kSortChunk, pairs - base);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += blockDim.x) s_idx[i] = idx[base + i];
+        __syncthreads();
+        if (ex > e) continue;
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const int v = i < n ? s_idx[i] : 0;
+            if (ex == e) {
+                if (i < n && (v < 0 || v >= e)) inv_perm[base + i] = -1;
+            } else {
+                c += __popc(__ballot_sync(0xFFFFFFFFu, i < n && v == ex));
+            }
         }
     }
     if (ex < e && lane == 0) counts[ex] = c;
 }
 
 // Pass 2: exclusive prefix over the experts and the two tile lists (one CTA).
-__global__ void __launch_bounds__(512) qwc_moe_plan_kernel(const int32_t* counts, int e, int32_t* expert_off,
+__global__ void __launch_bounds__(512) qwc_moe_plan_kernel(const int32_t* counts, int e, int kTileX, int32_t* expert_off,
                                                            int gu_rows, int dn_rows, qwc_moe_tile* __restrict__ tiles_gu,
                                                            qwc_moe_tile* __restrict__ tiles_dn, int32_t* __restrict__ tile_counts) {
     __shared__ int s_off[513];
@@ -174,49 +188,88 @@ __global__ void __launch_bounds__(512) qwc_moe_plan_kernel(const int32_t* counts
     }
 }
 
-// Pass 3: one warp per expert places its pairs in ascending pair order.
-__global__ void __launch_bounds__(256) qwc_moe_place_kernel(const int32_t* __restrict__ idx, int pairs, int e, int k,
+// Pass 3: one warp per expert places its pairs in ascending pair order (same staging as pass 1).
+__global__ void __launch_bounds__(512) qwc_moe_place_kernel(const int32_t* __restrict__ idx, int pairs, int e, int k,
                                                             const int32_t* __restrict__ expert_off, int32_t* __restrict__ sorted_pair,
                                                             int32_t* __restrict__ sorted_tok, int32_t* __restrict__ inv_perm) {
+    __shared__ int s_idx[kSortChunk];
     const int lane = threadIdx.x & 31;
     const int ex = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (ex >= e) return;
-    int at = expert_off[ex];
-    for (int i0 = 0; i0 < pairs; i0 += 32) {
-        const int i = i0 + lane;
-        const bool hit = i < pairs && idx[i] == ex;
-        const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
-        if (hit) {
-            const int pos = at + __popc(m & ((1u << lane) - 1u));
-            sorted_pair[pos] = i;
-            sorted_tok[pos] = i / k;
-            inv_perm[i] = pos;
+    int at = ex < e ? expert_off[ex] : 0;
+    for (int base = 0; base < pairs; base += kSortChunk) {
+        const int n = min(kSortChunk, pairs - base);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += blockDim.x) s_idx[i] = idx[base + i];
+        __syncthreads();
+        if (ex >= e) continue;
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < n && s_idx[i] == ex;
+            const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
+            if (hit) {
+                const int pos = at + __popc(m & ((1u << lane) - 1u));
+                sorted_pair[pos] = base + i;
+                sorted_tok[pos] = (base + i) / k;
+                inv_perm[base + i] = pos;
+            }
+            at += __popc(m);
         }
-        at += __popc(m);
     }
 }
 
-// xs[p, :] = rot(x[sorted_tok[p], :]).  One warp per (sorted row, 32-element unit).
+// xs[p, :] = rot(x[sorted_tok[p], :]).  A quad handles one (sorted row, 32-element unit): lane t holds elements
+// 8t..8t+7 (one 16-byte load), rotates with three in-lane butterfly stages and two xor-shuffle stages (the
+// reference's h = 1, 2, 4, 8, 16 order) and writes one 16-byte chunk.  vec != 0 needs 16-byte aligned rows.
 __global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __restrict__ x, int64_t ldx, int h,
                                                              const int32_t* __restrict__ sorted_tok,
-                                                             const int32_t* __restrict__ expert_off, int e, int rotate,
+                                                             const int32_t* __restrict__ expert_off, int e, int rotate, int vec,
                                                              __half* __restrict__ xs) {
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, t4 = lane & 3, q8 = lane >> 2;
     const int units = h / 32;
-    const int64_t valid = expert_off[e];
-    const int64_t total = valid * units;
-    const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
-    for (int64_t it = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); it < total; it += warps) {
-        const int64_t pr = it / units;
-        const int u = static_cast<int>(it % units);
-        const int tok = sorted_tok[pr];
-        float v = __half2float(x[static_cast<int64_t>(tok) * ldx + u * 32 + lane]);
-        if (rotate) {
+    const int64_t total = static_cast<int64_t>(expert_off[e]) * units;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5) * 8;
+    for (int64_t base = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 8; base < total; base += step) {
+        const int64_t it = base + q8;
+        const bool live = it < total;
+        const int64_t pr = live ? it / units : 0;
+        const int u = live ? static_cast<int>(it % units) : 0;
+        const __half* src = x + static_cast<int64_t>(live ? sorted_tok[pr] : 0) * ldx + u * 32 + 8 * t4;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (live) {
+            if (vec) raw = *reinterpret_cast<const uint4*>(src);
+            else {
+                __half tmp[8];
 #pragma unroll
-            for (int s = 1; s < 32; s <<= 1) v = fwht_xor_stage(v, s, (lane & s) != 0);
-            v = __fmul_rn(v, qwc_inv_sqrt32());
+                for (int i = 0; i < 8; ++i) tmp[i] = src[i];
+                raw = *reinterpret_cast<const uint4*>(tmp);
+            }
         }
-        xs[pr * h + u * 32 + lane] = __float2half_rn(v);
+        if (rotate) {
+            __half2 hv[4] = {*reinterpret_cast<__half2*>(&raw.x), *reinterpret_cast<__half2*>(&raw.y),
+                             *reinterpret_cast<__half2*>(&raw.z), *reinterpret_cast<__half2*>(&raw.w)};
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(hv[i]); f[2 * i + 1] = __high2float(hv[i]); }
+#pragma unroll
+            for (int s = 1; s < 8; s <<= 1)
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if ((i & s) == 0) {
+                        const float a = f[i], b = f[i + s];
+                        f[i] = __fadd_rn(a, b);
+                        f[i + s] = __fsub_rn(a, b);
+                    }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 1, (t4 & 1) != 0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 2, (t4 & 2) != 0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                hv[i] = __floats2half2_rn(__fmul_rn(f[2 * i], qwc_inv_sqrt32()), __fmul_rn(f[2 * i + 1], qwc_inv_sqrt32()));
+            raw = make_uint4(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[1]),
+                             *reinterpret_cast<uint32_t*>(&hv[2]), *reinterpret_cast<uint32_t*>(&hv[3]));
+        }
+        if (live) *reinterpret_cast<uint4*>(xs + pr * h + u * 32 + 8 * t4) = raw;
     }
 }
 
@@ -322,9 +375,11 @@ MoeScratch moe_layout(int64_t t, int64_t e, int64_t k, int64_t h, int64_t inter)
 
 extern "C" {
 
+int32_t qwc_moe_tile_rows(int64_t pairs, int64_t e) { return moe_tile_rows(pairs, e > 0 ? e : 1); }
+
 int64_t qwc_moe_max_tiles(int64_t pairs, int64_t e, int64_t rows_per_expert) {
-    // sum over experts of ceil(cnt / 256) <= min(pairs, e + pairs / 256)
-    int64_t tx = e + pairs / kTileX;
+    // sum over experts of ceil(cnt / tile rows) <= min(pairs, e + pairs / tile rows)
+    int64_t tx = e + pairs / moe_tile_rows(pairs, e);
     if (tx > pairs) tx = pairs;
     return tx * ((rows_per_expert + kTileW - 1) / kTileW);
 }
@@ -359,12 +414,12 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // expert_off doubles as the count buffer of pass 1; the plan kernel reads all counts before it writes offsets
     const int warps = static_cast<int>(e) + 1;
-    qwc_moe_count_kernel<<<(warps + 7) / 8, 256, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e), expert_off, inv_perm);
+    qwc_moe_count_kernel<<<(warps + 15) / 16, 512, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e), expert_off, inv_perm);
     QWC_CUDA_TRY(cudaGetLastError());
-    qwc_moe_plan_kernel<<<1, 512, 0, st>>>(expert_off, static_cast<int>(e), expert_off, static_cast<int>(gu_rows),
+    qwc_moe_plan_kernel<<<1, 512, 0, st>>>(expert_off, static_cast<int>(e), moe_tile_rows(pairs, e), expert_off, static_cast<int>(gu_rows),
                                            static_cast<int>(dn_rows), tiles_gu, tiles_dn, tile_counts);
     QWC_CUDA_TRY(cudaGetLastError());
-    qwc_moe_place_kernel<<<(static_cast<int>(e) + 7) / 8, 256, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e),
+    qwc_moe_place_kernel<<<(static_cast<int>(e) + 15) / 16, 512, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e),
                                                                        static_cast<int>(k), expert_off, sorted_pair, sorted_tok, inv_perm);
     QWC_CUDA_TRY(cudaGetLastError());
     return QWC_OK;
@@ -378,17 +433,21 @@ int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t l
     if (ldx < h) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldx < hidden");
     if (pairs == 0) return QWC_OK;
     if (!x_f16 || !sorted_tok || !expert_off || !xs_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
-    qwc_moe_gather_kernel<<<grid_for(hal, pairs * (h / 32), 8, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), sorted_tok, expert_off, static_cast<int>(e), !x_is_rotated,
+    const int vec = reinterpret_cast<uintptr_t>(x_f16) % 16 == 0 && ldx % 8 == 0;
+    if (reinterpret_cast<uintptr_t>(xs_f16) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "xs must be 16-byte aligned");
+    qwc_moe_gather_kernel<<<grid_for(hal, pairs * (h / 32), 64, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), sorted_tok, expert_off, static_cast<int>(e), !x_is_rotated, vec,
         static_cast<__half*>(xs_f16));
     QWC_CUDA_TRY(cudaGetLastError());
     return QWC_OK;
 }
 
 int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank, const void* xs_f16, int64_t pairs,
-                         const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, void* y, int32_t y_dtype,
-                         int64_t ldy) {
+                         const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, int32_t x_tile_rows, void* y,
+                         int32_t y_dtype, int64_t ldy) {
     qwc_clear_error();
+    if (x_tile_rows != 64 && x_tile_rows != 192 && x_tile_rows != 256)
+        return qwc_fail(QWC_ERR_BAD_GEOMETRY, "x_tile_rows must be 64, 192 or 256 (qwc_moe_tile_rows)");
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
     if (!bank || !bank->blocks) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "bank is null");
     if (pairs <= 0 || max_tiles <= 0) return QWC_OK;
@@ -399,7 +458,7 @@ int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view*
         return qwc_fail(QWC_ERR_BLOCKED, "grouped expert GEMM needs an HQ4_G32_M5 / HQ8_G32 bank with k %% 128 == 0, 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(xs_f16) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "xs must be 16-byte aligned");
     return qwc_launch_gemm_tc_grouped(hal, static_cast<cudaStream_t>(stream), bank, xs_f16, pairs, tiles, tile_count, max_tiles, y,
-                                      y_dtype, ldy);
+                                      y_dtype, ldy, x_tile_rows);
 }
 
 int qwc_moe_silu_mul(qwc_hal* hal, qwc_stream stream, const void* gu_f16, int64_t rows, int64_t inter, int32_t rotate,
@@ -477,11 +536,12 @@ int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank
     if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h,
                                   tiles_gu, tiles_dn, tile_counts))) return rc;
     if ((rc = qwc_moe_gather(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs))) return rc;
+    const int32_t xrows = qwc_moe_tile_rows(pairs, e);
     if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_gu, sc + L.xs, pairs, tiles_gu, tile_counts, qwc_moe_max_tiles(pairs, e, 2 * inter),
-                                   sc + L.gu, QWC_F16, 2 * inter))) return rc;
+                                   xrows, sc + L.gu, QWC_F16, 2 * inter))) return rc;
     if ((rc = qwc_moe_silu_mul(hal, stream, sc + L.gu, pairs, inter, 1, sc + L.hs))) return rc;
     if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_dn, sc + L.hs, pairs, tiles_dn, tile_counts + 1, qwc_moe_max_tiles(pairs, e, h),
-                                   sc + L.dn, QWC_F16, h))) return rc;
+                                   xrows, sc + L.dn, QWC_F16, h))) return rc;
     return qwc_moe_combine(hal, stream, sc + L.dn, QWC_F16, inv_perm, wts, t, k, h, out, out_dtype);
 }
 

@@ -24,7 +24,8 @@ _lib.register("qwc_moe_route", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _
 _lib.register("qwc_moe_group_pairs", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp])
 _lib.register("qwc_moe_max_tiles", _i64, [_i64, _i64, _i64])
 _lib.register("qwc_moe_gather", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _i64, _i32, _vp])
-_lib.register("qwc_moe_grouped_gemm", ctypes.c_int, [_vp, _vp, _WV, _vp, _i64, _vp, _vp, _i64, _vp, _i32, _i64])
+_lib.register("qwc_moe_grouped_gemm", ctypes.c_int, [_vp, _vp, _WV, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _i32, _i64])
+_lib.register("qwc_moe_tile_rows", _i32, [_i64, _i64])
 _lib.register("qwc_moe_silu_mul", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i32, _vp])
 _lib.register("qwc_moe_combine", ctypes.c_int, [_vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _vp, _i32])
 _lib.register("qwc_moe_forward", ctypes.c_int, [_vp, _vp, _WV, _WV, _i64, _i64, _vp, _i64, _i64, _i32, _vp, _i64, _i32,

@@ -233,12 +233,12 @@ class EPMoE:
                                       loff.data_ptr(), self.per, r, 1, xg.data_ptr()))
             gu = torch.empty((r, 2 * inter), dtype=torch.float16, device=dev)
             _check(lib.qwc_moe_grouped_gemm(hal.handle, _stream_ptr(None), ctypes.byref(self.bank_gu.c), xg.data_ptr(), r,
-                                            tg.data_ptr(), tc.data_ptr(), tg.shape[0], gu.data_ptr(), 0, 2 * inter))
+                                            tg.data_ptr(), tc.data_ptr(), tg.shape[0], lib.qwc_moe_tile_rows(r, self.per), gu.data_ptr(), 0, 2 * inter))
             hs = torch.empty((r, inter), dtype=torch.float16, device=dev)
             _check(lib.qwc_moe_silu_mul(hal.handle, _stream_ptr(None), gu.data_ptr(), r, inter, 1, hs.data_ptr()))
             dn = torch.empty((r, h), dtype=torch.float16, device=dev)
             _check(lib.qwc_moe_grouped_gemm(hal.handle, _stream_ptr(None), ctypes.byref(self.bank_dn.c), hs.data_ptr(), r,
-                                            td.data_ptr(), tc[1:].data_ptr(), td.shape[0], dn.data_ptr(), 0, h))
+                                            td.data_ptr(), tc[1:].data_ptr(), td.shape[0], lib.qwc_moe_tile_rows(r, self.per), dn.data_ptr(), 0, h))
             ones = torch.ones((r, 1), dtype=torch.float32, device=dev)
             QWGemmMoE.encodeMoECombine(hal, dn, linv, ones, out_rows[:r])
         back = ep_return(out_rows[:r], plan, self.group)

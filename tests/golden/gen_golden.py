@@ -40,7 +40,7 @@ sys.path.insert(0, str(ROOT))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("QW_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("QW_REFERENCE", os.path.join(os.path.dirname(str(ROOT)), "reference")))
     args = ap.parse_args()
     ref = Path(args.reference)
     sys.path.insert(0, str(ref / "Scripts" / "quantize"))

@@ -60,7 +60,8 @@ def test_group_pairs_matches_the_oracle(hal, oracle, t, e, k):
     # tile plan: every expert's rows are covered exactly once per 128-row weight tile
     counts = tc.cpu().numpy()
     tiles = tg.cpu().numpy()[: counts[0]]
-    assert counts[0] == sum(-(-int(c) // 256) for c in np.diff(roff)) * 8
+    xt = 192
+    assert counts[0] == sum(-(-int(c) // xt) for c in np.diff(roff)) * 8
     cover = np.zeros(valid, dtype=np.int32)
     for w0, wr, x0, xr, y0, ex, _, _ in tiles:
         assert wr == 128 and w0 == ex * 1024 + y0 and roff[ex] <= x0 and x0 + xr <= roff[ex + 1]
