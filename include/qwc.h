@@ -83,6 +83,13 @@ const char* qwc_last_error(void);
  * gave up (the CUDA stand-in for MTLCommandBuffer.error, Sources/Runtime/QWEngine/Driver/DriverDecode.swift:142-158). */
 int qwc_hal_device_status(qwc_hal* hal, int32_t* status_out);
 int qwc_sm_count(const qwc_hal* hal);
+/* The reference loads its weight planes once and never writes them again (Sources/Foundation/QWLoad/PlaneIO.swift:64-198;
+ * the decode loop only reads QWWeightView banks).  A caller that keeps that discipline can say so: with enabled != 0
+ * the decode / verify kernels are launched with programmatic stream serialization and start streaming their packed
+ * weights while the previous kernel of the stream is still finishing; activations, outputs and scratch are still
+ * touched only after the previous work has completed.  Leave it off (the default) if a weight bank may still be
+ * written by work in flight on the same stream when a matmul door is called (e.g. quantize-then-multiply). */
+int qwc_hal_set_static_weights(qwc_hal* hal, int32_t enabled);
 
 /* ---- weights -------------------------------------------------------------- */
 /* QWWeightView.init? (QWWeightView.swift:108-152): fills *view or refuses (k % group, bank too short, unknown kind). */

@@ -37,6 +37,7 @@ SIGNATURES = {
     "qwc_last_error": (ctypes.c_char_p, []),
     "qwc_hal_device_status": (ctypes.c_int, [_vp, ctypes.POINTER(_i32)]),
     "qwc_sm_count": (ctypes.c_int, [_vp]),
+    "qwc_hal_set_static_weights": (ctypes.c_int, [_vp, _i32]),
     "qwc_weight_view_init": (ctypes.c_int, [_WV, _vp, _sz, _i64, _i64, _i32, _i32, _i32]),
     "qwc_block_bytes": (_i64, [_i32, _i32, _i32]),
     "qwc_gemm_plan": (ctypes.c_int, [_i64, _i64, _i64, _i32, _i32, _i32, _i32, _i64, ctypes.POINTER(PlanC)]),

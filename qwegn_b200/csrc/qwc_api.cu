@@ -53,6 +53,7 @@ int qwc_hal_create(int device, qwc_hal** out) {
     h->sm_count = prop.multiProcessorCount;
     h->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
     h->encode_tiled = nullptr;
+    h->static_weights = 0;
     {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -86,6 +87,13 @@ int qwc_hal_device_status(qwc_hal* hal, int32_t* status_out) {
 }
 
 int qwc_sm_count(const qwc_hal* hal) { return hal ? hal->sm_count : 0; }
+
+int qwc_hal_set_static_weights(qwc_hal* hal, int32_t enabled) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    hal->static_weights = enabled != 0;
+    return QWC_OK;
+}
 
 int64_t qwc_block_bytes(int32_t kind, int32_t bits, int32_t group) {
     if (kind == QWC_KIND_HQ4_G32_M5) return 20;

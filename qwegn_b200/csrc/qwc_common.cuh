@@ -13,6 +13,7 @@ struct qwc_hal {
     int max_smem_optin;
     int32_t* status;  // device: [0] first error code written by a kernel, [1] detail
     void* encode_tiled;  // driver entry point cuTensorMapEncodeTiled (null if unavailable)
+    int static_weights;  // the caller promised that weight banks are never written by in-flight work (see qwc_hal_set_static_weights)
 };
 
 // Error reporting (thread-local message, status code returned).

@@ -69,6 +69,7 @@ struct GemvParams {
     int red_bytes;    // smem bytes of the team reduction region
     uint32_t sh4, sh8, sh12;  // 2^28, 2^24, 2^20: mul.hi by these is a right shift by 4, 8, 12
     int dbg_skip;     // experiment: consumers skip the math
+    int pdl;          // launched with programmatic stream serialization: weights prefetch before the dependency wait
     int use_tmap;     // full 16-row tiles arrive by one 2-D tensor copy instead of 16 row copies
 };
 
@@ -206,6 +207,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         return static_cast<int64_t>(out0) + (up ? p.n_out : 0);
     };
 
+    if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (warp == kConsumerWarps) {
         // ------------------------------ producer warp ------------------------------
         uint32_t q = 0;
@@ -270,6 +272,10 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         return;
     }
 
+    // Under programmatic dependent launch this grid may have started before the previous grid of the stream finished:
+    // everything the previous grid may have produced (activations, outputs, the K-slice scratch) is touched only after
+    // this point.  The producer warp above does not wait: packed weights are load-time data.
+    if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     // ---------------- consumers: stage the rotated activations once per CTA ----------------
     // A quad handles one (token, unit): lane t holds elements 8t..8t+7, rotates them with three in-lane butterfly
     // stages and two xor-shuffle stages (the reference's h = 1, 2, 4, 8, 16 order), and writes one 16-byte chunk.
@@ -659,6 +665,20 @@ int launch_stream_inst(const qwc_hal* hal, cudaStream_t st, const GemvParams& p,
                                           kSmemBudget));
         configured[hal->device & 63] = true;
     }
+    if (p.pdl) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem_bytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        QWC_CUDA_TRY(cudaLaunchKernelEx(&cfg, qwc_gemv_stream_kernel<FMT, NT, SUB>, p, tmap));
+        return QWC_OK;
+    }
     qwc_gemv_stream_kernel<FMT, NT, SUB><<<grid, kThreads, smem_bytes, st>>>(p, tmap);
     QWC_CUDA_TRY(cudaGetLastError());
     return QWC_OK;
@@ -795,6 +815,7 @@ int qwc_launch_gemv(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* 
     p.x_is_rotated = x_is_rotated;
     p.row_quantum = epilogue == QWC_EPI_SILU_PAIR_FWHT ? 32 : 1;
     p.dbg_skip = getenv("QWC_DBG_SKIP") != nullptr;
+    p.pdl = hal->static_weights;
     p.sh4 = 1u << 28;
     p.sh8 = 1u << 24;
     p.sh12 = 1u << 20;

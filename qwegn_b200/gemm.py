@@ -83,6 +83,11 @@ class QWHal:
     def sm_count(self) -> int:
         return int(self._lib.qwc_sm_count(self._h))
 
+    def set_static_weights(self, enabled: bool = True) -> None:
+        """Promise that weight banks are load-time data (never written by in-flight work): the decode kernels then
+        prefetch their weights while the previous kernel of the stream is finishing."""
+        _check(self._lib.qwc_hal_set_static_weights(self._h, int(enabled)))
+
     def device_status(self) -> int:
         """Synchronise and return the kernels' status word (0 = no bounded wait gave up)."""
         out = ctypes.c_int32(0)

@@ -217,3 +217,30 @@ def test_k_sliced_call_needs_and_uses_the_workspace(hal, oracle):
     href = oracle.swiglu_f16(oracle.matmul(gu, fmt, x), rotate=True).astype(np.float32)
     assert_matmul_close(_run(q, hal, _bank(q, gu, "HQ4_G32"), x, epi=q.EPI_SILU_PAIR_FWHT, out_dtype=torch.float16),
                         href, tight=4e-3)
+
+
+def test_static_weights_mode_gives_identical_results(oracle):
+    # qwc_hal_set_static_weights: the kernels prefetch weights before the previous kernel of the stream has
+    # finished; results must not change, including for back-to-back dependent calls (y of one call is x of the next).
+    import qwegn_b200 as q
+    hal2 = q.QWHal(0)
+    n, k = 1024, 1024
+    fmt = oracle.HQ4_G32
+    rng = np.random.default_rng(31)
+    blocks = oracle.quantize(rng.normal(0.0, 0.03, (n, k)).astype(np.float32), fmt)
+    view = _bank(q, blocks, "HQ4_G32")
+    x = torch.from_numpy(rng.standard_normal((1, k)).astype(np.float16)).cuda()
+    outs = []
+    for mode in (False, True):
+        torch.cuda.synchronize()
+        hal2.set_static_weights(mode)
+        a = x.clone()
+        for _ in range(6):   # a chain: each call consumes the previous call's output
+            y = torch.empty((1, n), dtype=torch.float16, device="cuda")
+            q.QWGemm.encode(hal2, view, a, y)
+            a = y
+        torch.cuda.synchronize()
+        outs.append(a.float().cpu().numpy())
+    assert np.array_equal(outs[0], outs[1])
+    assert hal2.device_status() == 0
+    hal2.close()
