@@ -58,7 +58,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -68,6 +68,9 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
+
+    def count(self):
+        return len(self.lines)
 
     def stop(self):
         if self.proc is None:
@@ -144,16 +147,45 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------------------------
-def time_region(fn, steps, dist, stream):
-    """Barrier + synchronize on both sides, CUDA events on the launching stream, max over ranks (ms)."""
+GRAPH_STEPS = 500   # calls per captured graph; a timed region of K steps replays it K // 500 times (+ one graph of K % 500)
+
+
+def time_region(fn, steps, dist, stream, graph=False):
+    """Barrier + synchronize on both sides, CUDA events on the launching stream, max over ranks (ms).
+
+    graph=True captures the calls in CUDA graphs (the way a decode loop submits its kernels) and replays them inside
+    the timed region, so the host's per-call cost (ctypes + launch, ~15 us from Python) is not what is measured.
+    Exactly `steps` calls run between the events; one untimed replay of each graph precedes the timed region."""
     import torch
+    plan = []   # (graph, replays)
+    if graph:
+        side = torch.cuda.Stream()
+        done = 0
+        for size, reps in ((GRAPH_STEPS, steps // GRAPH_STEPS), (steps % GRAPH_STEPS, 1)):
+            if size == 0 or reps == 0:
+                continue
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    for i in range(size):
+                        fn(done + i)
+            torch.cuda.synchronize()
+            g.replay()
+            plan.append((g, reps))
+            done += size
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for i in range(steps):
-        fn(i)
+    if graph:
+        for g, reps in plan:
+            for _ in range(reps):
+                g.replay()
+    else:
+        for i in range(steps):
+            fn(i)
     e1.record(stream)
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
@@ -199,7 +231,7 @@ def bench_gemv_point(q, hal, n, k, m, cname, steps, warmup, dist=None, seed=0):
     hal.set_static_weights(True)
     for i in range(warmup):
         step(i)
-    ms = time_region(step, steps, dist, stream)
+    ms = time_region(step, steps, dist, stream, graph=True)
     hal.set_static_weights(False)
     nbytes = gemv_bytes(n, k, m, cont.block_bytes, cont.group)
     return ms / steps, nbytes, banks, x, y
@@ -240,11 +272,10 @@ def run_ours(args):
 
     torch.cuda.synchronize()
     hal.set_static_weights(True)   # the banks are complete: from here on weights are load-time data, as in a decode loop
+    sampler.start()                # samples SM clocks and throttle reasons from here to the end of the e2e region
     for i in range(args.warmup):
         step(i)
-    sampler.start()
-    ms = time_region(step, args.steps, dist, stream)
-    clocks = sampler.stop()
+    ms = time_region(step, args.steps, dist, stream, graph=True)
     nbytes = gemv_bytes(n, k, m)
     ms_per_step = ms / args.steps
     value = world * nbytes / (ms_per_step * 1e-3) / 1e9
@@ -264,6 +295,14 @@ def run_ours(args):
         step_e2e(i)
     ms_e2e = time_region(step_e2e, args.steps, dist, stream)
     e2e_val = world * nbytes / (ms_e2e / args.steps * 1e-3) / 1e9
+    if sampler.count() < 5:
+        # a short run (small --steps) ends before nvidia-smi has sampled: keep the same load up, untimed, for ~0.3 s
+        t_end = time.perf_counter() + 0.3
+        while time.perf_counter() < t_end:
+            for i in range(200):
+                step(i)
+            torch.cuda.synchronize()
+    clocks = sampler.stop()
 
     status = hal.device_status()
     line = {
@@ -272,7 +311,7 @@ def run_ours(args):
         "dtype": "f16 (f16 weights decoded from u4, f16 activations, f32 accumulate)", "data": "synthetic",
         "config": {"workload": WORKLOAD["name"], "n": n, "k": k, "m": m, "format": "HQ4_G32",
                    "l2": f"rotation over {copies} distinct weight banks ({copies * per_bank / 1e6:.0f} MB > 126 MB L2)",
-                   "launch": "static-weights mode: kernels launched with programmatic stream serialization (weights prefetch under the previous kernel's tail)",
+                   "launch": "the K calls are captured in CUDA graphs of <= 500 calls and replayed inside the timed region; static-weights mode: programmatic dependent launch between calls (weights prefetch under the previous kernel's tail)",
                    "parallelism": "one replica of the projection per GPU (column-parallel shards, no collective)" if world > 1 else "1 GPU"},
         "clocks": clocks,
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel() * 2),
@@ -464,7 +503,7 @@ def cpu_baseline(q, hal, n, k, m):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sections", default="", help="comma list of extra sections at N=1: sweep,c1,cpu")

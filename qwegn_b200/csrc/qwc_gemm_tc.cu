@@ -40,7 +40,6 @@ constexpr int kFirstConvWarp = 3;   // warps 0, 1, 2: activation TMA, MMA issue,
 constexpr int kWarps = kFirstConvWarp + kConvWarps + kEpiWarps;
 constexpr int kTcThreads = kWarps * 32;
 constexpr int kWTileBytes = kBM * kBK * 2;   // 16 KB
-constexpr int kXTileBytes = kBN * kBK * 2;   // 32 KB
 constexpr int kStages = 4;    // operand stages (one decoded weight tile + one activation tile each)
 constexpr int kMaxRaw = 4;    // raw (packed weight) stages
 
@@ -201,6 +200,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     uint64_t* acc_empty = acc_full + 2;          // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint32_t* raw_issued = tmem_slot + 2;   // raw steps the weight producer has started
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -217,6 +217,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
             mbar_init(&acc_empty[s], kEpiWarps);
         }
         *abort_flag = 0;
+        *raw_issued = 0;
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -301,6 +302,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                     }
                     mbar_arrive_expect_tx(&raw_full[s], static_cast<uint32_t>(kBM * p.raw_row_bytes));
                     tma_load_2d(raw + s * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[s]);
+                    asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(raw_issued)), "r"(r + 1) : "memory");
                 }
             }
         }
@@ -354,7 +356,20 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                 if (static_cast<int>(r % kConvGroups) != grp) continue;
                 const uint32_t rslot = r % p.raw_stages, rpar = (r / p.raw_stages) & 1u;
                 const uint32_t use = r / kConvGroups;   // how often this group has filled its stages before
-                if (!mbar_wait(&raw_full[rslot], rpar) ||
+                // With an odd ring depth successive phases of a raw slot go to different groups, and a parity wait
+                // cannot tell phase k from phase k - 2: wait first until the producer has started step r (which it
+                // does only after phase k - 1 was consumed); from then on the parity wait is exact.
+                bool started = false;
+                for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(raw_issued)) : "memory");
+                    if (v > r) {
+                        started = true;
+                        break;
+                    }
+                    __nanosleep(spin < 64 ? 20 : 200);
+                }
+                if (!started || !mbar_wait(&raw_full[rslot], rpar) ||
                     (use > 0 && (!mbar_wait(&empty[s0], (use - 1) & 1u) || !mbar_wait(&empty[s1], (use - 1) & 1u)))) {
                     if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
                     ok = false;

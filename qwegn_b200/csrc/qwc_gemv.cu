@@ -20,6 +20,7 @@
 //    is needed between the packed layout and the fragment layout.
 #include <cuda.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -65,18 +66,32 @@ struct GemvParams {
     int acc_in;       // add `partial` before the epilogue
     int acc_out;      // store raw sums to `partial` instead of y
     int row_quantum;  // CTA row ranges start on multiples of this (32 for the fused-FWHT epilogue)
+    int q_lo, q_rem;  // (n_out / row_quantum) / grid and % grid: how the row quanta are dealt to the CTAs
     int x_bytes;      // smem bytes of the activation region
     int red_bytes;    // smem bytes of the team reduction region
-    uint32_t sh4, sh8, sh12;  // 2^28, 2^24, 2^20: mul.hi by these is a right shift by 4, 8, 12
-    int dbg_skip;     // experiment: consumers skip the math
     int pdl;          // launched with programmatic stream serialization: weights prefetch before the dependency wait
     int use_tmap;     // full 16-row tiles arrive by one 2-D tensor copy instead of 16 row copies
 };
 
-__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+// Shared-memory loads by 32-bit shared-window address (no 64-bit pointer arithmetic in the inner loop).
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
 
 __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, __half2 s2, __half2 b2) {
     const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), s2, b2);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t hfma2_k(uint32_t a, uint32_t mul, uint32_t add) {
+    const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&mul),
+                              *reinterpret_cast<const __half2*>(&add));
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 __device__ __forceinline__ uint32_t hsub2_1024(uint32_t a) {
@@ -84,52 +99,56 @@ __device__ __forceinline__ uint32_t hsub2_1024(uint32_t a) {
     const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&k));
     return *reinterpret_cast<const uint32_t*>(&r);
 }
+// (v & mask) | 0x64006400 as one three-input logic op.  With mask 0x000F000F the two nibbles become the f16 pair
+// (1024 + q, 1024 + q'); with mask 0x00F000F0 the nibbles four bits up become (1024 + 16 q, 1024 + 16 q').
+template <uint32_t MASK> __device__ __forceinline__ uint32_t nib2_f16x2(uint32_t v) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(v), "r"(MASK), "r"(0x64006400u));
+    return d;
+}
+constexpr uint32_t kH2Sixteenth = 0x2C002C00u;   // f16x2 (1/16, 1/16)
+constexpr uint32_t kH2_960 = 0x63806380u;        // f16x2 (960, 960)
+constexpr uint32_t kH2_m64 = 0xD400D400u;        // f16x2 (-64, -64)
 
 // Decode one whole unit (32 k of one row) into 16 f16x2 registers a[P], P = pair index.  The k each pair holds
 // is fixed per format (natural order for HQ4_G32_M5 / HQ8_G32; (8w+p, 8w+p+4) for the linear-nibble HQ4_G64) and
-// the activation staging writes x in the same order.  ublk = address of the unit's header word in shared memory;
-// wofs = byte offset of the unit's first payload word from the header.
+// the activation staging writes x in the same order.  ublk = shared address of the unit's header word; wofs =
+// byte offset of the unit's first payload word from the header.
 //
-// The integer/logic pipe is the scarce resource of this kernel, so the nibble shifts v >> 4, 8, 12 are computed
-// as mul.hi(v, 2^28 / 2^24 / 2^20) on the FMA pipe; sh = {2^28, 2^24, 2^20} arrives as kernel parameters so the
-// compiler cannot turn the multiplies back into shifts.
-__device__ __forceinline__ uint32_t shr_fma(uint32_t v, uint32_t pow2) { return __umulhi(v, pow2); }
-// (v & 0x000F000F) | 0x64006400 as one three-input logic op: two nibbles -> the f16 pair (1024 + q, 1024 + q').
-__device__ __forceinline__ uint32_t nib2_f16x2(uint32_t v) {
-    uint32_t d;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(v), "r"(0x000F000Fu), "r"(0x64006400u));
-    return d;
-}
-
+// The integer/logic pipe is the scarce resource of this kernel (it runs at half the rate of the FMA pipe), so only
+// one shift per word is spent there: the nibbles at bits 4..7 of a byte are taken in place as 1024 + 16 q and brought
+// to 1024 + q by an exact f16 FMA (x / 16 + 960), which leaves every decoded weight bit-identical to the one-FMA
+// form (1024 + q) * scale + bias of the reference (Sources/QWMetal/include/qw_dequant.metalh:53-61).
 template <int FMT>
-__device__ __forceinline__ void decode_unit(const uint8_t* ublk, int wofs, const uint32_t sh[3], uint32_t a[16]) {
+__device__ __forceinline__ void decode_unit(uint32_t ublk, int wofs, uint32_t a[16]) {
     const uint32_t hdr = lds32(ublk);
     const __half2 h = *reinterpret_cast<const __half2*>(&hdr);
     const __half2 s2 = __half2half2(__low2half(h)), b2 = __half2half2(__high2half(h));
+    const uint32_t pay = ublk + wofs;
     if (FMT == FMT_HQ4_G32_M5) {
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const uint32_t v = lds32(ublk + wofs + 4 * w);
-            a[4 * w] = hfma2_u32(nib2_f16x2(v), s2, b2);
-#pragma unroll
-            for (int i = 1; i < 4; ++i)
-                a[4 * w + i] = hfma2_u32(nib2_f16x2(v >> (4 * i)), s2, b2);
+            const uint32_t v = lds32(pay + 4 * w), v8 = v >> 8;
+            a[4 * w] = hfma2_u32(nib2_f16x2<0x000F000Fu>(v), s2, b2);
+            a[4 * w + 1] = hfma2_u32(hfma2_k(nib2_f16x2<0x00F000F0u>(v), kH2Sixteenth, kH2_960), s2, b2);
+            a[4 * w + 2] = hfma2_u32(nib2_f16x2<0x000F000Fu>(v8), s2, b2);
+            a[4 * w + 3] = hfma2_u32(hfma2_k(nib2_f16x2<0x00F000F0u>(v8), kH2Sixteenth, kH2_960), s2, b2);
         }
     } else if (FMT == FMT_HQ8_G32) {
 #pragma unroll
         for (int w = 0; w < 8; ++w) {
-            const uint32_t v = lds32(ublk + wofs + 4 * w);
+            const uint32_t v = lds32(pay + 4 * w);
             a[2 * w] = hfma2_u32(hsub2_1024(__byte_perm(v, 0x64646464u, 0x4140)), s2, b2);
             a[2 * w + 1] = hfma2_u32(hsub2_1024(__byte_perm(v, 0x64646464u, 0x4342)), s2, b2);
         }
     } else {
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const uint32_t v = lds32(ublk + wofs + 4 * w);
-            a[4 * w] = hfma2_u32(hsub2_1024(nib2_f16x2(v)), s2, b2);
-#pragma unroll
-            for (int i = 1; i < 4; ++i)
-                a[4 * w + i] = hfma2_u32(hsub2_1024(nib2_f16x2(v >> (4 * i))), s2, b2);
+            const uint32_t v = lds32(pay + 4 * w), v8 = v >> 8;
+            a[4 * w] = hfma2_u32(hsub2_1024(nib2_f16x2<0x000F000Fu>(v)), s2, b2);
+            a[4 * w + 1] = hfma2_u32(hfma2_k(nib2_f16x2<0x00F000F0u>(v), kH2Sixteenth, kH2_m64), s2, b2);
+            a[4 * w + 2] = hfma2_u32(hsub2_1024(nib2_f16x2<0x000F000Fu>(v8)), s2, b2);
+            a[4 * w + 3] = hfma2_u32(hfma2_k(nib2_f16x2<0x00F000F0u>(v8), kH2Sixteenth, kH2_m64), s2, b2);
         }
     }
 }
@@ -150,6 +169,16 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
             smem_u32(dst)),
         "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
+}
+
+// Release store / acquire load of a shared-memory word (CTA scope).
+__device__ __forceinline__ void st_release_cta(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_cta(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+    return v;
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
@@ -174,26 +203,35 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.x_bytes + p.red_bytes);
     uint64_t* empty = full + kMaxStages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMaxStages);
+    uint32_t* issued = reinterpret_cast<uint32_t*>(empty + kMaxStages) + 1;   // fills the producer has started
     uint8_t* stage0 = smem + p.x_bytes + p.red_bytes + kBarrierBytes;  // 128-byte aligned
     const int stage_bytes = kTileRows * p.stride;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int W = p.team_warps, T = kConsumerWarps / W;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], W);
+    // The producer warp initialises the barriers and goes straight on to fill the ring; the consumers meet it at
+    // named barrier 10 only after they have staged the activations, so nobody waits for anybody at kernel start.
+    if (warp == kConsumerWarps) {
+        if (lane < p.stages) {
+            mbar_init(&full[lane], 1);
+            mbar_init(&empty[lane], W);
         }
-        *abort_flag = 0;
+        if (lane == 0) {
+            *abort_flag = 0;
+            *issued = 0;
+            if (p.use_tmap) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
+        }
         fence_barrier_init();
+        __syncwarp();
+        asm volatile("bar.arrive 10, %0;" ::"r"(kThreads) : "memory");
     }
-    __syncthreads();
 
     // This CTA's output rows [rb, re) and its jobs: one job = 16 output rows (32 for the fused-FWHT epilogue) =
-    // SUB weight sub-tiles of 16 rows.  Job i goes to team i % T in round i / T.
-    const int quanta = p.n_out / p.row_quantum;
-    const int rb = static_cast<int>((static_cast<int64_t>(quanta) * blockIdx.x) / gridDim.x) * p.row_quantum;
-    const int re = static_cast<int>((static_cast<int64_t>(quanta) * (blockIdx.x + 1)) / gridDim.x) * p.row_quantum;
+    // SUB weight sub-tiles of 16 rows.  Job i goes to team i % T in round i / T.  The row quanta are dealt evenly,
+    // the first q_rem CTAs taking one more.
+    const int bq = static_cast<int>(blockIdx.x);
+    const int rb = (p.q_lo * bq + min(bq, p.q_rem)) * p.row_quantum;
+    const int re = rb + (p.q_lo + (bq < p.q_rem ? 1 : 0)) * p.row_quantum;
     constexpr int kJobRows = SUB == 4 ? 32 : 16;
     const int njobs = (re - rb + kJobRows - 1) / kJobRows;
     const int E = SUB * p.nchunks;  // stage fills per job
@@ -216,8 +254,11 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         bool ok = true;
         for (int r = 0; r < rounds && ok; ++r) {
             const int tl = min(T, njobs - r * T);
-            for (int e = 0; e < E && ok; ++e) {
-                const int sub = e / p.nchunks, c = e % p.nchunks;
+            for (int e = 0, sub = 0, c = 0; e < E && ok; ++e, ++c) {
+                if (c == p.nchunks) {
+                    c = 0;
+                    ++sub;
+                }
                 const int u0 = c * p.chunk_units;
                 const uint32_t cbytes = static_cast<uint32_t>(min(p.chunk_units, p.units - u0)) * C::kUnitBytes;
                 for (int tau = 0; tau < tl; ++tau, ++q) {
@@ -239,20 +280,27 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                     const int64_t wrow = first_weight_row(r * T + tau, sub, valid);
                     if (valid <= 0) {
                         // sub-tile past the CTA's rows (second half of a short FWHT job): nothing to copy
-                        if (lane == 0) mbar_arrive(&full[slot]);
+                        if (lane == 0) {
+                            mbar_arrive(&full[slot]);
+                            st_release_cta(issued, q + 1);
+                        }
                         continue;
                     }
                     if (p.use_tmap && valid == kTileRows) {
                         // one 2-D tensor copy per stage: 16 rows x (chunk + 16 pad bytes), rows land `stride` apart
                         if (lane == 0) {
                             mbar_arrive_expect_tx(&full[slot], static_cast<uint32_t>(stage_bytes));
+                            st_release_cta(issued, q + 1);
                             tma_load_2d(stage0 + slot * stage_bytes, &tmap,
                                         static_cast<int>((static_cast<int64_t>(p.unit0 + u0) * C::kUnitBytes) >> 3),
                                         static_cast<int>(wrow), &full[slot]);
                         }
                         continue;
                     }
-                    if (lane == 0) mbar_arrive_expect_tx(&full[slot], cbytes * valid);
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(&full[slot], cbytes * valid);
+                        st_release_cta(issued, q + 1);
+                    }
                     __syncwarp();
                     if (lane < valid) {
                         const uint8_t* src = p.blocks + (wrow + lane) * p.row_bytes +
@@ -272,90 +320,136 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         return;
     }
 
-    // Under programmatic dependent launch this grid may have started before the previous grid of the stream finished:
-    // everything the previous grid may have produced (activations, outputs, the K-slice scratch) is touched only after
-    // this point.  The producer warp above does not wait: packed weights are load-time data.
-    if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
-    // ---------------- consumers: stage the rotated activations once per CTA ----------------
-    // A quad handles one (token, unit): lane t holds elements 8t..8t+7, rotates them with three in-lane butterfly
-    // stages and two xor-shuffle stages (the reference's h = 1, 2, 4, 8, 16 order), and writes one 16-byte chunk.
-    {
-        const int t4 = lane & 3, sub8 = lane >> 2;
-        const int items = p.m * p.units;  // (token, unit) pairs
-        const bool vec_ok = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.ldx % 8 == 0);
-        for (int base = warp * 8; base < items; base += kConsumerWarps * 8) {
-            const int it = base + sub8;
-            const bool live = it < items;
-            const int tok = live ? it / p.units : 0, unit = live ? it % p.units : 0;
-            const __half* src = p.x + tok * p.ldx + static_cast<int64_t>(p.unit0 + unit) * 32 + 8 * t4;
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (live) {
-                if (vec_ok) raw = *reinterpret_cast<const uint4*>(src);
-                else {
-                    __half tmp[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) tmp[i] = src[i];
-                    raw = *reinterpret_cast<const uint4*>(tmp);
-                }
-            }
-            __half2 hv[4] = {*reinterpret_cast<__half2*>(&raw.x), *reinterpret_cast<__half2*>(&raw.y),
-                             *reinterpret_cast<__half2*>(&raw.z), *reinterpret_cast<__half2*>(&raw.w)};
-            if (!p.x_is_rotated) {
-                float f[8];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(hv[i]); f[2 * i + 1] = __high2float(hv[i]); }
-#pragma unroll
-                for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        if ((i & h) == 0) {
-                            const float u = f[i], v = f[i + h];
-                            f[i] = __fadd_rn(u, v);
-                            f[i + h] = __fsub_rn(u, v);
-                        }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 1, (t4 & 1) != 0);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 2, (t4 & 2) != 0);
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    hv[i] = __floats2half2_rn(__fmul_rn(f[2 * i], qwc_inv_sqrt32()), __fmul_rn(f[2 * i + 1], qwc_inv_sqrt32()));
-            }
-            if (live) {
-                uint4 outv;
-                if (FMT == FMT_HQ4_G64) {
-                    // slot order inside a chunk: e0 e4 e1 e5 e2 e6 e3 e7
-                    outv.x = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[2]), 0x5410);
-                    outv.y = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[2]), 0x7632);
-                    outv.z = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[1]), *reinterpret_cast<uint32_t*>(&hv[3]), 0x5410);
-                    outv.w = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[1]), *reinterpret_cast<uint32_t*>(&hv[3]), 0x7632);
-                } else {
-                    outv = make_uint4(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[1]),
-                                      *reinterpret_cast<uint32_t*>(&hv[2]), *reinterpret_cast<uint32_t*>(&hv[3]));
-                }
-                *reinterpret_cast<uint4*>(xs + x_offset<FMT>(tok, unit, t4, p.units)) = outv;
-            }
-        }
-    }
-    named_bar_sync(9, kConsumerWarps * 32);
-
+    // ---------------- consumers ----------------
+    // Everything that needs no global data is set up first: under programmatic dependent launch it runs while the
+    // previous grid of the stream is still finishing.
     const int gid = lane >> 2, t = lane & 3;
     const int team = warp / W, wj = warp % W;
     const int team_threads = W * 32;
-    bool ok = true;
-    const uint32_t sh[3] = {p.sh4, p.sh8, p.sh12};
+    const uint32_t xs_a = smem_u32(xs), stage0_a = smem_u32(stage0);
     // Per-lane constants of the activation fragment loads: the chunk swizzle depends only on (t, token parity)
     // because chunk starts and group starts are multiples of 4 units (8 for HQ4_G64).
-    const uint8_t* xtok[NT];
+    uint32_t xtok[NT];
     int xsw[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         const int tok = min(nt * 8 + gid, p.m - 1);
-        xtok[nt] = xs + static_cast<size_t>(tok) * p.units * 64;
+        xtok[nt] = xs_a + static_cast<uint32_t>(tok) * p.units * 64;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) xsw[nt][cc] = (cc ^ t ^ (tok & 1)) << 4;
     }
+    // this lane's unit inside a chunk for group wj (advances by W groups), as byte offsets into the row / x
+    int hofs0, wofs, xofs0;
+    if (FMT == FMT_HQ4_G64) {
+        const int ul = 8 * (wj >> 1) + (wj & 1) + 2 * t;  // even units, then odd units, of an 8-unit span
+        hofs0 = (ul >> 1) * 36;
+        wofs = 4 + 16 * (ul & 1);
+        xofs0 = ul * 64;
+    } else {
+        const int ul = 4 * wj + t;
+        hofs0 = ul * C::kUnitBytes;
+        wofs = 4;
+        xofs0 = ul * 64;
+    }
+    // HQ4_G64 with odd W would alternate the unit parity between steps; the host only picks W = 1 there when
+    // forced, and the general form in the loop handles it by recomputing the offsets per group.
+    const bool g64_recompute = FMT == FMT_HQ4_G64 && (W & 1);
+    const int hstep = FMT == FMT_HQ4_G64 ? (W >> 1) * 4 * 36 : W * 4 * C::kUnitBytes;  // W groups further along the row
+    const int xstep = W * 4 * 64;
+    const int row_ofs = gid * p.stride + hofs0, hi_ofs = 8 * p.stride;
 
+    // Staging of the rotated activations, once per CTA.  A quad handles one (token, unit): lane t holds elements
+    // 8t..8t+7, rotates them with three in-lane butterfly stages and two xor-shuffle stages (the reference's
+    // h = 1, 2, 4, 8, 16 order), and writes one 16-byte chunk.  Items are taken two at a time so that both global
+    // loads are in flight together.
+    const int t4 = lane & 3, sub8 = lane >> 2;
+    const int items = p.m * p.units;  // (token, unit) pairs
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.ldx % 8 == 0);
+    struct StageItem {
+        const __half* src;
+        int tok, unit;
+        bool live;
+    };
+    auto make_item = [&](int it) {
+        StageItem si;
+        si.live = it < items;
+        si.tok = si.live ? it / p.units : 0;
+        si.unit = si.live ? it - si.tok * p.units : 0;
+        si.src = p.x + si.tok * p.ldx + static_cast<int64_t>(p.unit0 + si.unit) * 32 + 8 * t4;
+        return si;
+    };
+    auto load_item = [&](const StageItem& si) {
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (si.live) {
+            if (vec_ok) raw = *reinterpret_cast<const uint4*>(si.src);
+            else {
+                __half tmp[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) tmp[i] = si.src[i];
+                raw = *reinterpret_cast<const uint4*>(tmp);
+            }
+        }
+        return raw;
+    };
+    auto finish_item = [&](const StageItem& si, uint4 raw) {
+        __half2 hv[4] = {*reinterpret_cast<__half2*>(&raw.x), *reinterpret_cast<__half2*>(&raw.y),
+                         *reinterpret_cast<__half2*>(&raw.z), *reinterpret_cast<__half2*>(&raw.w)};
+        if (!p.x_is_rotated) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(hv[i]); f[2 * i + 1] = __high2float(hv[i]); }
+#pragma unroll
+            for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if ((i & h) == 0) {
+                        const float u = f[i], v = f[i + h];
+                        f[i] = __fadd_rn(u, v);
+                        f[i + h] = __fsub_rn(u, v);
+                    }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 1, (t4 & 1) != 0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 2, (t4 & 2) != 0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                hv[i] = __floats2half2_rn(__fmul_rn(f[2 * i], qwc_inv_sqrt32()), __fmul_rn(f[2 * i + 1], qwc_inv_sqrt32()));
+        }
+        if (si.live) {
+            uint4 outv;
+            if (FMT == FMT_HQ4_G64) {
+                // slot order inside a chunk: e0 e4 e1 e5 e2 e6 e3 e7
+                outv.x = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[2]), 0x5410);
+                outv.y = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[2]), 0x7632);
+                outv.z = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[1]), *reinterpret_cast<uint32_t*>(&hv[3]), 0x5410);
+                outv.w = __byte_perm(*reinterpret_cast<uint32_t*>(&hv[1]), *reinterpret_cast<uint32_t*>(&hv[3]), 0x7632);
+            } else {
+                outv = make_uint4(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[1]),
+                                  *reinterpret_cast<uint32_t*>(&hv[2]), *reinterpret_cast<uint32_t*>(&hv[3]));
+            }
+            *reinterpret_cast<uint4*>(xs + x_offset<FMT>(si.tok, si.unit, t4, p.units)) = outv;
+        }
+    };
+    constexpr int kItemStride = kConsumerWarps * 8;
+    StageItem ia = make_item(warp * 8 + sub8), ib = make_item(warp * 8 + sub8 + kItemStride);
+
+    // Under programmatic dependent launch this grid may have started before the previous grid of the stream finished:
+    // everything the previous grid may have produced (activations, outputs, the K-slice scratch) is touched only after
+    // this point.  The producer warp above does not wait: packed weights are load-time data.
+    if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int base = warp * 8; base < items; base += 2 * kItemStride) {
+        const uint4 ra = load_item(ia), rb4 = load_item(ib);
+        const StageItem na = make_item(base + 2 * kItemStride + sub8), nb = make_item(base + 3 * kItemStride + sub8);
+        finish_item(ia, ra);
+        finish_item(ib, rb4);
+        ia = na;
+        ib = nb;
+    }
+    named_bar_sync(9, kConsumerWarps * 32);
+    named_bar_sync(10, kThreads);   // the producer arrived here after initialising the barriers
+
+    bool ok = true;
+    const int ET = E * T;
     for (int r = 0; r < rounds; ++r) {
         const int job = r * T + team;
         const int tl = min(T, njobs - r * T);
@@ -372,32 +466,29 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 
         // Ring position of this team's first fill of the job; it advances by tl (the teams active in this round)
         // per fill, so slot and phase parity are kept incrementally (no division in the loop).
-        const uint32_t q0 = static_cast<uint32_t>(r) * E * T + team;
-        int slot = q0 % p.stages;
-        uint32_t parity = (q0 / p.stages) & 1;
-        // this lane's unit inside a chunk for group wj (advances by W groups), as byte offsets into the row / x
-        int hofs0, wofs, xofs0;
-        if (FMT == FMT_HQ4_G64) {
-            const int ul = 8 * (wj >> 1) + (wj & 1) + 2 * t;  // even units, then odd units, of an 8-unit span
-            hofs0 = (ul >> 1) * 36;
-            wofs = 4 + 16 * (ul & 1);
-            xofs0 = ul * 64;
-        } else {
-            const int ul = 4 * wj + t;
-            hofs0 = ul * C::kUnitBytes;
-            wofs = 4;
-            xofs0 = ul * 64;
+        uint32_t qn = static_cast<uint32_t>(r) * ET + team;   // index of this team's next fill in the producer's order
+        int slot = team;
+        uint32_t parity = 0;
+        if (r > 0) {
+            slot = qn % p.stages;
+            parity = (qn / p.stages) & 1;
         }
-        // HQ4_G64 with odd W would alternate the unit parity between steps; the host only picks W = 1 there when
-        // forced, and the general form below handles it by recomputing the offsets per group.
-        const bool g64_recompute = FMT == FMT_HQ4_G64 && (W & 1);
-        const int hstep = FMT == FMT_HQ4_G64 ? (W >> 1) * 4 * 36 : W * 4 * C::kUnitBytes;  // W groups further along the row
-        const int xstep = W * 4 * 64;
 #pragma unroll
         for (int sub = 0; sub < SUB; ++sub) {
             for (int c = 0; c < p.nchunks; ++c) {
                 if (ok) {
-                    ok = mbar_wait(&full[slot], parity);
+                    // A slot is shared by teams: successive phases of full[slot] belong to different teams, and a parity
+                    // wait cannot tell phase k from phase k - 2.  So first wait until the producer has started fill qn
+                    // (it does that only after phase k - 1 of the slot was consumed); from then on the barrier is in
+                    // phase k or past it and the parity wait is exact.
+                    for (uint32_t spin = 0; ld_acquire_cta(issued) <= qn; ++spin) {
+                        if (spin > (1u << 22)) {
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(spin < 64 ? 20 : 200);
+                    }
+                    ok = ok && mbar_wait(&full[slot], parity);
                     if (!ok) {
                         *abort_flag = 1;
                         if (lane == 0) atomicCAS(p.status, 0, QWC_DEV_WAIT_FULL_TIMEOUT);
@@ -405,10 +496,9 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                 }
                 const int u0 = c * p.chunk_units;
                 const int cu = min(p.chunk_units, p.units - u0);
-                if (ok && !p.dbg_skip) {
-                    const uint8_t* row_lo = stage0 + slot * stage_bytes + gid * p.stride + hofs0;
-                    const uint8_t* row_hi = row_lo + 8 * p.stride;
-                    const uint8_t* xu[NT];
+                if (ok) {
+                    uint32_t row_lo = stage0_a + slot * stage_bytes + row_ofs;
+                    uint32_t xu[NT];
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) xu[nt] = xtok[nt] + u0 * 64 + xofs0;
                     const int ngroups = cu / C::kGroupUnits;
@@ -416,20 +506,19 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                         int wo = wofs;
                         if (g64_recompute) {
                             const int ul = 8 * (g >> 1) + (g & 1) + 2 * t;
-                            row_lo = stage0 + slot * stage_bytes + gid * p.stride + (ul >> 1) * 36;
-                            row_hi = row_lo + 8 * p.stride;
+                            row_lo = stage0_a + slot * stage_bytes + gid * p.stride + (ul >> 1) * 36;
                             wo = 4 + 16 * (ul & 1);
 #pragma unroll
                             for (int nt = 0; nt < NT; ++nt) xu[nt] = xtok[nt] + (u0 + ul) * 64;
                         }
                         uint32_t alo[16], ahi[16];
-                        decode_unit<FMT>(row_lo, wo, sh, alo);
-                        decode_unit<FMT>(row_hi, wo, sh, ahi);
+                        decode_unit<FMT>(row_lo, wo, alo);
+                        decode_unit<FMT>(row_lo + hi_ofs, wo, ahi);
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) {
                             uint4 xv[4];
 #pragma unroll
-                            for (int cc = 0; cc < 4; ++cc) xv[cc] = *reinterpret_cast<const uint4*>(xu[nt] + xsw[nt][cc]);
+                            for (int cc = 0; cc < 4; ++cc) xv[cc] = lds128(xu[nt] + xsw[nt][cc]);
                             const uint32_t* xp = reinterpret_cast<const uint32_t*>(xv);
 #pragma unroll
                             for (int s = 0; s < 8; ++s)
@@ -438,11 +527,11 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                             xu[nt] += xstep;
                         }
                         row_lo += hstep;
-                        row_hi += hstep;
                     }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[slot]);
+                qn += tl;
                 slot += tl;
                 if (slot >= p.stages) {
                     slot -= p.stages;
@@ -611,15 +700,17 @@ struct StreamGeom {
 constexpr int kXCapBytes = 112 * 1024;  // at most this much shared memory for the staged activations of a K slice
 
 // units: 32-element units of this launch's K slice; jobs: 16-row (32 for FWHT) jobs per CTA.  The team count T
-// follows the jobs a CTA has (teams work on different jobs concurrently), the chunk is the largest one that
-// still leaves the ring T + max(2, T/2) stages deep.  QWC_GEMV_W / QWC_GEMV_CHUNK override both (tuning knobs).
-// Returns false when no geometry fits.
+// follows the jobs a CTA has (teams work on different jobs concurrently); K is cut into the fewest equal chunks that
+// leave the ring T + 2 stages deep (measured: wide chunks beat a deep ring, equal chunks beat a short last one).
+// Chunks are multiples of 8 units: with the 16-byte row pad the smem row stride in words is then 4 mod 8, which
+// makes the per-lane word reads of 8 rows x 4 units hit 32 distinct banks (a multiple of 4 only gives 8-way
+// conflicts).  QWC_GEMV_W / QWC_GEMV_CHUNK override both (tuning knobs).  Returns false when no geometry fits.
 template <int FMT>
-bool plan_geometry(int units, int m, int nt, int sub, int jobs, StreamGeom* g) {
+bool plan_geometry(int units, int m, int nt, int sub, int jobs, int budget, StreamGeom* g) {
     using C = StreamCfg<FMT>;
-    const int quantum = FMT == FMT_HQ4_G64 ? 8 : 4;      // units per chunk must be a multiple of this
+    const int quantum = 8;      // units per chunk must be a multiple of this
     // chunk bytes + 16 pad <= 2048: the box of the 2-D tensor copy is at most 256 8-byte elements wide
-    const int max_chunk = FMT == FMT_HQ4_G32_M5 ? 100 : (FMT == FMT_HQ8_G32 ? 56 : 112);
+    const int max_chunk = FMT == FMT_HQ4_G32_M5 ? 96 : (FMT == FMT_HQ8_G32 ? 56 : 112);
     g->x_bytes = ((m * units * 64 + 127) / 128) * 128;
     g->red_bytes = kConsumerWarps * sub * nt * 32 * 16;
     const int fixed = g->x_bytes + g->red_bytes + kBarrierBytes;
@@ -630,15 +721,15 @@ bool plan_geometry(int units, int m, int nt, int sub, int jobs, StreamGeom* g) {
     if (env_w == 1 || env_w == 2 || env_w == 4 || env_w == 8 || env_w == 16) teams = kConsumerWarps / env_w;
     for (; teams >= 1; teams >>= 1) {
         const int w = kConsumerWarps / teams;
-        const int want = teams + (teams / 2 > 2 ? teams / 2 : 2);
+        const int want = teams + 2;
         int best_per = 0, best_stages = 0;
-        for (int nch = 1; nch <= units / quantum; ++nch) {
+        for (int nch = 1; nch <= (units + quantum - 1) / quantum; ++nch) {
             int per = (units + nch - 1) / nch;
             per = ((per + quantum - 1) / quantum) * quantum;
             if (env_chunk > 0) per = ((env_chunk + quantum - 1) / quantum) * quantum;
             if (per > max_chunk) continue;
             const int stage_bytes = kTileRows * (per * C::kUnitBytes + kRowPad);
-            int stages = (kSmemBudget - fixed) / stage_bytes;
+            int stages = (budget - fixed) / stage_bytes;
             if (stages > kMaxStages) stages = kMaxStages;
             if (stages >= want || (env_chunk > 0 && stages >= teams + 1)) { best_per = per; best_stages = stages; break; }
             if (env_chunk > 0) break;
@@ -703,6 +794,8 @@ int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_u
     if (grid < 1) grid = 1;
     for (int s = 0; s < slices; ++s) {
         GemvParams q = p;
+        q.q_lo = quanta / grid;
+        q.q_rem = quanta % grid;
         q.unit0 = s * per_slice;
         q.units = total_units - q.unit0 < per_slice ? total_units - q.unit0 : per_slice;
         q.partial = workspace;
@@ -711,8 +804,14 @@ int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_u
         StreamGeom g;
         const int rows_per_cta = (p.n_out + grid - 1) / grid;
         const int job_rows = sub == 4 ? 32 : 16;
-        if (!plan_geometry<FMT>(q.units, q.m, NT, sub, (rows_per_cta + job_rows - 1) / job_rows, &g))
+        const int jobs = (rows_per_cta + job_rows - 1) / job_rows;
+        if (!plan_geometry<FMT>(q.units, q.m, NT, sub, jobs, kSmemBudget, &g))
             return qwc_fail(QWC_ERR_BAD_GEOMETRY, "no shared-memory geometry fits this k slice");
+        static const bool trace = getenv("QWC_GEMV_TRACE") != nullptr;   // tuning aid: print the chosen geometry
+        if (trace)
+            fprintf(stderr, "qwc_gemv: fmt %d m %d units %d jobs/cta %d -> chunk %d x %d, teams %d x %d warps, %d stages, stride %d, smem %d\n",
+                    FMT, q.m, q.units, jobs, g.chunk_units, g.nchunks, kConsumerWarps / g.team_warps, g.team_warps, g.stages,
+                    g.stride, g.smem_bytes);
         q.chunk_units = g.chunk_units;
         q.nchunks = g.nchunks;
         q.team_warps = g.team_warps;
@@ -814,11 +913,7 @@ int qwc_launch_gemv(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* 
     p.epilogue = epilogue;
     p.x_is_rotated = x_is_rotated;
     p.row_quantum = epilogue == QWC_EPI_SILU_PAIR_FWHT ? 32 : 1;
-    p.dbg_skip = getenv("QWC_DBG_SKIP") != nullptr;
     p.pdl = hal->static_weights;
-    p.sh4 = 1u << 28;
-    p.sh8 = 1u << 24;
-    p.sh12 = 1u << 20;
     const int total_units = static_cast<int>(w->k / 32);
     const bool stream_ok = (p.row_bytes % 16 == 0) && (reinterpret_cast<uintptr_t>(w->blocks) % 16 == 0);
     const size_t need = stream_ok ? qwc_gemv_workspace_bytes(w, m) : 0;
