@@ -323,12 +323,13 @@ def run_ours(args):
                      "algorithmic_bytes_per_launch": nbytes},
         "device_status": status,
     }
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    # DRAM traffic per launch of this kernel on this workload, from the committed ncu summary (read + write bytes)
+    traffic_file = os.path.join(ROOT, "profiles", "qwc_gemv_stream_kernel_hq4g32_n17408_k5120_m1.md")
     if os.path.exists(traffic_file):
-        try:
-            line["roofline"]["traffic"] = json.load(open(traffic_file)).get("gemv_hq4g32_m1_bytes_per_launch")
-        except (ValueError, OSError):
-            pass
+        import re
+        mt = re.search(r"dram_bytes_per_launch:\s*(\d+)", open(traffic_file).read())
+        if mt:
+            line["roofline"]["traffic"] = int(mt.group(1))
 
     hal.set_static_weights(False)   # the sections below build fresh banks on the same stream
     extra = {}

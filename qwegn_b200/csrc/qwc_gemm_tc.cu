@@ -345,7 +345,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         // tensor core's critical path, with alternating groups they overlap with the other group's MMAs.
         const int cw = warp - kFirstConvWarp;
         const int grp = cw / kGroupWarps, cwl = cw % kGroupWarps;
-        const int r8 = lane >> 2, u = lane & 3;   // 8 rows x 4 units per warp step
+        const int r8 = lane & 7, u = lane >> 3;   // 8 rows x 4 units per warp step; a quarter warp = 8 rows of one unit, so its 16-byte stores fall in 8 distinct bank groups of the swizzled tile
         const int unit_bytes = p.raw_row_bytes / 4;
         const uint32_t s0 = 2 * grp, s1 = 2 * grp + 1;   // this group's operand stages
         uint8_t* wdst = wt + ((u >> 1) ? s1 : s0) * kWTileBytes;
