@@ -217,6 +217,145 @@ __global__ void __launch_bounds__(512) qwc_moe_place_kernel(const int32_t* __res
     }
 }
 
+// The whole pair sort in one launch, for pair counts where reading the pair list once per CTA is cheap (the list is
+// 64 KB at 2048 tokens x top-8 and sits in L2).  CTA c owns pairs [256 c, 256 c + 256).  Every CTA histograms ALL
+// pairs in shared memory (one shared atomic per pair), snapshotting the histogram when it reaches its own range: that
+// snapshot is the number of earlier pairs per expert.  An exclusive scan of the totals gives expert_off; the rank of a
+// pair inside its CTA comes from __match_any_sync (rank inside the warp) plus a per-warp, per-expert table (rank of the
+// warp inside the CTA).  The result is the stable counting sort of the reference (pairs of one expert in ascending pair
+// order).  CTA 0 publishes expert_off and the tile counts; the tile lists are written by all CTAs, experts dealt round
+// robin.  No scratch, no inter-CTA communication.
+constexpr int kSortCta = 256;
+
+__global__ void __launch_bounds__(kSortCta) qwc_moe_sort_kernel(const int32_t* __restrict__ idx, int pairs, int e, int k, int kTileX,
+                                                                int gu_rows, int dn_rows, int32_t* __restrict__ expert_off,
+                                                                int32_t* __restrict__ sorted_pair, int32_t* __restrict__ sorted_tok,
+                                                                int32_t* __restrict__ inv_perm, qwc_moe_tile* __restrict__ tiles_gu,
+                                                                qwc_moe_tile* __restrict__ tiles_dn, int32_t* __restrict__ tile_counts) {
+    __shared__ int s_cnt[512];
+    __shared__ int s_prev[512];
+    __shared__ int s_off[513];
+    __shared__ int s_tx[513];
+    __shared__ int s_wh[kSortCta / 32][512];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lo = blockIdx.x * kSortCta;
+    for (int i = tid; i < e; i += kSortCta) s_cnt[i] = 0;
+    for (int i = tid; i < (kSortCta / 32) * 512; i += kSortCta) (&s_wh[0][0])[i] = 0;
+    __syncthreads();
+    const bool vec = (reinterpret_cast<uintptr_t>(idx) & 15) == 0;
+    auto count_range = [&](int a, int b) {   // a is a multiple of 256
+        if (vec) {
+            const int b4 = a + ((b - a) & ~3);
+            for (int i = a + tid * 4; i < b4; i += kSortCta * 4) {
+                const int4 v = *reinterpret_cast<const int4*>(idx + i);
+                if (v.x >= 0 && v.x < e) atomicAdd(&s_cnt[v.x], 1);
+                if (v.y >= 0 && v.y < e) atomicAdd(&s_cnt[v.y], 1);
+                if (v.z >= 0 && v.z < e) atomicAdd(&s_cnt[v.z], 1);
+                if (v.w >= 0 && v.w < e) atomicAdd(&s_cnt[v.w], 1);
+            }
+            a = b4;
+        }
+        for (int i = a + tid; i < b; i += kSortCta) {
+            const int v = idx[i];
+            if (v >= 0 && v < e) atomicAdd(&s_cnt[v], 1);
+        }
+    };
+    count_range(0, min(lo, pairs));
+    __syncthreads();
+    for (int i = tid; i < e; i += kSortCta) s_prev[i] = s_cnt[i];
+    __syncthreads();
+    count_range(min(lo, pairs), pairs);
+    __syncthreads();
+    // exclusive scans over the experts (one warp, each lane a contiguous run of experts)
+    if (warp == 0) {
+        const int per = (e + 31) / 32;
+        const int b0 = min(lane * per, e), b1 = min(b0 + per, e);
+        int sc = 0, st = 0;
+        for (int i = b0; i < b1; ++i) {
+            sc += s_cnt[i];
+            st += (s_cnt[i] + kTileX - 1) / kTileX;
+        }
+        int ic = sc, it = st;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int uc = __shfl_up_sync(0xFFFFFFFFu, ic, o), ut = __shfl_up_sync(0xFFFFFFFFu, it, o);
+            if (lane >= o) {
+                ic += uc;
+                it += ut;
+            }
+        }
+        int rc = ic - sc, rt = it - st;
+        for (int i = b0; i < b1; ++i) {
+            s_off[i] = rc;
+            s_tx[i] = rt;
+            rc += s_cnt[i];
+            rt += (s_cnt[i] + kTileX - 1) / kTileX;
+        }
+        if (lane == 31) {
+            s_off[e] = ic;
+            s_tx[e] = it;
+        }
+    }
+    __syncthreads();
+    if (blockIdx.x == 0) {
+        for (int i = tid; i <= e; i += kSortCta) expert_off[i] = s_off[i];
+        if (tid == 0) {
+            tile_counts[0] = s_tx[e] * ((gu_rows + kTileW - 1) / kTileW);
+            tile_counts[1] = s_tx[e] * ((dn_rows + kTileW - 1) / kTileW);
+        }
+    }
+    // tile lists: weight tiles fastest inside an activation tile, so consecutive tiles re-read the same activations
+    for (int ex = blockIdx.x; ex < e; ex += gridDim.x) {
+        const int cnt = s_cnt[ex], ntx = s_tx[ex + 1] - s_tx[ex];
+        for (int which = 0; which < 2; ++which) {
+            const int rows = which == 0 ? gu_rows : dn_rows;
+            qwc_moe_tile* tiles = which == 0 ? tiles_gu : tiles_dn;
+            if (tiles == nullptr) continue;
+            const int ntw = (rows + kTileW - 1) / kTileW;
+            for (int it = tid; it < ntx * ntw; it += kSortCta) {
+                const int mt = it / ntw, j = it - mt * ntw;
+                qwc_moe_tile tl;
+                tl.w_row0 = ex * rows + j * kTileW;
+                tl.w_rows = min(kTileW, rows - j * kTileW);
+                tl.x_row0 = s_off[ex] + mt * kTileX;
+                tl.x_rows = min(kTileX, cnt - mt * kTileX);
+                tl.y_col0 = j * kTileW;
+                tl.expert = ex;
+                tl.pad0 = tl.pad1 = 0;
+                tiles[(s_tx[ex] + mt) * ntw + j] = tl;
+            }
+        }
+    }
+    // this CTA's pairs
+    const int p = lo + tid;
+    const int v = p < pairs ? idx[p] : -1;
+    const bool valid = v >= 0 && v < e;
+    const unsigned same = __match_any_sync(0xFFFFFFFFu, valid ? v : (0x40000000 | lane));
+    const int rank_w = __popc(same & ((1u << lane) - 1u));
+    if (valid && rank_w == 0) s_wh[warp][v] = __popc(same);
+    __syncthreads();
+    for (int i = tid; i < e; i += kSortCta) {
+        int run = s_prev[i];
+#pragma unroll
+        for (int w = 0; w < kSortCta / 32; ++w) {
+            const int t = s_wh[w][i];
+            s_wh[w][i] = run;
+            run += t;
+        }
+    }
+    __syncthreads();
+    if (p < pairs) {
+        if (valid) {
+            const int pos = s_off[v] + s_wh[warp][v] + rank_w;
+            sorted_pair[pos] = p;
+            sorted_tok[pos] = p / k;
+            inv_perm[p] = pos;
+        } else {
+            inv_perm[p] = -1;
+        }
+    }
+}
+
 // xs[p, :] = rot(x[sorted_tok[p], :]).  A quad handles one (sorted row, 32-element unit): lane t holds elements
 // 8t..8t+7 (one 16-byte load), rotates with three in-lane butterfly stages and two xor-shuffle stages (the
 // reference's h = 1, 2, 4, 8, 16 order) and writes one 16-byte chunk.  vec != 0 needs 16-byte aligned rows.
@@ -412,6 +551,16 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
     if (pairs >= (int64_t(1) << 30)) return qwc_fail(QWC_ERR_BAD_SHAPE, "too many pairs");
     if (!idx || !expert_off || !sorted_pair || !sorted_tok || !inv_perm || !tile_counts) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (pairs <= (int64_t(1) << 18)) {
+        // one launch: every CTA reads the whole pair list (<= 1 MB, L2-resident)
+        const int grid = static_cast<int>(pairs > 0 ? (pairs + kSortCta - 1) / kSortCta : 1);
+        qwc_moe_sort_kernel<<<grid, kSortCta, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e), static_cast<int>(k),
+                                                       moe_tile_rows(pairs, e), static_cast<int>(gu_rows), static_cast<int>(dn_rows),
+                                                       expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn, tile_counts);
+        QWC_CUDA_TRY(cudaGetLastError());
+        return QWC_OK;
+    }
+    // larger lists: three passes, one warp per expert.
     // expert_off doubles as the count buffer of pass 1; the plan kernel reads all counts before it writes offsets
     const int warps = static_cast<int>(e) + 1;
     qwc_moe_count_kernel<<<(warps + 15) / 16, 512, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e), expert_off, inv_perm);

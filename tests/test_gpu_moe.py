@@ -45,7 +45,7 @@ def test_route_refusals(hal):
     assert e.value.case == "badGeometry"
 
 
-@pytest.mark.parametrize("t,e,k", [(37, 8, 4), (2048, 256, 8), (3, 16, 2)])
+@pytest.mark.parametrize("t,e,k", [(37, 8, 4), (2048, 256, 8), (3, 16, 2), (1, 512, 16), (4100, 384, 3), (66000, 64, 4)])
 def test_group_pairs_matches_the_oracle(hal, oracle, t, e, k):
     import qwegn_b200 as q
     rng = np.random.default_rng(t * 7 + e)
