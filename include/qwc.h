@@ -48,7 +48,7 @@ enum {
 };
 
 /* QWDType subset used by this path (Sources/Foundation/QWCore/QWDType.swift:5-23). */
-enum { QWC_F16 = 0, QWC_F32 = 1 };
+enum { QWC_F16 = 0, QWC_F32 = 1, QWC_BF16 = 2 /* raw router planes only */ };
 
 /* QWEpilogue (QWGemm.swift:19-22) plus the fused-FWHT mode bit of
  * qwg_gemv_q4g_silu_pair_dx_h16 (Sources/QWMetal/gemm/qwgemm.metal:204-379). */
@@ -162,8 +162,16 @@ typedef struct {
     int32_t x_rows; /* valid activation rows (<= 256) */
     int32_t y_col0; /* output column of the tile's first weight row */
     int32_t expert;
-    int32_t pad0, pad1;
+    int32_t pad0;   /* paired tiles (pad1 != 0): first up row; rows w_row0.. are 64 gate rows, rows pad0.. the 64 up rows */
+    int32_t pad1;   /* 1 for a paired gate/up tile feeding a SwiGLU epilogue, else 0 */
 } qwc_moe_tile;
+
+/* QWGemm.encodeFnRouterGemm (Sources/Operators/QWGEMM/QWGemmMoERouter.swift:78-125; kernel qwg_router_gemm,
+ * Sources/QWMetal/subsystems/qwrouter.metal:460-520): logits f32 [t, e] = x [t, h] . w [e, h]^T with f32 accumulate.  x:
+ * the plain (un-rotated) hidden states, f16 or f32, row stride ldx; w: the raw router plane, bf16 / f16 / f32 (never
+ * rotated or quantized, Scripts/quantize/pack.py:332).  h % 32 == 0. */
+int qwc_moe_router_gemm(qwc_hal* hal, qwc_stream stream, const void* x, int32_t x_dtype, int64_t ldx, int64_t t, int64_t h,
+                        const void* w, int32_t w_dtype, int64_t e, float* logits);
 
 /* QWGemm.encodeFnMoeRoute (Sources/Operators/QWGEMM/QWGemmMoERouter.swift:78-113; kernel qwg_moe_route,
  * Sources/QWMetal/subsystems/qwrouter.metal:84-168): f32 softmax over all experts, top-k by repeated argmax (ties to
@@ -176,10 +184,12 @@ int qwc_moe_route(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t 
  * counting sort of the t*k (token, route) pairs by expert, slot order inside an expert = ascending pair index.
  * expert_off i32 [e + 1]; sorted_pair, sorted_tok, inv_perm i32 [pairs] (inv_perm = -1 for dropped pairs).  Also
  * writes the tile lists of the two grouped GEMMs (gate/up with gu_rows = 2 * inter rows per expert, down with dn_rows
- * = hidden rows per expert): tiles_gu / tiles_dn hold up to qwc_moe_max_tiles() entries, tile_counts i32 [2]. */
+ * = hidden rows per expert): tiles_gu / tiles_dn hold up to qwc_moe_max_tiles() entries, tile_counts i32 [2].
+ * gu_epilogue: QWC_EPI_NONE lists plain 128-row gate/up tiles; a SwiGLU epilogue (the one the gate/up grouped GEMM will
+ * be called with; needs inter % 64 == 0) lists tiles of 64 gate rows + their 64 up rows. */
 int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int64_t pairs, int64_t e, int64_t k,
                         int32_t* expert_off, int32_t* sorted_pair, int32_t* sorted_tok, int32_t* inv_perm,
-                        int64_t gu_rows, int64_t dn_rows, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
+                        int64_t gu_rows, int64_t dn_rows, int32_t gu_epilogue, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
                         int32_t* tile_counts);
 int64_t qwc_moe_max_tiles(int64_t pairs, int64_t e, int64_t rows_per_expert);
 /* Activation rows per tile the plan uses for this problem size (192 today; the kernel also takes 64 and 256). */
@@ -193,10 +203,13 @@ int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t l
 
 /* QWGemm.encodeMoEGateUpNax / encodeMoENaxSplitF32 (QWGemmMoE.swift:201-296): grouped expert GEMM over the tile list.
  * bank: stacked expert bank [e * rows_per_expert, k]; xs: expert-sorted rotated activations f16 [pairs, k];
- * y: f16 or f32 [pairs, rows_per_expert].  x_tile_rows = qwc_moe_tile_rows() of the call that built the list. */
+ * y: f16 or f32 [pairs, rows_per_expert].  x_tile_rows = qwc_moe_tile_rows() of the call that built the list.
+ * epilogue: QWC_EPI_NONE, or (gate/up bank with a paired tile list) QWC_EPI_SILU_PAIR / QWC_EPI_SILU_PAIR_FWHT: y is
+ * then h = f16(silu(gate) * up) [pairs, inter], rotated per 32 columns for the FWHT form — the fused twin of the
+ * reference's gemmBatchedH16SwiGLU (Sources/Runtime/QWEngine/Driver/EncodeKernels.swift:156-228). */
 int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank, const void* xs_f16, int64_t pairs,
                          const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, int32_t x_tile_rows, void* y,
-                         int32_t y_dtype, int64_t ldy);
+                         int32_t y_dtype, int64_t ldy, int32_t epilogue);
 
 /* QWGemm.encodeSiluMulSplitF16 (Sources/Operators/QWGEMM/QWGemmF32.swift:96-105; kernels
  * Sources/QWMetal/gemm/qwgemm_batched.metal:55-97): h[p, i] = fwht32(f16(silu(gu[p, i]) * gu[p, inter + i])). */

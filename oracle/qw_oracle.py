@@ -164,6 +164,13 @@ def swiglu_f16(gu: np.ndarray, rotate: bool = False) -> np.ndarray:
     return h
 
 
+def router_gemm(x: np.ndarray, w: np.ndarray) -> np.ndarray:
+    """Router logits [t, e] = x [t, h] . w [e, h]^T (qwg_router_gemm, Sources/QWMetal/subsystems/qwrouter.metal:457-520):
+    plain dot products of the un-rotated hidden states with the raw router plane; accumulated in f64 here, so the device's
+    f32 accumulation is compared against the exact value.  bf16 planes are passed in already widened to f32."""
+    return (np.asarray(x, dtype=np.float64) @ np.asarray(w, dtype=np.float64).T).astype(np.float32)
+
+
 def moe_route(logits: np.ndarray, topk: int, norm_topk: bool = True, routed_scale: float = 0.0):
     lg = _c(logits, np.float32)
     t, e = lg.shape

@@ -18,7 +18,7 @@ size_t qwc_gemv_workspace_bytes(const qwc_weight_view*, int64_t);
 bool qwc_gemm_tc_supported(const qwc_hal*, const qwc_weight_view*, int64_t, int);
 size_t qwc_gemm_tc_workspace_bytes(const qwc_weight_view*, int64_t, int);
 int qwc_launch_gemm_tc(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int, int64_t,
-                       int, void*, size_t);
+                       int, int, void*, size_t);
 
 static thread_local char g_err[512] = "";
 
@@ -244,8 +244,8 @@ int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const vo
     if (ldy < n_out) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldy=%lld < output width %lld", (long long)ldy, (long long)n_out);
     if (reinterpret_cast<uintptr_t>(x_f16) % 2 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "x must be 2-byte aligned");
     if (qwc_gemm_tc_supported(hal, w, m, epilogue))
-        return qwc_launch_gemm_tc(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, x_is_rotated,
-                                  workspace, workspace_bytes);
+        return qwc_launch_gemm_tc(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, epilogue,
+                                  x_is_rotated, workspace, workspace_bytes);
     return qwc_launch_gemv(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, epilogue,
                            x_is_rotated, workspace, workspace_bytes);
 }

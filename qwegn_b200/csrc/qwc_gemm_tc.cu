@@ -54,6 +54,9 @@ struct TcParams {
     int x_slot_bytes;    // bytes of one activation stage: 256 rows x 128 B, or 64 x 128 B when every tile has <= 64 rows
     int raw_row_bytes;   // packed bytes of 128 k of one row: 80 (HQ4_G32_M5) or 144 (HQ8_G32)
     int m_tiles, n_tiles;
+    int epilogue;        // QWC_EPI_NONE, or a SwiGLU epilogue: a tile is then 64 gate rows + the 64 matching up rows
+    int up_delta;        // dense SwiGLU mode: row distance gate -> up (= n / 2)
+    int xch_bytes;       // shared memory of the gate/up exchange buffer (SwiGLU epilogues)
     // grouped mode (MoE expert GEMMs): tiles come from a device-side list built by the pair sort
     const qwc_moe_tile* tiles;   // null in dense mode
     const int32_t* tile_count;   // device: number of valid entries of `tiles`
@@ -62,6 +65,7 @@ struct TcParams {
 // One unit of work of the kernel: 128 weight rows x up to 256 activation rows.
 struct TileInfo {
     int w_row0;     // first weight row (row coordinate of the weight tensor map)
+    int w_row1;     // SwiGLU epilogues: first up row (rows 64..127 of the tile); unused otherwise
     int w_rows;     // valid weight rows in the tile (<= 128)
     int x_row0;     // first activation row (row coordinate of the activation tensor map)
     int x_rows;     // valid activation rows (<= 256)
@@ -87,6 +91,19 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(1024 >> 4) << 32;
     d |= static_cast<uint64_t>(1) << 46;
     d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// One lane of the (converged) warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
+__device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
     return d;
 }
 
@@ -117,6 +134,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t r[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
 }
@@ -183,7 +208,8 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
 template <int FMT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                   const __grid_constant__ CUtensorMap xmap128, const __grid_constant__ CUtensorMap xmap64) {
+                   const __grid_constant__ CUtensorMap xmap128, const __grid_constant__ CUtensorMap xmap64,
+                   const __grid_constant__ CUtensorMap wmap64) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // layout (1024-byte aligned base): [W tiles][X tiles][raw stages][barriers]
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -201,6 +227,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     uint32_t* raw_issued = tmem_slot + 2;   // raw steps the weight producer has started
+    uint8_t* xch = reinterpret_cast<uint8_t*>(bars) + 512;   // SwiGLU epilogues: up values of 64 rows x 16 tokens (f16)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -236,14 +263,22 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         if (p.tiles != nullptr) {
             const qwc_moe_tile g = p.tiles[tile];
             t.w_row0 = g.w_row0;
+            t.w_row1 = g.pad0;
             t.w_rows = g.w_rows;
             t.x_row0 = g.x_row0;
             t.x_rows = g.x_rows;
             t.y_col0 = g.y_col0;
         } else {
             const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;   // token tiles fastest: CTAs share weight rows in L2
-            t.w_row0 = nt * kBM;
-            t.w_rows = min(kBM, p.n - t.w_row0);
+            if (p.epilogue == QWC_EPI_NONE) {
+                t.w_row0 = nt * kBM;
+                t.w_row1 = 0;
+                t.w_rows = min(kBM, p.n - t.w_row0);
+            } else {
+                t.w_row0 = nt * (kBM / 2);
+                t.w_row1 = t.w_row0 + p.up_delta;
+                t.w_rows = kBM;
+            }
             t.x_row0 = mt * p.x_tile_rows;
             t.x_rows = min(p.x_tile_rows, p.m - t.x_row0);
             t.y_col0 = t.w_row0;
@@ -301,7 +336,13 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                         break;
                     }
                     mbar_arrive_expect_tx(&raw_full[s], static_cast<uint32_t>(kBM * p.raw_row_bytes));
-                    tma_load_2d(raw + s * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[s]);
+                    if (p.epilogue == QWC_EPI_NONE) {
+                        tma_load_2d(raw + s * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[s]);
+                    } else {   // 64 gate rows, then the 64 up rows that pair with them
+                        tma_load_2d(raw + s * raw_stage_bytes, &wmap64, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[s]);
+                        tma_load_2d(raw + s * raw_stage_bytes + (kBM / 2) * p.raw_row_bytes, &wmap64, rs * (p.raw_row_bytes / 8),
+                                    ti.w_row1, &raw_full[s]);
+                    }
                     asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(raw_issued)), "r"(r + 1) : "memory");
                 }
             }
@@ -309,13 +350,20 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------- MMA issuer -------------------------------
-        if (lane == 0) {
+        // The whole warp runs the loop in lockstep and one elected lane issues: control flow and the descriptor
+        // arithmetic stay warp-uniform (uniform registers feed tcgen05.mma directly), and the issuing warp, which shares
+        // its scheduler with converter warps that are always ready, executes as few instructions per K tile as possible.
+        {
             uint32_t j = 0, tiles_done = 0;
             bool ok = true;
+            const uint64_t a_d0 = umma_desc_sw128(smem_u32(wt)), b_d0 = umma_desc_sw128(smem_u32(xt));
+            const uint32_t a_lo0 = static_cast<uint32_t>(a_d0), a_hi = static_cast<uint32_t>(a_d0 >> 32);
+            const uint32_t b_lo0 = static_cast<uint32_t>(b_d0), b_hi = static_cast<uint32_t>(b_d0 >> 32);
+            const uint32_t a_step = kWTileBytes >> 4, b_step = static_cast<uint32_t>(p.x_slot_bytes) >> 4;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tiles_done) {
                 const int as = tiles_done & 1;
                 if (tiles_done >= 2 && !mbar_wait_spin(&acc_empty[as], ((tiles_done >> 1) - 1) & 1)) {
-                    fail(QWC_DEV_WAIT_TMEM_TIMEOUT);
+                    if (lane == 0) fail(QWC_DEV_WAIT_TMEM_TIMEOUT);
                     break;
                 }
                 tc_fence_after();
@@ -323,18 +371,23 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                 const uint32_t idesc = make_idesc(min(kBN, (get_tile(tile).x_rows + 15) & ~15));
                 for (int kt = 0; kt < ktiles; ++kt, ++j) {
                     const uint32_t s = j % kStages;
-                    if (!mbar_wait_spin(&full[s], (j / kStages) & 1u)) {
-                        fail(QWC_DEV_WAIT_FULL_TIMEOUT);
+                    if (!mbar_wait_spin(&full[s], (j / kStages) & 1u)) {   // all lanes poll: measured faster than one polling lane
+                        if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
                         ok = false;
                         break;
                     }
-                    const uint32_t a_addr = smem_u32(wt + s * kWTileBytes), b_addr = smem_u32(xt + s * p.x_slot_bytes);
+                    // descriptors differ from the stage-0 ones only in the 14-bit start-address field (16-byte units)
+                    const uint32_t a_lo = a_lo0 + s * a_step, b_lo = b_lo0 + s * b_step;
+                    if (elect_one()) {
 #pragma unroll
-                    for (int q = 0; q < kBK / 16; ++q)
-                        umma_f16(d_tmem, umma_desc_sw128(a_addr + q * 32), umma_desc_sw128(b_addr + q * 32), idesc, (kt > 0 || q > 0) ? 1u : 0u);
-                    umma_commit(&empty[s]);   // the stage is free once these MMAs have read it
+                        for (int q = 0; q < kBK / 16; ++q)
+                            umma_f16(d_tmem, pack_desc(a_lo + 2 * q, a_hi), pack_desc(b_lo + 2 * q, b_hi), idesc, (kt > 0 || q > 0) ? 1u : 0u);
+                        umma_commit(&empty[s]);   // the stage is free once these MMAs have read it
+                    }
+                    __syncwarp();
                 }
-                if (ok) umma_commit(&acc_full[as]);
+                if (ok && elect_one()) umma_commit(&acc_full[as]);
+                __syncwarp();
             }
         }
         __syncwarp();
@@ -408,24 +461,99 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
             }
             tc_fence_after();
             const int wr = quarter * 32 + lane;          // weight row inside the tile
-            const int64_t ycol = ti.y_col0 + wr;
-            const int chunks = (ti.x_rows + 31) / 32;    // only the token columns the MMA wrote
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * kBN);
+            if (p.epilogue != QWC_EPI_NONE) {
+                // SwiGLU epilogues (the reference's qwg_gemm_q4g_h16_swiglu, include/qw_gemm_nax_swiglu.metalh:8-154): TMEM
+                // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows, so the two halves of a pair sit in
+                // different warps.  Per 16 tokens each warp parks the 8 tokens its partner will finish (f16, as the
+                // reference's threadgroup tile) in shared memory: the gate warps finish tokens 0..7 with the partner's up
+                // values, the up warps tokens 8..15 with the partner's gate values, so all four warps share the SwiGLU,
+                // the FWHT-32 across the 32 rows a warp holds, and the stores.
+                const bool is_up = quarter >= 2;
+                const int hrow = (quarter & 1) * 32 + lane;   // row of h inside the tile
+                uint4* park = reinterpret_cast<uint4*>(xch + (is_up ? 0 : 1024) + hrow * 16);        // what this warp gives
+                const uint4* take = reinterpret_cast<const uint4*>(xch + (is_up ? 1024 : 0) + hrow * 16);   // what it gets
+                const float sgn[5] = {(lane & 1) ? -1.0f : 1.0f, (lane & 2) ? -1.0f : 1.0f, (lane & 4) ? -1.0f : 1.0f,
+                                      (lane & 8) ? -1.0f : 1.0f, (lane & 16) ? -1.0f : 1.0f};
+                const int chunks16 = (ti.x_rows + 15) / 16;
+#pragma unroll 1
+                for (int c = 0; c < chunks16; ++c) {
+                    uint32_t rr[16];
+                    tmem_ld16(taddr + c * 16, rr);
+                    tmem_ld_wait();
+                    {
+                        const int g0 = is_up ? 0 : 8;   // the gate warps give tokens 8..15, the up warps tokens 0..7
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const __half2 h2 = __floats2half2_rn(__uint_as_float(rr[g0 + 2 * i]), __uint_as_float(rr[g0 + 2 * i + 1]));
+                            pk[i] = *reinterpret_cast<const uint32_t*>(&h2);
+                        }
+                        *park = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const uint4 got = *take;
+                    const uint32_t other[4] = {got.x, got.y, got.z, got.w};
+                    const int m0 = is_up ? 8 : 0;       // the tokens this warp finishes
+                    const int tok0 = c * 16 + m0;
+                    uint8_t* yrow = static_cast<uint8_t*>(p.y) +
+                                    (static_cast<int64_t>(ti.x_row0 + tok0) * p.ldy + ti.y_col0 + hrow) * (p.y_f16 ? 2 : 4);
+                    const int64_t ystep = p.ldy * (p.y_f16 ? 2 : 4);
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) {
+                        const __half2 o2 = *reinterpret_cast<const __half2*>(&other[jj >> 1]);
+                        const float o = (jj & 1) ? __high2float(o2) : __low2float(o2);
+                        const float mine = __half2float(__float2half_rn(__uint_as_float(rr[m0 + jj])));
+                        const float g = is_up ? o : mine, u = is_up ? mine : o;
+                        float h = __half2float(__float2half_rn(__fdividef(g, 1.0f + __expf(-g)) * u));
+                        if (p.epilogue == QWC_EPI_SILU_PAIR_FWHT) {
+#pragma unroll
+                            for (int st = 0; st < 5; ++st) h = fmaf(h, sgn[st], __shfl_xor_sync(0xFFFFFFFFu, h, 1 << st));
+                            h = __fmul_rn(h, qwc_inv_sqrt32());
+                        }
+                        if (tok0 + jj < ti.x_rows) {
+                            if (p.y_f16) *reinterpret_cast<__half*>(yrow) = __float2half_rn(h);
+                            else *reinterpret_cast<float*>(yrow) = __half2float(__float2half_rn(h));
+                        }
+                        yrow += ystep;
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");   // the exchange buffer is reused by the next 16 tokens
+                }
+            } else {
+            // plain epilogue: lane = weight row, 32 token columns per TMEM load; a lane's stores walk down one output column
+            const int chunks = (ti.x_rows + 31) / 32;    // only the token columns the MMA wrote
+            const int esz = p.y_f16 ? 2 : 4;
+            const int64_t ystep = p.ldy * esz;
+            uint8_t* ycolp = static_cast<uint8_t*>(p.y) + (static_cast<int64_t>(ti.x_row0) * p.ldy + ti.y_col0 + wr) * esz;
+            const bool row_ok = wr < ti.w_rows;
 #pragma unroll 1
             for (int c = 0; c < chunks; ++c) {
                 uint32_t rr[32];
                 tmem_ld32(taddr + c * 32, rr);
                 tmem_ld_wait();
-                if (wr < ti.w_rows) {
+                const int left = ti.x_rows - c * 32;   // valid tokens in this chunk (>= 1)
+                if (row_ok) {
+                    uint8_t* yp = ycolp;
+                    if (left >= 32) {
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        if (c * 32 + jj < ti.x_rows) {
-                            const int64_t o = static_cast<int64_t>(ti.x_row0 + c * 32 + jj) * p.ldy + ycol;
-                            if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(__uint_as_float(rr[jj]));
-                            else static_cast<float*>(p.y)[o] = __uint_as_float(rr[jj]);
+                        for (int jj = 0; jj < 32; ++jj) {
+                            if (p.y_f16) *reinterpret_cast<__half*>(yp) = __float2half_rn(__uint_as_float(rr[jj]));
+                            else *reinterpret_cast<float*>(yp) = __uint_as_float(rr[jj]);
+                            yp += ystep;
+                        }
+                    } else {
+#pragma unroll
+                        for (int jj = 0; jj < 32; ++jj) {
+                            if (jj < left) {
+                                if (p.y_f16) *reinterpret_cast<__half*>(yp) = __float2half_rn(__uint_as_float(rr[jj]));
+                                else *reinterpret_cast<float*>(yp) = __uint_as_float(rr[jj]);
+                            }
+                            yp += ystep;
                         }
                     }
                 }
+                ycolp += 32 * ystep;
+            }
             }
             tc_fence_before();
             __syncwarp();
@@ -460,14 +588,14 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 template <int FMT>
-int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap* xmaps, int smem,
-              int grid) {
+int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap64,
+              const CUtensorMap* xmaps, int smem, int grid) {
     static bool configured[64] = {};
     if (!configured[hal->device & 63]) {
         QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured[hal->device & 63] = true;
     }
-    qwc_gemm_tc_kernel<FMT><<<grid, kTcThreads, smem, st>>>(p, wmap, xmaps[0], xmaps[1], xmaps[2]);
+    qwc_gemm_tc_kernel<FMT><<<grid, kTcThreads, smem, st>>>(p, wmap, xmaps[0], xmaps[1], xmaps[2], wmap64);
     QWC_CUDA_TRY(cudaGetLastError());
     return QWC_OK;
 }
@@ -477,8 +605,10 @@ int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUte
 // Can the tensor-core path take this call?  (HQ4_G32_M5 and HQ8_G32 banks, K % 128 == 0, 16-byte aligned rows.)
 bool qwc_gemm_tc_supported(const qwc_hal* hal, const qwc_weight_view* w, int64_t m, int epilogue) {
     const int fmt = qwc_fmt_of(*w);
-    if (hal->encode_tiled == nullptr || epilogue != QWC_EPI_NONE) return false;
+    if (hal->encode_tiled == nullptr) return false;
     if (fmt != FMT_HQ4_G32_M5 && fmt != FMT_HQ8_G32) return false;
+    // SwiGLU epilogues pair 64 gate rows with 64 up rows per tile
+    if (epilogue != QWC_EPI_NONE && (w->n % 2 != 0 || (w->n / 2) % (kBM / 2) != 0)) return false;
     if (w->k % kRawK != 0 || m <= 16) return false;
     if (reinterpret_cast<uintptr_t>(w->blocks) % 16 != 0) return false;
     static const bool off = getenv("QWC_NO_TCGEN05") != nullptr;
@@ -493,7 +623,7 @@ size_t qwc_gemm_tc_workspace_bytes(const qwc_weight_view* w, int64_t m, int x_is
 // Shared by the dense door and the grouped (MoE) door: tensor maps, shared-memory budget, launch.
 static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const __half* xr, int64_t ldxr, int64_t m,
                   void* y, int y_dtype, int64_t ldy, const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles,
-                  int x_tile_rows) {
+                  int x_tile_rows, int epilogue) {
     const int fmt = qwc_fmt_of(*w);
     TcParams p{};
     p.tiles = tiles;
@@ -509,25 +639,28 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     if (tiles == nullptr && fmt != FMT_HQ4_G32_M5) x_tile_rows = 192;   // 36-byte blocks: the raw stages are 1.8x larger
     p.x_tile_rows = x_tile_rows;
     p.m_tiles = static_cast<int>((m + x_tile_rows - 1) / x_tile_rows);
-    p.n_tiles = static_cast<int>((w->n + kBM - 1) / kBM);
+    p.epilogue = epilogue;
+    p.up_delta = static_cast<int>(w->n / 2);
+    p.xch_bytes = epilogue == QWC_EPI_NONE ? 0 : (kBM / 2) * 16 * 2;
+    p.n_tiles = epilogue == QWC_EPI_NONE ? static_cast<int>((w->n + kBM - 1) / kBM) : static_cast<int>(w->n / kBM);
     const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
     p.x_slot_bytes = x_tile_rows * kBK * 2;
     p.raw_stages = kMaxRaw;
-    auto smem_need = [&](int rs) { return 1024 + kStages * (p.x_slot_bytes + kWTileBytes) + rs * raw_stage_bytes + 512; };
+    auto smem_need = [&](int rs) { return 1024 + kStages * (p.x_slot_bytes + kWTileBytes) + rs * raw_stage_bytes + 512 + p.xch_bytes; };
     while (smem_need(p.raw_stages) > 227 * 1024 && p.raw_stages > 2) --p.raw_stages;
     if (smem_need(p.raw_stages) > 227 * 1024) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "shared-memory budget exceeded");
     const int smem = smem_need(p.raw_stages);
 
     const EncodeFn enc = reinterpret_cast<EncodeFn>(hal->encode_tiled);
-    alignas(64) CUtensorMap wmap;
+    alignas(64) CUtensorMap wmaps[2];   // packed-weight boxes of 128 rows and (SwiGLU epilogues) 64 rows
     alignas(64) CUtensorMap xmaps[3];   // activation boxes of 256, 128 and 64 rows
     const int64_t row_bytes = (w->k / 32) * (fmt == FMT_HQ4_G32_M5 ? 20 : 36);
-    {
+    for (int i = 0; i < 2; ++i) {
         const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(row_bytes / 8), static_cast<cuuint64_t>(w->n)};
         const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(row_bytes)};
-        const cuuint32_t box[2] = {static_cast<cuuint32_t>(p.raw_row_bytes / 8), static_cast<cuuint32_t>(kBM)};
+        const cuuint32_t box[2] = {static_cast<cuuint32_t>(p.raw_row_bytes / 8), static_cast<cuuint32_t>(i == 0 ? kBM : kBM / 2)};
         const cuuint32_t estr[2] = {1, 1};
-        const CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w->blocks), gdim, gstride, box, estr,
+        const CUresult cr = enc(&wmaps[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w->blocks), gdim, gstride, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return qwc_fail(QWC_ERR_CUDA, "cuTensorMapEncodeTiled(weights) failed with %d", static_cast<int>(cr));
@@ -544,12 +677,12 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     }
     const int64_t ntiles = tiles != nullptr ? max_tiles : static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     const int grid = static_cast<int>(ntiles < hal->sm_count ? (ntiles < 1 ? 1 : ntiles) : hal->sm_count);
-    if (fmt == FMT_HQ4_G32_M5) return launch_tc<FMT_HQ4_G32_M5>(hal, st, p, wmap, xmaps, smem, grid);
-    return launch_tc<FMT_HQ8_G32>(hal, st, p, wmap, xmaps, smem, grid);
+    if (fmt == FMT_HQ4_G32_M5) return launch_tc<FMT_HQ4_G32_M5>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
+    return launch_tc<FMT_HQ8_G32>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
 }
 
 int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
-                       void* y, int y_dtype, int64_t ldy, int x_is_rotated, void* workspace, size_t workspace_bytes) {
+                       void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace, size_t workspace_bytes) {
     const __half* xr = static_cast<const __half*>(x);
     int64_t ldxr = ldx;
     if (!x_is_rotated) {
@@ -566,13 +699,13 @@ int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_vie
     } else if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || ldx % 8 != 0) {
         return qwc_fail(QWC_ERR_BAD_SHAPE, "rotated activations must be 16-byte aligned with ldx %% 8 == 0 for the tensor-core path");
     }
-    return tc_run(hal, st, w, xr, ldxr, m, y, y_dtype, ldy, nullptr, nullptr, 0, kBN);
+    return tc_run(hal, st, w, xr, ldxr, m, y, y_dtype, ldy, nullptr, nullptr, 0, kBN, epilogue);
 }
 
 // Grouped expert GEMM: the same kernel over a device-side tile list (see qwc_moe_group_pairs).
 int qwc_launch_gemm_tc_grouped(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* bank, const void* xs, int64_t pairs,
                                const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, void* y, int y_dtype,
-                               int64_t ldy, int x_tile_rows) {
+                               int64_t ldy, int x_tile_rows, int epilogue) {
     return tc_run(hal, st, bank, static_cast<const __half*>(xs), bank->k, pairs, y, y_dtype, ldy, tiles, tile_count, max_tiles,
-                  x_tile_rows);
+                  x_tile_rows, epilogue);
 }

@@ -9,7 +9,7 @@
 #include "qwc_common.cuh"
 
 int qwc_launch_gemm_tc_grouped(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, const qwc_moe_tile*,
-                               const int32_t*, int64_t, void*, int, int64_t, int);
+                               const int32_t*, int64_t, void*, int, int64_t, int, int);
 bool qwc_gemm_tc_supported(const qwc_hal*, const qwc_weight_view*, int64_t, int);
 
 namespace {
@@ -112,6 +112,78 @@ __global__ void __launch_bounds__(128) qwc_moe_route_kernel(const float* __restr
     }
 }
 
+// Router logits: y[t, e] = x[t, :] . W[e, :], f32 accumulate (the reference's qwg_router_gemm,
+// Sources/QWMetal/subsystems/qwrouter.metal:460-520; host door QWGemmMoERouter.swift:78-125).  The router weight is a
+// raw, un-rotated plane (bf16, f16 or f32), the activations are the plain (un-rotated) hidden states (f16 or f32).
+// A CTA computes 64 tokens x 64 experts; K goes through shared memory 32 columns at a time; a thread owns a 4 x 4
+// block (tokens 4 ty .. 4 ty + 3, experts tx, tx + 16, tx + 32, tx + 48).
+__device__ __forceinline__ float router_cvt(float v) { return v; }
+__device__ __forceinline__ float router_cvt(__half v) { return __half2float(v); }
+__device__ __forceinline__ float router_cvt(unsigned short v) { return __uint_as_float(static_cast<uint32_t>(v) << 16); }   // bf16 bits
+
+template <typename XT, typename WT>
+__global__ void __launch_bounds__(256) qwc_moe_router_gemm_kernel(const XT* __restrict__ x, int64_t ldx, const WT* __restrict__ w,
+                                                                  int t_rows, int e, int h, float* __restrict__ y) {
+    __shared__ float xs[64][33];
+    __shared__ float ws[64][33];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int t0 = blockIdx.y * 64, e0 = blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < h; k0 += 32) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = (tid >> 5) + 8 * i, c = tid & 31;
+            xs[r][c] = t0 + r < t_rows ? router_cvt(x[static_cast<int64_t>(t0 + r) * ldx + k0 + c]) : 0.0f;
+            ws[r][c] = e0 + r < e ? router_cvt(w[static_cast<int64_t>(e0 + r) * h + k0 + c]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < 32; ++kk) {
+            float xv[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                xv[i] = xs[4 * ty + i][kk];
+                wv[i] = ws[tx + 16 * i][kk];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int t = t0 + 4 * ty + i, ex = e0 + tx + 16 * j;
+            if (t < t_rows && ex < e) y[static_cast<int64_t>(t) * e + ex] = acc[i][j];
+        }
+}
+
+// Tile j of expert ex for a bank with `rows` rows per expert.  paired != 0 (gate||up bank feeding a SwiGLU epilogue):
+// the tile is 64 gate rows followed by the 64 up rows that pair with them, and its output columns are the 64 rows of h.
+__device__ __forceinline__ qwc_moe_tile moe_make_tile(int ex, int rows, int j, int paired, int x_row0, int x_rows) {
+    qwc_moe_tile tl;
+    if (paired) {
+        tl.w_row0 = ex * rows + j * (kTileW / 2);
+        tl.pad0 = tl.w_row0 + rows / 2;
+        tl.w_rows = kTileW;
+        tl.y_col0 = j * (kTileW / 2);
+        tl.pad1 = 1;
+    } else {
+        tl.w_row0 = ex * rows + j * kTileW;
+        tl.pad0 = 0;
+        tl.w_rows = min(kTileW, rows - j * kTileW);
+        tl.y_col0 = j * kTileW;
+        tl.pad1 = 0;
+    }
+    tl.x_row0 = x_row0;
+    tl.x_rows = x_rows;
+    tl.expert = ex;
+    return tl;
+}
+
 // Pass 1 of the pair sort: one warp per expert counts its pairs; warp `e` (one past the last expert) marks the
 // dropped pairs (idx < 0 or >= e) in inv_perm.  The CTA stages the pair list through shared memory in chunks so the
 // per-warp scans run at shared-memory latency instead of one L2 round trip per 32 pairs.
@@ -144,7 +216,7 @@ __global__ void __launch_bounds__(512) qwc_moe_count_kernel(const int32_t* __res
 
 // Pass 2: exclusive prefix over the experts and the two tile lists (one CTA).
 __global__ void __launch_bounds__(512) qwc_moe_plan_kernel(const int32_t* counts, int e, int kTileX, int32_t* expert_off,
-                                                           int gu_rows, int dn_rows, qwc_moe_tile* __restrict__ tiles_gu,
+                                                           int gu_rows, int dn_rows, int gu_paired, qwc_moe_tile* __restrict__ tiles_gu,
                                                            qwc_moe_tile* __restrict__ tiles_dn, int32_t* __restrict__ tile_counts) {
     __shared__ int s_off[513];
     __shared__ int s_tx[513];   // activation-tile prefix
@@ -173,17 +245,9 @@ __global__ void __launch_bounds__(512) qwc_moe_plan_kernel(const int32_t* counts
             const int ntw = (rows + kTileW - 1) / kTileW;
             // weight tiles fastest inside an activation tile: consecutive tiles re-read the same activations
             for (int mt = 0; mt < ntx; ++mt)
-                for (int j = 0; j < ntw; ++j) {
-                    qwc_moe_tile tl;
-                    tl.w_row0 = ex * rows + j * kTileW;
-                    tl.w_rows = min(kTileW, rows - j * kTileW);
-                    tl.x_row0 = s_off[ex] + mt * kTileX;
-                    tl.x_rows = min(kTileX, cnt - mt * kTileX);
-                    tl.y_col0 = j * kTileW;
-                    tl.expert = ex;
-                    tl.pad0 = tl.pad1 = 0;
-                    tiles[(s_tx[ex] + mt) * ntw + j] = tl;
-                }
+                for (int j = 0; j < ntw; ++j)
+                    tiles[(s_tx[ex] + mt) * ntw + j] = moe_make_tile(ex, rows, j, which == 0 && gu_paired, s_off[ex] + mt * kTileX,
+                                                                     min(kTileX, cnt - mt * kTileX));
         }
     }
 }
@@ -228,7 +292,7 @@ __global__ void __launch_bounds__(512) qwc_moe_place_kernel(const int32_t* __res
 constexpr int kSortCta = 256;
 
 __global__ void __launch_bounds__(kSortCta) qwc_moe_sort_kernel(const int32_t* __restrict__ idx, int pairs, int e, int k, int kTileX,
-                                                                int gu_rows, int dn_rows, int32_t* __restrict__ expert_off,
+                                                                int gu_rows, int dn_rows, int gu_paired, int32_t* __restrict__ expert_off,
                                                                 int32_t* __restrict__ sorted_pair, int32_t* __restrict__ sorted_tok,
                                                                 int32_t* __restrict__ inv_perm, qwc_moe_tile* __restrict__ tiles_gu,
                                                                 qwc_moe_tile* __restrict__ tiles_dn, int32_t* __restrict__ tile_counts) {
@@ -314,15 +378,8 @@ __global__ void __launch_bounds__(kSortCta) qwc_moe_sort_kernel(const int32_t* _
             const int ntw = (rows + kTileW - 1) / kTileW;
             for (int it = tid; it < ntx * ntw; it += kSortCta) {
                 const int mt = it / ntw, j = it - mt * ntw;
-                qwc_moe_tile tl;
-                tl.w_row0 = ex * rows + j * kTileW;
-                tl.w_rows = min(kTileW, rows - j * kTileW);
-                tl.x_row0 = s_off[ex] + mt * kTileX;
-                tl.x_rows = min(kTileX, cnt - mt * kTileX);
-                tl.y_col0 = j * kTileW;
-                tl.expert = ex;
-                tl.pad0 = tl.pad1 = 0;
-                tiles[(s_tx[ex] + mt) * ntw + j] = tl;
+                tiles[(s_tx[ex] + mt) * ntw + j] = moe_make_tile(ex, rows, j, which == 0 && gu_paired, s_off[ex] + mt * kTileX,
+                                                                 min(kTileX, cnt - mt * kTileX));
             }
         }
     }
@@ -523,6 +580,37 @@ int64_t qwc_moe_max_tiles(int64_t pairs, int64_t e, int64_t rows_per_expert) {
     return tx * ((rows_per_expert + kTileW - 1) / kTileW);
 }
 
+int qwc_moe_router_gemm(qwc_hal* hal, qwc_stream stream, const void* x, int32_t x_dtype, int64_t ldx, int64_t t, int64_t h,
+                        const void* w, int32_t w_dtype, int64_t e, float* logits) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    // QWGemmMoERouter.swift:82: the router GEMM needs K % 32 == 0
+    if (h <= 0 || h % 32 != 0) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "hidden=%lld must be a positive multiple of 32", (long long)h);
+    if (e <= 0 || t < 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "bad extents");
+    if (t == 0) return QWC_OK;
+    if (ldx < h) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldx < hidden");
+    if (!x || !w || !logits) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    if (x_dtype != QWC_F16 && x_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "activations must be f16 or f32");
+    if (w_dtype != QWC_F16 && w_dtype != QWC_F32 && w_dtype != QWC_BF16) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "router weights must be bf16, f16 or f32");
+    const dim3 grid(static_cast<unsigned>((e + 63) / 64), static_cast<unsigned>((t + 63) / 64));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int ti = static_cast<int>(t), ei = static_cast<int>(e), hi = static_cast<int>(h);
+#define QWC_ROUTER_LAUNCH(XT, WT) \
+    qwc_moe_router_gemm_kernel<XT, WT><<<grid, 256, 0, st>>>(static_cast<const XT*>(x), ldx, static_cast<const WT*>(w), ti, ei, hi, logits)
+    if (x_dtype == QWC_F32) {
+        if (w_dtype == QWC_F32) QWC_ROUTER_LAUNCH(float, float);
+        else if (w_dtype == QWC_F16) QWC_ROUTER_LAUNCH(float, __half);
+        else QWC_ROUTER_LAUNCH(float, unsigned short);
+    } else {
+        if (w_dtype == QWC_F32) QWC_ROUTER_LAUNCH(__half, float);
+        else if (w_dtype == QWC_F16) QWC_ROUTER_LAUNCH(__half, __half);
+        else QWC_ROUTER_LAUNCH(__half, unsigned short);
+    }
+#undef QWC_ROUTER_LAUNCH
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
+
 int qwc_moe_route(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t t, int64_t e, int64_t k, int32_t norm_topk,
                   float routed_scale, int32_t* idx, float* wts) {
     qwc_clear_error();
@@ -542,9 +630,12 @@ int qwc_moe_route(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t 
 
 int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int64_t pairs, int64_t e, int64_t k,
                         int32_t* expert_off, int32_t* sorted_pair, int32_t* sorted_tok, int32_t* inv_perm,
-                        int64_t gu_rows, int64_t dn_rows, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
+                        int64_t gu_rows, int64_t dn_rows, int32_t gu_epilogue, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
                         int32_t* tile_counts) {
     qwc_clear_error();
+    const int paired = gu_epilogue != QWC_EPI_NONE;
+    if (paired && gu_rows % kTileW != 0)
+        return qwc_fail(QWC_ERR_BAD_GEOMETRY, "a SwiGLU epilogue needs inter %% 64 == 0, got gate||up rows = %lld", (long long)gu_rows);
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
     if (e <= 0 || e > 512) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "experts=%lld must be in 1..512", (long long)e);
     if (k <= 0 || pairs < 0 || pairs % k != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "pairs=%lld is not a multiple of k=%lld", (long long)pairs, (long long)k);
@@ -556,7 +647,7 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
         const int grid = static_cast<int>(pairs > 0 ? (pairs + kSortCta - 1) / kSortCta : 1);
         qwc_moe_sort_kernel<<<grid, kSortCta, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e), static_cast<int>(k),
                                                        moe_tile_rows(pairs, e), static_cast<int>(gu_rows), static_cast<int>(dn_rows),
-                                                       expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn, tile_counts);
+                                                       paired, expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn, tile_counts);
         QWC_CUDA_TRY(cudaGetLastError());
         return QWC_OK;
     }
@@ -566,7 +657,7 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
     qwc_moe_count_kernel<<<(warps + 15) / 16, 512, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e), expert_off, inv_perm);
     QWC_CUDA_TRY(cudaGetLastError());
     qwc_moe_plan_kernel<<<1, 512, 0, st>>>(expert_off, static_cast<int>(e), moe_tile_rows(pairs, e), expert_off, static_cast<int>(gu_rows),
-                                           static_cast<int>(dn_rows), tiles_gu, tiles_dn, tile_counts);
+                                           static_cast<int>(dn_rows), paired, tiles_gu, tiles_dn, tile_counts);
     QWC_CUDA_TRY(cudaGetLastError());
     qwc_moe_place_kernel<<<(static_cast<int>(e) + 15) / 16, 512, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e),
                                                                        static_cast<int>(k), expert_off, sorted_pair, sorted_tok, inv_perm);
@@ -593,8 +684,9 @@ int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t l
 
 int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank, const void* xs_f16, int64_t pairs,
                          const qwc_moe_tile* tiles, const int32_t* tile_count, int64_t max_tiles, int32_t x_tile_rows, void* y,
-                         int32_t y_dtype, int64_t ldy) {
+                         int32_t y_dtype, int64_t ldy, int32_t epilogue) {
     qwc_clear_error();
+    if (epilogue < QWC_EPI_NONE || epilogue > QWC_EPI_SILU_PAIR_FWHT) return qwc_fail(QWC_ERR_BAD_SHAPE, "unknown epilogue %d", epilogue);
     if (x_tile_rows != 64 && x_tile_rows != 192 && x_tile_rows != 256)
         return qwc_fail(QWC_ERR_BAD_GEOMETRY, "x_tile_rows must be 64, 192 or 256 (qwc_moe_tile_rows)");
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
@@ -607,7 +699,7 @@ int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view*
         return qwc_fail(QWC_ERR_BLOCKED, "grouped expert GEMM needs an HQ4_G32_M5 / HQ8_G32 bank with k %% 128 == 0, 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(xs_f16) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "xs must be 16-byte aligned");
     return qwc_launch_gemm_tc_grouped(hal, static_cast<cudaStream_t>(stream), bank, xs_f16, pairs, tiles, tile_count, max_tiles, y,
-                                      y_dtype, ldy, x_tile_rows);
+                                      y_dtype, ldy, x_tile_rows, epilogue);
 }
 
 int qwc_moe_silu_mul(qwc_hal* hal, qwc_stream stream, const void* gu_f16, int64_t rows, int64_t inter, int32_t rotate,
@@ -682,15 +774,22 @@ int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank
     int32_t* tile_counts = reinterpret_cast<int32_t*>(sc + L.tile_counts);
     int rc;
     if ((rc = qwc_moe_route(hal, stream, logits, t, e, k, norm_topk, routed_scale, idx, wts))) return rc;
-    if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h,
+    // SwiGLU + FWHT run in the gate/up GEMM's epilogue when the tiles can pair 64 gate rows with their up rows
+    const int32_t gu_epi = inter % 64 == 0 ? QWC_EPI_SILU_PAIR_FWHT : QWC_EPI_NONE;
+    if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h, gu_epi,
                                   tiles_gu, tiles_dn, tile_counts))) return rc;
     if ((rc = qwc_moe_gather(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs))) return rc;
     const int32_t xrows = qwc_moe_tile_rows(pairs, e);
-    if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_gu, sc + L.xs, pairs, tiles_gu, tile_counts, qwc_moe_max_tiles(pairs, e, 2 * inter),
-                                   xrows, sc + L.gu, QWC_F16, 2 * inter))) return rc;
-    if ((rc = qwc_moe_silu_mul(hal, stream, sc + L.gu, pairs, inter, 1, sc + L.hs))) return rc;
+    if (gu_epi != QWC_EPI_NONE) {
+        if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_gu, sc + L.xs, pairs, tiles_gu, tile_counts, qwc_moe_max_tiles(pairs, e, 2 * inter),
+                                       xrows, sc + L.hs, QWC_F16, inter, gu_epi))) return rc;
+    } else {
+        if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_gu, sc + L.xs, pairs, tiles_gu, tile_counts, qwc_moe_max_tiles(pairs, e, 2 * inter),
+                                       xrows, sc + L.gu, QWC_F16, 2 * inter, QWC_EPI_NONE))) return rc;
+        if ((rc = qwc_moe_silu_mul(hal, stream, sc + L.gu, pairs, inter, 1, sc + L.hs))) return rc;
+    }
     if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_dn, sc + L.hs, pairs, tiles_dn, tile_counts + 1, qwc_moe_max_tiles(pairs, e, h),
-                                   xrows, sc + L.dn, QWC_F16, h))) return rc;
+                                   xrows, sc + L.dn, QWC_F16, h, QWC_EPI_NONE))) return rc;
     return qwc_moe_combine(hal, stream, sc + L.dn, QWC_F16, inv_perm, wts, t, k, h, out, out_dtype);
 }
 

@@ -21,10 +21,11 @@ class MoeTileC(ctypes.Structure):
 
 
 _lib.register("qwc_moe_route", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, ctypes.c_float, _vp, _vp])
-_lib.register("qwc_moe_group_pairs", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp])
+_lib.register("qwc_moe_router_gemm", ctypes.c_int, [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _i32, _i64, _vp])
+_lib.register("qwc_moe_group_pairs", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp])
 _lib.register("qwc_moe_max_tiles", _i64, [_i64, _i64, _i64])
 _lib.register("qwc_moe_gather", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _i64, _i32, _vp])
-_lib.register("qwc_moe_grouped_gemm", ctypes.c_int, [_vp, _vp, _WV, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _i32, _i64])
+_lib.register("qwc_moe_grouped_gemm", ctypes.c_int, [_vp, _vp, _WV, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _i32, _i64, _i32])
 _lib.register("qwc_moe_tile_rows", _i32, [_i64, _i64])
 _lib.register("qwc_moe_silu_mul", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i32, _vp])
 _lib.register("qwc_moe_combine", ctypes.c_int, [_vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _vp, _i32])
@@ -75,6 +76,22 @@ class QWGemmMoE:
     """The individual MoE doors (QWGemmMoE.swift, QWGemmMoERouter.swift)."""
 
     @staticmethod
+    def encodeFnRouterGemm(hal: QWHal, weight: torch.Tensor, x: torch.Tensor, y: torch.Tensor, stream=None) -> None:
+        """Router logits y f32 [t, e] = x [t, h] . weight [e, h]^T (QWGemmMoERouter.swift:78-125).  weight: the raw router
+        plane, bf16 / f16 / f32, un-rotated; x: plain hidden states, f16 or f32."""
+        dts = {torch.float16: 0, torch.float32: 1, torch.bfloat16: 2}
+        if weight.dtype not in dts or x.dtype not in (torch.float16, torch.float32) or y.dtype != torch.float32:
+            raise QWGemmError(3, "router GEMM takes bf16/f16/f32 weights, f16/f32 activations and f32 logits")
+        if not (weight.is_contiguous() and y.is_contiguous() and x.stride(1) == 1):
+            raise QWGemmError(3, "weight and y must be contiguous, x rows contiguous")
+        t, h = x.shape
+        e = weight.shape[0]
+        if weight.shape[1] != h or tuple(y.shape) != (t, e):
+            raise QWGemmError(3, "shape mismatch")
+        _check(_lib.load().qwc_moe_router_gemm(hal.handle, _stream_ptr(stream), x.data_ptr(), dts[x.dtype], x.stride(0), t, h,
+                                               weight.data_ptr(), dts[weight.dtype], e, y.data_ptr()))
+
+    @staticmethod
     def encodeFnMoeRoute(hal: QWHal, logits: torch.Tensor, top_k: int, idx: torch.Tensor, wts: torch.Tensor,
                          norm_topk: bool = True, routed_scale: float = 0.0, stream=None) -> None:
         t, e = logits.shape
@@ -86,8 +103,10 @@ class QWGemmMoE:
         return int(_lib.load().qwc_moe_max_tiles(pairs, experts, rows_per_expert))
 
     @staticmethod
-    def encodeMoEGroupPairs(hal: QWHal, idx: torch.Tensor, experts: int, gu_rows: int, dn_rows: int, stream=None):
-        """Returns (expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn, tile_counts), all on the device."""
+    def encodeMoEGroupPairs(hal: QWHal, idx: torch.Tensor, experts: int, gu_rows: int, dn_rows: int, stream=None,
+                            gu_epilogue: int = 0):
+        """Returns (expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn, tile_counts), all on the device.
+        gu_epilogue != 0 lists paired gate/up tiles (64 gate rows + their 64 up rows) for a SwiGLU epilogue."""
         t, k = idx.shape
         pairs = t * k
         dev = idx.device
@@ -99,7 +118,7 @@ class QWGemmMoE:
         td = torch.zeros((QWGemmMoE.maxTiles(pairs, experts, dn_rows), 8), dtype=torch.int32, device=dev)
         tc = torch.zeros(4, dtype=torch.int32, device=dev)
         _check(_lib.load().qwc_moe_group_pairs(hal.handle, _stream_ptr(stream), idx.data_ptr(), pairs, experts, k, off.data_ptr(),
-                                               sp.data_ptr(), st.data_ptr(), inv.data_ptr(), gu_rows, dn_rows, tg.data_ptr(),
+                                               sp.data_ptr(), st.data_ptr(), inv.data_ptr(), gu_rows, dn_rows, gu_epilogue, tg.data_ptr(),
                                                td.data_ptr(), tc.data_ptr()))
         return off, sp, st, inv, tg, td, tc
 

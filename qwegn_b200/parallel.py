@@ -227,18 +227,25 @@ class EPMoE:
         if r > 0:
             # regroup the received rows by local expert (K = 1 pair sort), run the experts, undo the regroup
             eid = ep_received_expert_ids(plan).view(r, 1).contiguous()
-            loff, _, lsorted, linv, tg, td, tc = QWGemmMoE.encodeMoEGroupPairs(hal, eid, self.per, 2 * inter, h)
+            fused = 2 if inter % 64 == 0 else 0   # SwiGLU + FWHT in the gate/up GEMM's epilogue
+            loff, _, lsorted, linv, tg, td, tc = QWGemmMoE.encodeMoEGroupPairs(hal, eid, self.per, 2 * inter, h, gu_epilogue=fused)
             xg = torch.empty((r, h), dtype=torch.float16, device=dev)
             _check(lib.qwc_moe_gather(hal.handle, _stream_ptr(None), recv.data_ptr(), recv.stride(0), h, lsorted.data_ptr(),
                                       loff.data_ptr(), self.per, r, 1, xg.data_ptr()))
-            gu = torch.empty((r, 2 * inter), dtype=torch.float16, device=dev)
-            _check(lib.qwc_moe_grouped_gemm(hal.handle, _stream_ptr(None), ctypes.byref(self.bank_gu.c), xg.data_ptr(), r,
-                                            tg.data_ptr(), tc.data_ptr(), tg.shape[0], lib.qwc_moe_tile_rows(r, self.per), gu.data_ptr(), 0, 2 * inter))
             hs = torch.empty((r, inter), dtype=torch.float16, device=dev)
-            _check(lib.qwc_moe_silu_mul(hal.handle, _stream_ptr(None), gu.data_ptr(), r, inter, 1, hs.data_ptr()))
+            if fused:
+                _check(lib.qwc_moe_grouped_gemm(hal.handle, _stream_ptr(None), ctypes.byref(self.bank_gu.c), xg.data_ptr(), r,
+                                                tg.data_ptr(), tc.data_ptr(), tg.shape[0], lib.qwc_moe_tile_rows(r, self.per),
+                                                hs.data_ptr(), 0, inter, fused))
+            else:
+                gu = torch.empty((r, 2 * inter), dtype=torch.float16, device=dev)
+                _check(lib.qwc_moe_grouped_gemm(hal.handle, _stream_ptr(None), ctypes.byref(self.bank_gu.c), xg.data_ptr(), r,
+                                                tg.data_ptr(), tc.data_ptr(), tg.shape[0], lib.qwc_moe_tile_rows(r, self.per),
+                                                gu.data_ptr(), 0, 2 * inter, 0))
+                _check(lib.qwc_moe_silu_mul(hal.handle, _stream_ptr(None), gu.data_ptr(), r, inter, 1, hs.data_ptr()))
             dn = torch.empty((r, h), dtype=torch.float16, device=dev)
             _check(lib.qwc_moe_grouped_gemm(hal.handle, _stream_ptr(None), ctypes.byref(self.bank_dn.c), hs.data_ptr(), r,
-                                            td.data_ptr(), tc[1:].data_ptr(), td.shape[0], lib.qwc_moe_tile_rows(r, self.per), dn.data_ptr(), 0, h))
+                                            td.data_ptr(), tc[1:].data_ptr(), td.shape[0], lib.qwc_moe_tile_rows(r, self.per), dn.data_ptr(), 0, h, 0))
             ones = torch.ones((r, 1), dtype=torch.float32, device=dev)
             QWGemmMoE.encodeMoECombine(hal, dn, linv, ones, out_rows[:r])
         back = ep_return(out_rows[:r], plan, self.group)

@@ -41,6 +41,30 @@ def test_prefill_vs_oracle(hal, oracle, name, shape):
     assert_matmul_close(_run(q, hal, view, xr, rotated=True, out_dtype=torch.float32), yref)
 
 
+@pytest.mark.parametrize("name", ["HQ4_G32", "HQ8_G32"])
+@pytest.mark.parametrize("shape", [(17, 64, 128), (100, 192, 512), (300, 512, 640), (513, 128, 2048)])
+def test_prefill_fused_swiglu_epilogues(hal, oracle, name, shape):
+    # Fused gate/up GEMM + SwiGLU (+ FWHT-32) on the tensor path: gate rows [0, I), up rows [I, 2I) of one bank
+    # (the reference's gemmBatchedH16SwiGLU, EncodeKernels.swift:156-228); oracle as gen_mlp_fixtures.py:71-79.
+    import qwegn_b200 as q
+    m, inter, k = shape
+    fmt = oracle.FORMATS[name]
+    rng = np.random.default_rng(m + inter + k)
+    blocks = oracle.quantize(rng.normal(0.0, 0.03, (2 * inter, k)).astype(np.float32), fmt)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    view = _bank(q, blocks, name)
+    gu = oracle.matmul(blocks, fmt, x)
+    xd = torch.from_numpy(x).cuda()
+    for epi, rotate, tight in ((q.EPI_SILU_PAIR, False, 4e-3), (q.EPI_SILU_PAIR_FWHT, True, 5e-3)):
+        href = oracle.swiglu_f16(gu, rotate=rotate).astype(np.float32)
+        for dt in (torch.float16, torch.float32):
+            y = torch.full((m, inter), float("nan"), dtype=dt, device="cuda")
+            ws = torch.empty(q.QWGemm.workspaceBytes(hal, view, m, epi, False), dtype=torch.uint8, device="cuda")
+            q.QWGemm.encode(hal, view, xd, y, epi=epi, workspace=ws)
+            assert_matmul_close(y.float().cpu().numpy(), href, tight=tight)
+    assert hal.device_status() == 0
+
+
 def test_prefill_matches_the_gemv_path_row_by_row(hal, oracle):
     # Twin test (Tests/QWGEMMTests/QWBatchedGemmTests.swift:37-140: batched GEMM vs per-row GEMV, max |d| < 0.05).
     import qwegn_b200 as q

@@ -35,6 +35,26 @@ def test_route_matches_the_oracle(hal, oracle, t, e, k):
     np.testing.assert_allclose(wts.cpu().numpy(), rwts, rtol=2e-6, atol=1e-7)
 
 
+@pytest.mark.parametrize("t,e,h", [(1, 32, 64), (70, 96, 256), (300, 256, 2048)])
+@pytest.mark.parametrize("wdt", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("xdt", [torch.float16, torch.float32])
+def test_router_gemm_matches_the_oracle(hal, oracle, t, e, h, wdt, xdt):
+    # Twin of encodeFnRouterGemm: raw (un-rotated, un-quantized) router plane times the plain hidden states.
+    import qwegn_b200 as q
+    rng = np.random.default_rng(t + e + h)
+    w = torch.from_numpy(rng.normal(0.0, 0.05, (e, h)).astype(np.float32)).to(wdt).cuda()
+    x = torch.from_numpy(rng.standard_normal((t, h)).astype(np.float32)).to(xdt).cuda()
+    y = torch.full((t, e), float("nan"), dtype=torch.float32, device="cuda")
+    q.QWGemmMoE.encodeFnRouterGemm(hal, w, x, y)
+    ref = oracle.router_gemm(x.float().cpu().numpy(), w.float().cpu().numpy())
+    got = y.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= 2e-5 * np.abs(ref).max() + 1e-6   # f32 accumulation of <= 2048 terms
+    with pytest.raises(q.QWGemmError) as err:   # QWGemmMoERouter.swift:82: K % 32 == 0
+        q.QWGemmMoE.encodeFnRouterGemm(hal, w[:, :h - 16].contiguous(), x[:, :h - 16], y)
+    assert err.value.case == "badGeometry"
+
+
 def test_route_refusals(hal):
     import qwegn_b200 as q
     lg = torch.zeros((2, 600), dtype=torch.float32, device="cuda")
