@@ -205,6 +205,135 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
+// Tile number `tile` of the launch: from the device-side list (grouped mode) or the dense (weight tile, token tile) grid.
+__device__ __forceinline__ TileInfo tc_get_tile(const TcParams& p, int tile) {
+    TileInfo t;
+    if (p.tiles != nullptr) {
+        const qwc_moe_tile g = p.tiles[tile];
+        t.w_row0 = g.w_row0;
+        t.w_row1 = g.pad0;
+        t.w_rows = g.w_rows;
+        t.x_row0 = g.x_row0;
+        t.x_rows = g.x_rows;
+        t.y_col0 = g.y_col0;
+    } else {
+        const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;   // token tiles fastest: CTAs share weight rows in L2
+        if (p.epilogue == QWC_EPI_NONE) {
+            t.w_row0 = nt * kBM;
+            t.w_row1 = 0;
+            t.w_rows = min(kBM, p.n - t.w_row0);
+        } else {
+            t.w_row0 = nt * (kBM / 2);
+            t.w_row1 = t.w_row0 + p.up_delta;
+            t.w_rows = kBM;
+        }
+        t.x_row0 = mt * p.x_tile_rows;
+        t.x_rows = min(p.x_tile_rows, p.m - t.x_row0);
+        t.y_col0 = t.w_row0;
+    }
+    return t;
+}
+
+// Epilogue of one tile for one of the four epilogue warps: taddr = TMEM address of the accumulator's first column in
+// this warp's lane quarter; xch = 2 KB of shared memory (SwiGLU epilogues only).
+__device__ __forceinline__ void tc_epilogue_tile(const TcParams& p, const TileInfo& ti, uint32_t taddr, uint8_t* xch, int quarter,
+                                                 int lane) {
+    const int wr = quarter * 32 + lane;          // weight row inside the tile
+    if (p.epilogue != QWC_EPI_NONE) {
+        // SwiGLU epilogues (the reference's qwg_gemm_q4g_h16_swiglu, include/qw_gemm_nax_swiglu.metalh:8-154): TMEM
+        // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows, so the two halves of a pair sit in
+        // different warps.  Per 16 tokens each warp parks the 8 tokens its partner will finish (f16, as the
+        // reference's threadgroup tile) in shared memory: the gate warps finish tokens 0..7 with the partner's up
+        // values, the up warps tokens 8..15 with the partner's gate values, so all four warps share the SwiGLU,
+        // the FWHT-32 across the 32 rows a warp holds, and the stores.
+        const bool is_up = quarter >= 2;
+        const int hrow = (quarter & 1) * 32 + lane;   // row of h inside the tile
+        uint4* park = reinterpret_cast<uint4*>(xch + (is_up ? 0 : 1024) + hrow * 16);        // what this warp gives
+        const uint4* take = reinterpret_cast<const uint4*>(xch + (is_up ? 1024 : 0) + hrow * 16);   // what it gets
+        const float sgn[5] = {(lane & 1) ? -1.0f : 1.0f, (lane & 2) ? -1.0f : 1.0f, (lane & 4) ? -1.0f : 1.0f,
+                              (lane & 8) ? -1.0f : 1.0f, (lane & 16) ? -1.0f : 1.0f};
+        const int chunks16 = (ti.x_rows + 15) / 16;
+#pragma unroll 1
+        for (int c = 0; c < chunks16; ++c) {
+            uint32_t rr[16];
+            tmem_ld16(taddr + c * 16, rr);
+            tmem_ld_wait();
+            {
+                const int g0 = is_up ? 0 : 8;   // the gate warps give tokens 8..15, the up warps tokens 0..7
+                uint32_t pk[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __half2 h2 = __floats2half2_rn(__uint_as_float(rr[g0 + 2 * i]), __uint_as_float(rr[g0 + 2 * i + 1]));
+                    pk[i] = *reinterpret_cast<const uint32_t*>(&h2);
+                }
+                *park = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const uint4 got = *take;
+            const uint32_t other[4] = {got.x, got.y, got.z, got.w};
+            const int m0 = is_up ? 8 : 0;       // the tokens this warp finishes
+            const int tok0 = c * 16 + m0;
+            uint8_t* yrow = static_cast<uint8_t*>(p.y) +
+                            (static_cast<int64_t>(ti.x_row0 + tok0) * p.ldy + ti.y_col0 + hrow) * (p.y_f16 ? 2 : 4);
+            const int64_t ystep = p.ldy * (p.y_f16 ? 2 : 4);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                const __half2 o2 = *reinterpret_cast<const __half2*>(&other[jj >> 1]);
+                const float o = (jj & 1) ? __high2float(o2) : __low2float(o2);
+                const float mine = __half2float(__float2half_rn(__uint_as_float(rr[m0 + jj])));
+                const float g = is_up ? o : mine, u = is_up ? mine : o;
+                float h = __half2float(__float2half_rn(__fdividef(g, 1.0f + __expf(-g)) * u));
+                if (p.epilogue == QWC_EPI_SILU_PAIR_FWHT) {
+#pragma unroll
+                    for (int st = 0; st < 5; ++st) h = fmaf(h, sgn[st], __shfl_xor_sync(0xFFFFFFFFu, h, 1 << st));
+                    h = __fmul_rn(h, qwc_inv_sqrt32());
+                }
+                if (tok0 + jj < ti.x_rows) {
+                    if (p.y_f16) *reinterpret_cast<__half*>(yrow) = __float2half_rn(h);
+                    else *reinterpret_cast<float*>(yrow) = __half2float(__float2half_rn(h));
+                }
+                yrow += ystep;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // the exchange buffer is reused by the next 16 tokens
+        }
+    } else {
+    // plain epilogue: lane = weight row, 32 token columns per TMEM load; a lane's stores walk down one output column
+    const int chunks = (ti.x_rows + 31) / 32;    // only the token columns the MMA wrote
+    const int esz = p.y_f16 ? 2 : 4;
+    const int64_t ystep = p.ldy * esz;
+    uint8_t* ycolp = static_cast<uint8_t*>(p.y) + (static_cast<int64_t>(ti.x_row0) * p.ldy + ti.y_col0 + wr) * esz;
+    const bool row_ok = wr < ti.w_rows;
+#pragma unroll 1
+    for (int c = 0; c < chunks; ++c) {
+        uint32_t rr[32];
+        tmem_ld32(taddr + c * 32, rr);
+        tmem_ld_wait();
+        const int left = ti.x_rows - c * 32;   // valid tokens in this chunk (>= 1)
+        if (row_ok) {
+            uint8_t* yp = ycolp;
+            if (left >= 32) {
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj) {
+                    if (p.y_f16) *reinterpret_cast<__half*>(yp) = __float2half_rn(__uint_as_float(rr[jj]));
+                    else *reinterpret_cast<float*>(yp) = __uint_as_float(rr[jj]);
+                    yp += ystep;
+                }
+            } else {
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj) {
+                    if (jj < left) {
+                        if (p.y_f16) *reinterpret_cast<__half*>(yp) = __float2half_rn(__uint_as_float(rr[jj]));
+                        else *reinterpret_cast<float*>(yp) = __uint_as_float(rr[jj]);
+                    }
+                    yp += ystep;
+                }
+            }
+        }
+        ycolp += 32 * ystep;
+    }
+    }
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
@@ -258,33 +387,7 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     const uint32_t tmem_base = *tmem_slot;
 
     const int total_tiles = p.tiles != nullptr ? *p.tile_count : p.m_tiles * p.n_tiles;
-    auto get_tile = [&](int tile) {
-        TileInfo t;
-        if (p.tiles != nullptr) {
-            const qwc_moe_tile g = p.tiles[tile];
-            t.w_row0 = g.w_row0;
-            t.w_row1 = g.pad0;
-            t.w_rows = g.w_rows;
-            t.x_row0 = g.x_row0;
-            t.x_rows = g.x_rows;
-            t.y_col0 = g.y_col0;
-        } else {
-            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;   // token tiles fastest: CTAs share weight rows in L2
-            if (p.epilogue == QWC_EPI_NONE) {
-                t.w_row0 = nt * kBM;
-                t.w_row1 = 0;
-                t.w_rows = min(kBM, p.n - t.w_row0);
-            } else {
-                t.w_row0 = nt * (kBM / 2);
-                t.w_row1 = t.w_row0 + p.up_delta;
-                t.w_rows = kBM;
-            }
-            t.x_row0 = mt * p.x_tile_rows;
-            t.x_rows = min(p.x_tile_rows, p.m - t.x_row0);
-            t.y_col0 = t.w_row0;
-        }
-        return t;
-    };
+    auto get_tile = [&](int tile) { return tc_get_tile(p, tile); };
     const int ktiles = p.k / kBK;
     const int raw_steps = p.k / kRawK;
 
@@ -460,101 +563,8 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                 break;
             }
             tc_fence_after();
-            const int wr = quarter * 32 + lane;          // weight row inside the tile
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * kBN);
-            if (p.epilogue != QWC_EPI_NONE) {
-                // SwiGLU epilogues (the reference's qwg_gemm_q4g_h16_swiglu, include/qw_gemm_nax_swiglu.metalh:8-154): TMEM
-                // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows, so the two halves of a pair sit in
-                // different warps.  Per 16 tokens each warp parks the 8 tokens its partner will finish (f16, as the
-                // reference's threadgroup tile) in shared memory: the gate warps finish tokens 0..7 with the partner's up
-                // values, the up warps tokens 8..15 with the partner's gate values, so all four warps share the SwiGLU,
-                // the FWHT-32 across the 32 rows a warp holds, and the stores.
-                const bool is_up = quarter >= 2;
-                const int hrow = (quarter & 1) * 32 + lane;   // row of h inside the tile
-                uint4* park = reinterpret_cast<uint4*>(xch + (is_up ? 0 : 1024) + hrow * 16);        // what this warp gives
-                const uint4* take = reinterpret_cast<const uint4*>(xch + (is_up ? 1024 : 0) + hrow * 16);   // what it gets
-                const float sgn[5] = {(lane & 1) ? -1.0f : 1.0f, (lane & 2) ? -1.0f : 1.0f, (lane & 4) ? -1.0f : 1.0f,
-                                      (lane & 8) ? -1.0f : 1.0f, (lane & 16) ? -1.0f : 1.0f};
-                const int chunks16 = (ti.x_rows + 15) / 16;
-#pragma unroll 1
-                for (int c = 0; c < chunks16; ++c) {
-                    uint32_t rr[16];
-                    tmem_ld16(taddr + c * 16, rr);
-                    tmem_ld_wait();
-                    {
-                        const int g0 = is_up ? 0 : 8;   // the gate warps give tokens 8..15, the up warps tokens 0..7
-                        uint32_t pk[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const __half2 h2 = __floats2half2_rn(__uint_as_float(rr[g0 + 2 * i]), __uint_as_float(rr[g0 + 2 * i + 1]));
-                            pk[i] = *reinterpret_cast<const uint32_t*>(&h2);
-                        }
-                        *park = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    const uint4 got = *take;
-                    const uint32_t other[4] = {got.x, got.y, got.z, got.w};
-                    const int m0 = is_up ? 8 : 0;       // the tokens this warp finishes
-                    const int tok0 = c * 16 + m0;
-                    uint8_t* yrow = static_cast<uint8_t*>(p.y) +
-                                    (static_cast<int64_t>(ti.x_row0 + tok0) * p.ldy + ti.y_col0 + hrow) * (p.y_f16 ? 2 : 4);
-                    const int64_t ystep = p.ldy * (p.y_f16 ? 2 : 4);
-#pragma unroll
-                    for (int jj = 0; jj < 8; ++jj) {
-                        const __half2 o2 = *reinterpret_cast<const __half2*>(&other[jj >> 1]);
-                        const float o = (jj & 1) ? __high2float(o2) : __low2float(o2);
-                        const float mine = __half2float(__float2half_rn(__uint_as_float(rr[m0 + jj])));
-                        const float g = is_up ? o : mine, u = is_up ? mine : o;
-                        float h = __half2float(__float2half_rn(__fdividef(g, 1.0f + __expf(-g)) * u));
-                        if (p.epilogue == QWC_EPI_SILU_PAIR_FWHT) {
-#pragma unroll
-                            for (int st = 0; st < 5; ++st) h = fmaf(h, sgn[st], __shfl_xor_sync(0xFFFFFFFFu, h, 1 << st));
-                            h = __fmul_rn(h, qwc_inv_sqrt32());
-                        }
-                        if (tok0 + jj < ti.x_rows) {
-                            if (p.y_f16) *reinterpret_cast<__half*>(yrow) = __float2half_rn(h);
-                            else *reinterpret_cast<float*>(yrow) = __half2float(__float2half_rn(h));
-                        }
-                        yrow += ystep;
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");   // the exchange buffer is reused by the next 16 tokens
-                }
-            } else {
-            // plain epilogue: lane = weight row, 32 token columns per TMEM load; a lane's stores walk down one output column
-            const int chunks = (ti.x_rows + 31) / 32;    // only the token columns the MMA wrote
-            const int esz = p.y_f16 ? 2 : 4;
-            const int64_t ystep = p.ldy * esz;
-            uint8_t* ycolp = static_cast<uint8_t*>(p.y) + (static_cast<int64_t>(ti.x_row0) * p.ldy + ti.y_col0 + wr) * esz;
-            const bool row_ok = wr < ti.w_rows;
-#pragma unroll 1
-            for (int c = 0; c < chunks; ++c) {
-                uint32_t rr[32];
-                tmem_ld32(taddr + c * 32, rr);
-                tmem_ld_wait();
-                const int left = ti.x_rows - c * 32;   // valid tokens in this chunk (>= 1)
-                if (row_ok) {
-                    uint8_t* yp = ycolp;
-                    if (left >= 32) {
-#pragma unroll
-                        for (int jj = 0; jj < 32; ++jj) {
-                            if (p.y_f16) *reinterpret_cast<__half*>(yp) = __float2half_rn(__uint_as_float(rr[jj]));
-                            else *reinterpret_cast<float*>(yp) = __uint_as_float(rr[jj]);
-                            yp += ystep;
-                        }
-                    } else {
-#pragma unroll
-                        for (int jj = 0; jj < 32; ++jj) {
-                            if (jj < left) {
-                                if (p.y_f16) *reinterpret_cast<__half*>(yp) = __float2half_rn(__uint_as_float(rr[jj]));
-                                else *reinterpret_cast<float*>(yp) = __uint_as_float(rr[jj]);
-                            }
-                            yp += ystep;
-                        }
-                    }
-                }
-                ycolp += 32 * ystep;
-            }
-            }
+            tc_epilogue_tile(p, ti, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * kBN), xch,
+                             quarter, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[as]);
@@ -562,6 +572,319 @@ qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     }
 
     // teardown: everyone meets, then the allocating warp returns the tensor memory
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Variant with the decoded weights staged in TENSOR memory (tcgen05.mma with the A operand in TMEM) instead of a
+// swizzled shared-memory tile: the converters write their f16 pairs with tcgen05.st, so the decoded tile never crosses
+// shared memory (16 KB written + 16 KB read per K tile less on the unit that bounds the kernel) and no generic-to-async
+// proxy fence (several hundred cycles per converter step) is needed.  TMEM budget: two 128 x 192 f32 accumulators
+// (columns 0..383) + four A stages of 32 columns (128 lanes x 64 k of f16 pairs; columns 384..511), so a tile holds at
+// most 192 tokens.  Converter thread = one weight row (TMEM lane); warp w serves lane quarter w % 4.
+constexpr int kTsBN = 192;                 // tokens per tile (UMMA N) and accumulator stride in TMEM columns
+constexpr int kTsAccCols = 2 * kTsBN;      // A stages start here
+constexpr int kTsFirstConvWarp = 4;        // warps 0..2 as above, warp 3 idle so that converter warp c serves quarter c % 4
+constexpr int kTsWarps = kTsFirstConvWarp + kConvWarps + kEpiWarps;
+constexpr int kTsThreads = kTsWarps * 32;
+constexpr int kTsMaxRaw = 8;
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t r[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem desc]: M = 128, K = 16, A = 128 lanes x 8 columns of f16 pairs.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Decode UNITS consecutive 32-element units held in registers (header word + payload words each) into f16 pairs in
+// natural k order: out[16 u + c] = elements (2c, 2c + 1) of unit u.
+template <int FMT, int UNITS>
+__device__ __forceinline__ void decode_regs_natural(const uint32_t* w, uint32_t* out) {
+    constexpr int kWordsPerUnit = FMT == FMT_HQ4_G32_M5 ? 5 : 9;
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        const uint32_t hdr = w[u * kWordsPerUnit];
+        const __half2 h = *reinterpret_cast<const __half2*>(&hdr);
+        const __half2 s2 = __half2half2(__low2half(h)), b2 = __half2half2(__high2half(h));
+        if (FMT == FMT_HQ4_G32_M5) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t v = w[u * 5 + 1 + i];
+                out[16 * u + 4 * i + 0] = hfma2_u32(nib2_f16x2(v), s2, b2);
+                out[16 * u + 4 * i + 1] = hfma2_u32(nib2_f16x2(v >> 4), s2, b2);
+                out[16 * u + 4 * i + 2] = hfma2_u32(nib2_f16x2(v >> 8), s2, b2);
+                out[16 * u + 4 * i + 3] = hfma2_u32(nib2_f16x2(v >> 12), s2, b2);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t v = w[u * 9 + 1 + i];
+                out[16 * u + 2 * i + 0] = hfma2_u32(hsub2_1024(__byte_perm(v, 0x64646464u, 0x4140)), s2, b2);
+                out[16 * u + 2 * i + 1] = hfma2_u32(hsub2_1024(__byte_perm(v, 0x64646464u, 0x4342)), s2, b2);
+            }
+        }
+    }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(kTsThreads, 1)
+qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
+                   const __grid_constant__ CUtensorMap xmap128, const __grid_constant__ CUtensorMap xmap64,
+                   const __grid_constant__ CUtensorMap wmap64) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // layout (1024-byte aligned base): [X tiles][raw stages][barriers][SwiGLU exchange]
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* xt = smem;
+    uint8_t* raw = xt + kStages * p.x_slot_bytes;
+    const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + p.raw_stages * raw_stage_bytes);
+    uint64_t* full = bars;                        // [kStages]  activations landed (tx) + the four quarter warps stored A
+    uint64_t* empty = bars + kStages;             // [kStages]  tcgen05.commit: the MMAs have read both operands of the stage
+    uint64_t* raw_full = bars + 2 * kStages;      // [kTsMaxRaw]
+    uint64_t* raw_empty = raw_full + kTsMaxRaw;   // [kTsMaxRaw]
+    uint64_t* acc_full = raw_empty + kTsMaxRaw;   // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint32_t* raw_issued = tmem_slot + 2;
+    uint8_t* xch = reinterpret_cast<uint8_t*>(bars) + 512;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1 + 4);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < p.raw_stages; ++s) {
+            mbar_init(&raw_full[s], 1);
+            mbar_init(&raw_empty[s], kGroupWarps);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], kEpiWarps);
+        }
+        *abort_flag = 0;
+        *raw_issued = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = p.tiles != nullptr ? *p.tile_count : p.m_tiles * p.n_tiles;
+    const int ktiles = p.k / kBK;
+    const int raw_steps = p.k / kRawK;
+    auto fail = [&](int code) {
+        if (!*abort_flag) atomicCAS(p.status, 0, code);
+        *abort_flag = 1;
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer: rotated activations (one tile per K tile) ----------------
+        if (lane == 0) {
+            uint32_t j = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileInfo ti = tc_get_tile(p, tile);
+                const CUtensorMap* xm = ti.x_rows <= 64 ? &xmap64 : (ti.x_rows <= 128 ? &xmap128 : &xmap);
+                const uint32_t xbytes = (ti.x_rows <= 64 ? 64u : (ti.x_rows <= 128 ? 128u : static_cast<uint32_t>(p.x_tile_rows))) * kBK * 2u;
+                for (int kt = 0; kt < ktiles; ++kt, ++j) {
+                    const uint32_t s = j % kStages;
+                    if (j >= kStages && !mbar_wait_relaxed(&empty[s], ((j / kStages) - 1) & 1u)) {
+                        fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&full[s], xbytes);
+                    tma_load_2d(xt + s * p.x_slot_bytes, xm, kt * kBK, ti.x_row0, &full[s]);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 2) {
+        // ---------------- TMA producer: packed weight rows (one raw step = two K tiles) ----------------
+        if (lane == 0) {
+            uint32_t r = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileInfo ti = tc_get_tile(p, tile);
+                for (int rs = 0; rs < raw_steps; ++rs, ++r) {
+                    const uint32_t s = r % p.raw_stages;
+                    if (r >= static_cast<uint32_t>(p.raw_stages) && !mbar_wait_relaxed(&raw_empty[s], ((r / p.raw_stages) - 1) & 1u)) {
+                        fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&raw_full[s], static_cast<uint32_t>(kBM * p.raw_row_bytes));
+                    if (p.epilogue == QWC_EPI_NONE) {
+                        tma_load_2d(raw + s * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[s]);
+                    } else {   // 64 gate rows, then the 64 up rows that pair with them
+                        tma_load_2d(raw + s * raw_stage_bytes, &wmap64, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[s]);
+                        tma_load_2d(raw + s * raw_stage_bytes + (kBM / 2) * p.raw_row_bytes, &wmap64, rs * (p.raw_row_bytes / 8),
+                                    ti.w_row1, &raw_full[s]);
+                    }
+                    asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(raw_issued)), "r"(r + 1) : "memory");
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer (whole warp in lockstep, one elected lane issues) ----------------
+        uint32_t j = 0, tiles_done = 0;
+        bool ok = true;
+        const uint64_t b_d0 = umma_desc_sw128(smem_u32(xt));
+        const uint32_t b_lo0 = static_cast<uint32_t>(b_d0), b_hi = static_cast<uint32_t>(b_d0 >> 32);
+        const uint32_t b_step = static_cast<uint32_t>(p.x_slot_bytes) >> 4;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tiles_done) {
+            const int as = tiles_done & 1;
+            if (tiles_done >= 2 && !mbar_wait_spin(&acc_empty[as], ((tiles_done >> 1) - 1) & 1)) {
+                if (lane == 0) fail(QWC_DEV_WAIT_TMEM_TIMEOUT);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * kTsBN);
+            const uint32_t idesc = make_idesc(min(kTsBN, (tc_get_tile(p, tile).x_rows + 15) & ~15));
+            for (int kt = 0; kt < ktiles; ++kt, ++j) {
+                const uint32_t s = j % kStages;
+                if (!mbar_wait_spin(&full[s], (j / kStages) & 1u)) {
+                    if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();   // the converters' tcgen05.st happen-before these MMAs
+                const uint32_t b_lo = b_lo0 + s * b_step;
+                const uint32_t a_tmem = tmem_base + static_cast<uint32_t>(kTsAccCols + s * 32);
+                if (elect_one()) {
+#pragma unroll
+                    for (int q = 0; q < kBK / 16; ++q)
+                        umma_f16_ts(d_tmem, a_tmem + q * 8, pack_desc(b_lo + 2 * q, b_hi), idesc, (kt > 0 || q > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);
+                }
+                __syncwarp();
+            }
+            if (ok && elect_one()) umma_commit(&acc_full[as]);
+            __syncwarp();
+        }
+        __syncwarp();
+    } else if (warp >= kTsFirstConvWarp && warp < kTsFirstConvWarp + kConvWarps) {
+        // ------------------------------- converters -------------------------------
+        // Converter warp c: lane quarter c & 3, group (c >> 3) takes every other raw step, and inside a step the warp
+        // decodes K tile (c >> 2) & 1 of the two.  A thread owns one weight row: it reads that row's half of the raw
+        // step (two units) with 16-byte loads (the lane stride of 80 / 144 bytes puts a quarter warp's 16-byte chunks in
+        // 8 distinct bank groups), decodes, and stores 32 columns of f16 pairs into its TMEM lane.
+        const int c = warp - kTsFirstConvWarp;
+        const int qd = c & 3, kt2 = (c >> 2) & 1, grp = c >> 3;
+        constexpr int kHalfWords = FMT == FMT_HQ4_G32_M5 ? 10 : 18;   // words of two units
+        bool ok = true;
+        uint32_t r = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int rs = 0; rs < raw_steps; ++rs, ++r) {
+                if (static_cast<int>(r & 1u) != grp) continue;
+                const uint32_t rslot = r % p.raw_stages, rpar = (r / p.raw_stages) & 1u;
+                const uint32_t j = 2 * r + kt2, s = j % kStages, use = j / kStages;
+                bool started = false;
+                for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(raw_issued)) : "memory");
+                    if (v > r) {
+                        started = true;
+                        break;
+                    }
+                    __nanosleep(spin < 64 ? 20 : 200);
+                }
+                if (!started || !mbar_wait(&raw_full[rslot], rpar) || (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1u))) {
+                    if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();   // the MMAs that read this A stage are complete (tcgen05.commit -> empty[s])
+                const uint8_t* src = raw + rslot * raw_stage_bytes + (qd * 32 + lane) * p.raw_row_bytes + kt2 * (kHalfWords * 4);
+                uint32_t w[kHalfWords];
+                if (FMT == FMT_HQ4_G32_M5) {
+                    // 40 bytes at offset 0 (16-byte aligned) or 40 (8-byte aligned)
+                    if (kt2 == 0) {
+                        const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + 16);
+                        const uint2 d = *reinterpret_cast<const uint2*>(src + 32);
+                        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w; w[8] = d.x; w[9] = d.y;
+                    } else {
+                        const uint2 d = *reinterpret_cast<const uint2*>(src);
+                        const uint4 a = *reinterpret_cast<const uint4*>(src + 8), b = *reinterpret_cast<const uint4*>(src + 24);
+                        w[0] = d.x; w[1] = d.y; w[2] = a.x; w[3] = a.y; w[4] = a.z; w[5] = a.w; w[6] = b.x; w[7] = b.y; w[8] = b.z; w[9] = b.w;
+                    }
+                } else {
+                    // 72 bytes at offset 0 (16-byte aligned) or 72 (8-byte aligned)
+                    if (kt2 == 0) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint4 a = *reinterpret_cast<const uint4*>(src + 16 * i);
+                            w[4 * i] = a.x; w[4 * i + 1] = a.y; w[4 * i + 2] = a.z; w[4 * i + 3] = a.w;
+                        }
+                        const uint2 d = *reinterpret_cast<const uint2*>(src + 64);
+                        w[16] = d.x; w[17] = d.y;
+                    } else {
+                        const uint2 d = *reinterpret_cast<const uint2*>(src);
+                        w[0] = d.x; w[1] = d.y;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint4 a = *reinterpret_cast<const uint4*>(src + 8 + 16 * i);
+                            w[2 + 4 * i] = a.x; w[3 + 4 * i] = a.y; w[4 + 4 * i] = a.z; w[5 + 4 * i] = a.w;
+                        }
+                    }
+                }
+                uint32_t a32[32];
+                decode_regs_natural<FMT, 2>(w, a32);
+                tmem_st32(tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + static_cast<uint32_t>(kTsAccCols + s * 32), a32);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&full[s]);
+                    mbar_arrive(&raw_empty[rslot]);
+                }
+            }
+        }
+    } else if (warp >= kTsFirstConvWarp + kConvWarps) {
+        // ------------------------------- epilogue -------------------------------
+        const int quarter = warp & 3;
+        uint32_t tiles_done = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tiles_done) {
+            const TileInfo ti = tc_get_tile(p, tile);
+            const int as = tiles_done & 1;
+            if (!mbar_wait_relaxed(&acc_full[as], (tiles_done >> 1) & 1)) {
+                if (lane == 0) fail(QWC_DEV_WAIT_MMA_TIMEOUT);
+                break;
+            }
+            tc_fence_after();
+            tc_epilogue_tile(p, ti, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * kTsBN), xch,
+                             quarter, lane);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[as]);
+        }
+    }
+
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -596,6 +919,19 @@ int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUte
         configured[hal->device & 63] = true;
     }
     qwc_gemm_tc_kernel<FMT><<<grid, kTcThreads, smem, st>>>(p, wmap, xmaps[0], xmaps[1], xmaps[2], wmap64);
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
+
+template <int FMT>
+int launch_ts(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap64,
+              const CUtensorMap* xmaps, int smem, int grid) {
+    static bool configured[64] = {};
+    if (!configured[hal->device & 63]) {
+        QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemm_ts_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured[hal->device & 63] = true;
+    }
+    qwc_gemm_ts_kernel<FMT><<<grid, kTsThreads, smem, st>>>(p, wmap, xmaps[0], xmaps[1], xmaps[2], wmap64);
     QWC_CUDA_TRY(cudaGetLastError());
     return QWC_OK;
 }
@@ -637,6 +973,8 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     p.y_f16 = y_dtype == QWC_F16;
     p.raw_row_bytes = fmt == FMT_HQ4_G32_M5 ? 80 : 144;
     if (tiles == nullptr && fmt != FMT_HQ4_G32_M5) x_tile_rows = 192;   // 36-byte blocks: the raw stages are 1.8x larger
+    static const bool use_ts = getenv("QWC_TC_SS") == nullptr;   // default: decoded weights staged in tensor memory (tiles of <= 192 tokens)
+    if (use_ts && x_tile_rows > kTsBN) x_tile_rows = kTsBN;
     p.x_tile_rows = x_tile_rows;
     p.m_tiles = static_cast<int>((m + x_tile_rows - 1) / x_tile_rows);
     p.epilogue = epilogue;
@@ -645,8 +983,10 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     p.n_tiles = epilogue == QWC_EPI_NONE ? static_cast<int>((w->n + kBM - 1) / kBM) : static_cast<int>(w->n / kBM);
     const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
     p.x_slot_bytes = x_tile_rows * kBK * 2;
-    p.raw_stages = kMaxRaw;
-    auto smem_need = [&](int rs) { return 1024 + kStages * (p.x_slot_bytes + kWTileBytes) + rs * raw_stage_bytes + 512 + p.xch_bytes; };
+    p.raw_stages = use_ts ? kTsMaxRaw : kMaxRaw;
+    auto smem_need = [&](int rs) {
+        return 1024 + kStages * (p.x_slot_bytes + (use_ts ? 0 : kWTileBytes)) + rs * raw_stage_bytes + 512 + p.xch_bytes;
+    };
     while (smem_need(p.raw_stages) > 227 * 1024 && p.raw_stages > 2) --p.raw_stages;
     if (smem_need(p.raw_stages) > 227 * 1024) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "shared-memory budget exceeded");
     const int smem = smem_need(p.raw_stages);
@@ -677,6 +1017,10 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     }
     const int64_t ntiles = tiles != nullptr ? max_tiles : static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     const int grid = static_cast<int>(ntiles < hal->sm_count ? (ntiles < 1 ? 1 : ntiles) : hal->sm_count);
+    if (use_ts) {
+        if (fmt == FMT_HQ4_G32_M5) return launch_ts<FMT_HQ4_G32_M5>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
+        return launch_ts<FMT_HQ8_G32>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
+    }
     if (fmt == FMT_HQ4_G32_M5) return launch_tc<FMT_HQ4_G32_M5>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
     return launch_tc<FMT_HQ8_G32>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
 }

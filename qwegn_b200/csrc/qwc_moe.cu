@@ -6,6 +6,8 @@
 //   qwg_silu_mul_split_f16             Sources/QWMetal/gemm/qwgemm_batched.metal:55-97
 //   qwg_moe_down_reduce_combine_f32    Sources/QWMetal/gemm/qwgemm_moe_nax_f16.metal:7-126
 // The grouped expert GEMMs run on the tensor-core kernel of qwc_gemm_tc.cu over the tile list built here.
+#include <cstdlib>
+
 #include "qwc_common.cuh"
 
 int qwc_launch_gemm_tc_grouped(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, const qwc_moe_tile*,
@@ -19,7 +21,11 @@ constexpr int kTileW = 128;  // weight rows per grouped-GEMM tile
 // count, so fewer, taller tiles win (64-row tiles were measured 30 % slower at 64 rows per expert); 192 rows is the
 // tallest tile whose stages fit in shared memory for the 36-byte containers too.  The kernel still fetches only a
 // 64- or 128-row activation box when the tile is that small.
-__host__ __device__ inline int moe_tile_rows(int64_t pairs, int64_t e) { return (pairs >= 0 && e > 0) ? 192 : 192; }
+inline int moe_tile_rows(int64_t pairs, int64_t e) {
+    static const int env_rows = getenv("QWC_MOE_TILE_ROWS") ? atoi(getenv("QWC_MOE_TILE_ROWS")) : 0;   // tuning knob
+    if (env_rows == 64 || env_rows == 128 || env_rows == 192) return env_rows;
+    return (pairs >= 0 && e > 0) ? 192 : 192;
+}
 
 __device__ __forceinline__ bool finite_bits(float v) { return (__float_as_uint(v) & 0x7F800000u) != 0x7F800000u; }
 
@@ -687,8 +693,8 @@ int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view*
                          int32_t y_dtype, int64_t ldy, int32_t epilogue) {
     qwc_clear_error();
     if (epilogue < QWC_EPI_NONE || epilogue > QWC_EPI_SILU_PAIR_FWHT) return qwc_fail(QWC_ERR_BAD_SHAPE, "unknown epilogue %d", epilogue);
-    if (x_tile_rows != 64 && x_tile_rows != 192 && x_tile_rows != 256)
-        return qwc_fail(QWC_ERR_BAD_GEOMETRY, "x_tile_rows must be 64, 192 or 256 (qwc_moe_tile_rows)");
+    if (x_tile_rows != 64 && x_tile_rows != 128 && x_tile_rows != 192 && x_tile_rows != 256)
+        return qwc_fail(QWC_ERR_BAD_GEOMETRY, "x_tile_rows must be 64, 128, 192 or 256 (qwc_moe_tile_rows)");
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
     if (!bank || !bank->blocks) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "bank is null");
     if (pairs <= 0 || max_tiles <= 0) return QWC_OK;
