@@ -91,7 +91,11 @@ def test_group_pairs_matches_the_oracle(hal, oracle, t, e, k):
     assert counts[1] == counts[0] * 2
 
 
-@pytest.mark.parametrize("cfg", [(64, 8, 2, 256, 128), (300, 32, 4, 512, 256), (40, 16, 8, 128, 128)])
+# (tokens, experts, top-k, hidden, inter): prefill-sized blocks, the decode / verify sizes of the reference's per-pair path
+# (T <= 8, QWGemmMoE.swift:117-199: the grouped path serves them here), all with SwiGLU + FWHT fused into the gate/up epilogue (inter % 128 == 0
+# for the tensor path implies inter % 64 == 0; the unfused chain is covered door by door below)
+@pytest.mark.parametrize("cfg", [(64, 8, 2, 256, 128), (300, 32, 4, 512, 256), (40, 16, 8, 128, 128), (1, 32, 8, 256, 128),
+                                 (8, 64, 4, 256, 128), (5, 16, 2, 128, 128)])
 @pytest.mark.parametrize("name", ["HQ4_G32", "HQ8_G32"])
 def test_moe_forward_vs_oracle(hal, oracle, cfg, name):
     import qwegn_b200 as q
@@ -116,6 +120,55 @@ def test_moe_forward_vs_oracle(hal, oracle, cfg, name):
     out16 = torch.empty((t, hidden), dtype=torch.float16, device="cuda")
     op.encodeResident(torch.from_numpy(x).cuda(), torch.from_numpy(lg).cuda(), out16, scratch)
     assert_matmul_close(out16.float().cpu().numpy(), ref, tight=8e-3)
+
+
+@pytest.mark.parametrize("name", ["HQ4_G32", "HQ8_G32"])
+def test_gate_up_doors_fused_and_unfused_agree(hal, oracle, name):
+    # Door by door: pair sort -> gather -> grouped gate/up GEMM -> SwiGLU + FWHT as its own kernel, against the same
+    # chain with SwiGLU + FWHT in the GEMM's epilogue (paired tile list), and both against the oracle.
+    import ctypes
+    import qwegn_b200 as q
+    from qwegn_b200 import _lib
+    from qwegn_b200.gemm import _stream_ptr
+    lib = _lib.load()
+    t, e, k, hidden, inter = 96, 8, 2, 256, 128
+    fmt = oracle.FORMATS[name]
+    rng = np.random.default_rng(77)
+    gu, _ = _expert_banks(oracle, fmt, e, hidden, inter, rng)
+    bank = q.QWWeightView(torch.from_numpy(gu.reshape(-1)).cuda(), e * 2 * inter, hidden, q.CONTAINERS[name])
+    x = torch.from_numpy(rng.standard_normal((t, hidden)).astype(np.float16)).cuda()
+    idx = torch.from_numpy(rng.integers(0, e, size=(t, k)).astype(np.int32)).cuda()
+    pairs = t * k
+    rows = lib.qwc_moe_tile_rows(pairs, e)
+    hs = {}
+    for epi in (0, 2):
+        off, _, stok, _, tg, _, tc = q.QWGemmMoE.encodeMoEGroupPairs(hal, idx, e, 2 * inter, hidden, gu_epilogue=epi)
+        xs = torch.empty((pairs, hidden), dtype=torch.float16, device="cuda")
+        assert lib.qwc_moe_gather(hal.handle, _stream_ptr(None), x.data_ptr(), hidden, hidden, stok.data_ptr(), off.data_ptr(), e,
+                                  pairs, 0, xs.data_ptr()) == 0
+        h = torch.full((pairs, inter), float("nan"), dtype=torch.float16, device="cuda")
+        if epi == 0:
+            guo = torch.empty((pairs, 2 * inter), dtype=torch.float16, device="cuda")
+            assert lib.qwc_moe_grouped_gemm(hal.handle, _stream_ptr(None), ctypes.byref(bank.c), xs.data_ptr(), pairs, tg.data_ptr(),
+                                            tc.data_ptr(), tg.shape[0], rows, guo.data_ptr(), 0, 2 * inter, 0) == 0
+            assert lib.qwc_moe_silu_mul(hal.handle, _stream_ptr(None), guo.data_ptr(), pairs, inter, 1, h.data_ptr()) == 0
+        else:
+            assert lib.qwc_moe_grouped_gemm(hal.handle, _stream_ptr(None), ctypes.byref(bank.c), xs.data_ptr(), pairs, tg.data_ptr(),
+                                            tc.data_ptr(), tg.shape[0], rows, h.data_ptr(), 0, inter, epi) == 0
+        hs[epi] = h.float().cpu().numpy()
+        sorted_tok = stok.cpu().numpy()
+        sorted_exp = np.repeat(np.arange(e), np.diff(off.cpu().numpy()))
+    # oracle: per sorted pair, its expert's gate||up rows
+    xh = x.cpu().numpy()
+    ref = np.empty((pairs, inter), dtype=np.float32)
+    for ex in range(e):
+        sel = np.nonzero(sorted_exp == ex)[0]
+        if sel.size:
+            g = oracle.matmul(gu[ex * 2 * inter:(ex + 1) * 2 * inter], fmt, xh[sorted_tok[sel]])
+            ref[sel] = oracle.swiglu_f16(g, rotate=True).astype(np.float32)
+    assert_matmul_close(hs[0], ref, tight=5e-3)
+    assert_matmul_close(hs[2], ref, tight=5e-3)
+    assert hal.device_status() == 0
 
 
 def test_moe_forward_refusals(hal, oracle):
