@@ -163,8 +163,8 @@ int qwc_gemm_plan(int64_t m, int64_t n, int64_t k, int32_t kind, int32_t bits, i
         snprintf(out->kernel, sizeof(out->kernel), "qwc_gemv_rowwise_%s", fname);
     } else if (m > 16 && epilogue == QWC_EPI_NONE && (fmt == FMT_HQ4_G32_M5 || fmt == FMT_HQ8_G32) && k % 128 == 0) {
         out->backend = QWC_BACKEND_TCGEN05;
-        out->threads_per_cta = 14 * 32;
-        snprintf(out->kernel, sizeof(out->kernel), "qwc_gemm_tc_%s_128x256x64", fname);
+        out->threads_per_cta = 24 * 32;
+        snprintf(out->kernel, sizeof(out->kernel), "qwc_gemm_ts_%s_128x192x64", fname);
     } else {
         out->backend = QWC_BACKEND_STREAM_MMA;
         out->threads_per_cta = 17 * 32;
