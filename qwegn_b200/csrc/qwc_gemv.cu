@@ -708,7 +708,9 @@ constexpr int kXCapBytes = 112 * 1024;  // at most this much shared memory for t
 template <int FMT>
 bool plan_geometry(int units, int m, int nt, int sub, int jobs, int budget, StreamGeom* g) {
     using C = StreamCfg<FMT>;
-    const int quantum = 8;      // units per chunk must be a multiple of this
+    // units per chunk must be a multiple of this (HQ4_G64: 36-byte blocks of two units; 16 units keep the row stride in
+    // words at 4 mod 8 there, 8 units would give 0 mod 8 every other size)
+    const int quantum = FMT == FMT_HQ4_G64 ? 16 : 8;
     // chunk bytes + 16 pad <= 2048: the box of the 2-D tensor copy is at most 256 8-byte elements wide
     const int max_chunk = FMT == FMT_HQ4_G32_M5 ? 96 : (FMT == FMT_HQ8_G32 ? 56 : 112);
     g->x_bytes = ((m * units * 64 + 127) / 128) * 128;
