@@ -209,7 +209,7 @@ def make_banks(q, hal, n, k, container, copies, seed):
     return banks
 
 
-def bench_gemv_point(q, hal, n, k, m, cname, steps, warmup, dist=None, seed=0):
+def bench_gemv_point(q, hal, n, k, m, cname, steps, warmup, dist=None, seed=0, rotated=False):
     """Device-resident timing of one (format, M) point; returns (ms_per_step, bytes_per_step, banks, x, y)."""
     import torch
     cont = q.CONTAINERS[cname]
@@ -224,8 +224,11 @@ def bench_gemv_point(q, hal, n, k, m, cname, steps, warmup, dist=None, seed=0):
     nws = q.QWGemm.workspaceBytes(hal, banks[0], m)
     ws = torch.empty(nws, dtype=torch.uint8, device="cuda") if nws else None
 
+    if rotated:   # the reference's dataflow: the norm kernel before the matmul hands over rotated activations
+        q.QWGemm.encodeRMSNorm(hal, x.clone(), torch.zeros(k, dtype=torch.float16, device="cuda"), x)
+
     def step(i):
-        q.QWGemm.encode(hal, banks[i % copies], x, y, workspace=ws)
+        q.QWGemm.encode(hal, banks[i % copies], x, y, workspace=ws, x_is_rotated=rotated)
 
     torch.cuda.synchronize()
     hal.set_static_weights(True)
@@ -353,6 +356,10 @@ def run_ours(args):
         if "c1" in sections:
             t, b, *_ = bench_gemv_point(q, hal, 12288, 4096, 1, "HQ4_G32", args.steps, args.warmup)
             extra["c1_gemv_N12288_K4096"] = {"GBps": b / (t * 1e-3) / 1e9, "us": t * 1e3, "frac_of_peak": b / (t * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        if "c1" in sections:
+            t, b, *_ = bench_gemv_point(q, hal, n, k, 1, "HQ4_G32", args.steps, args.warmup, rotated=True)
+            extra["c2_gemv_M1_rotated_activations_in"] = {"GBps": b / (t * 1e-3) / 1e9, "us": t * 1e3,
+                                                          "note": "x_is_rotated=1: activations rotated by qwc_rmsnorm_fwht outside the timed loop, as in the reference's engine"}
         if "sweep" in sections:
             sweep = {}
             for cname in ("HQ4_G32", "HQ8_G32", "HQ4_G64"):

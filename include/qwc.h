@@ -106,6 +106,16 @@ int qwc_gemm_plan(int64_t m, int64_t n, int64_t k, int32_t kind, int32_t bits, i
 /* QWGemm.encodeFwht32 (QWGemm.swift:285-300): in-place f16 Walsh-Hadamard per aligned 32 block; count % 32 == 0. */
 int qwc_fwht32_f16(qwc_hal* hal, qwc_stream stream, void* x_f16, int64_t count);
 
+/* RMSNorm with rotated f16 output, the step before every quantized matmul in the reference's engine (qwg_rmsnorm /
+ * qwg_rmsnorm_residual, Sources/QWMetal/mlp_norm_rope/qwnorm.metal:27-79, 249-259; encodeRMSNormFast /
+ * encodeRMSNormResidualFast, Sources/Runtime/QWEngine/Driver/EncodeKernels.swift:339-404):
+ *   s = x, or s = f16(x + residual) written back to residual when residual != NULL;
+ *   y = f16(fwht32(s * rsqrt(mean(s^2) + eps) * (1 + gamma)))   (rotate == 0 leaves out the rotation).
+ * x, y, residual f16 [rows, hidden] dense; gamma f16 [hidden] stored raw (the +1 is applied here); hidden % 256 == 0.
+ * Feed y to qwc_gemm with x_is_rotated = 1. */
+int qwc_rmsnorm_fwht(qwc_hal* hal, qwc_stream stream, const void* x_f16, const void* gamma_f16, void* y_f16,
+                     void* residual_f16, int64_t rows, int64_t hidden, float eps, int32_t rotate);
+
 /* Host decode twin Pack.dequantHQ4Slab / dequantHQBlockSlab (Sources/Foundation/QWQuant/QWPack.swift:205-321),
  * on the device: blocks -> [n, k] values, bit-exact with the reference decode.  standard_domain != 0 applies the
  * inverse rotation (FWHT-32).  out_dtype QWC_F32, or QWC_F16 (one extra rounding). */

@@ -164,6 +164,24 @@ def swiglu_f16(gu: np.ndarray, rotate: bool = False) -> np.ndarray:
     return h
 
 
+def rmsnorm_fwht(x: np.ndarray, gamma: np.ndarray, eps: float = 1e-6, residual: np.ndarray | None = None, rotate: bool = True):
+    """RMSNorm of the reference's norm family (qwg_rmsnorm / qwg_rmsnorm_residual,
+    Sources/QWMetal/mlp_norm_rope/qwnorm.metal:19-79, 200-259): s = x or f16(x + residual); y = f16(fwht32(s * rsqrt(mean(s^2)
+    + eps) * (1 + gamma))) with f32 products and butterflies; the sum of squares is taken in f64 here (the device's f32
+    sum differs from it in the last bits only).  Returns (y f16, new residual f16 or None)."""
+    s = np.asarray(x, dtype=np.float16).astype(np.float32)
+    new_res = None
+    if residual is not None:
+        s = (s + np.asarray(residual, dtype=np.float16).astype(np.float32)).astype(np.float16)
+        new_res = s.copy()
+        s = s.astype(np.float32)
+    rstd = (1.0 / np.sqrt((s.astype(np.float64) ** 2).mean(axis=-1, keepdims=True) + eps)).astype(np.float32)
+    f = (s * rstd) * (np.asarray(gamma, dtype=np.float16).astype(np.float32) + np.float32(1.0))
+    if rotate:
+        f = fwht32(f.astype(np.float32))
+    return f.astype(np.float16), new_res
+
+
 def router_gemm(x: np.ndarray, w: np.ndarray) -> np.ndarray:
     """Router logits [t, e] = x [t, h] . w [e, h]^T (qwg_router_gemm, Sources/QWMetal/subsystems/qwrouter.metal:457-520):
     plain dot products of the un-rotated hidden states with the raw router plane; accumulated in f64 here, so the device's

@@ -1,0 +1,137 @@
+// RMSNorm with the rotated (Walsh-Hadamard) f16 output the quantized matmuls consume: the CUDA twin of the
+// reference's qwg_rmsnorm / qwg_rmsnorm_residual (Sources/QWMetal/mlp_norm_rope/qwnorm.metal:27-79, 249-259; host
+// doors encodeRMSNormFast / encodeRMSNormResidualFast, Sources/Runtime/QWEngine/Driver/EncodeKernels.swift:339-404).
+//   y = f16( fwht32( s * rsqrt(mean(s^2) + eps) * (1 + gamma) ) ),   s = x, or s = f16(x + residual) (stored back)
+// f32 sum of squares, f32 products, f32 butterflies, one rounding to f16 at the store ("plus-one law": gamma is stored
+// raw).  This is the step before every GEMM of the reference's engine: with it the matmuls are called with
+// x_is_rotated = 1 and do not rotate activations themselves.
+#include "qwc_common.cuh"
+
+namespace {
+
+// One CTA per row; thread t owns the 16-byte chunks t, t + T, ... (8 halves each).  A quad of consecutive threads
+// holds one aligned 32-element block, so the FWHT-32 is three in-lane butterfly stages plus two xor-shuffle stages.
+constexpr int kNormMaxChunks = 4;   // chunks kept in registers per thread (hidden <= 8 * 4 * blockDim)
+
+__global__ void __launch_bounds__(1024) qwc_rmsnorm_fwht_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma,
+                                                                __half* __restrict__ y, __half* residual, int hidden, float eps,
+                                                                int rotate) {
+    __shared__ float s_part[32];
+    __shared__ float s_rstd;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+    const int chunks = hidden / 8;
+    const int64_t row = blockIdx.x;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * hidden);
+    uint4* rr = residual ? reinterpret_cast<uint4*>(residual + row * hidden) : nullptr;
+    uint4* yr = reinterpret_cast<uint4*>(y + row * hidden);
+    const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+
+    uint4 reg[kNormMaxChunks];
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kNormMaxChunks; ++i) {
+        const int u = tid + i * nthreads;
+        if (u < chunks) {
+            uint4 v = xr[u];
+            if (rr) {
+                const uint4 r = rr[u];
+                __half2* a = reinterpret_cast<__half2*>(&v);
+                const __half2* b = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 fa = __half22float2(a[j]), fb = __half22float2(b[j]);
+                    a[j] = __floats2half2_rn(__fadd_rn(fa.x, fb.x), __fadd_rn(fa.y, fb.y));
+                }
+                rr[u] = v;   // residual += x, kept in f16 as the reference does
+            }
+            reg[i] = v;
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                acc = fmaf(f.x, f.x, acc);
+                acc = fmaf(f.y, f.y, acc);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    if (lane == 0) s_part[warp] = acc;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < (nthreads >> 5) ? s_part[lane] : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+        if (lane == 0) s_rstd = rsqrtf(t / static_cast<float>(hidden) + eps);
+    }
+    __syncthreads();
+    const float rstd = s_rstd;
+    const int t4 = lane & 3;
+#pragma unroll
+    for (int i = 0; i < kNormMaxChunks; ++i) {
+        const int u = tid + i * nthreads;
+        if (u < chunks) {   // uniform per warp: chunks and nthreads are multiples of 32
+            const uint4 g = gr[u];
+            const __half2* h = reinterpret_cast<const __half2*>(&reg[i]);
+            const __half2* gh = reinterpret_cast<const __half2*>(&g);
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 fv = __half22float2(h[j]), gv = __half22float2(gh[j]);
+                f[2 * j] = __fmul_rn(__fmul_rn(fv.x, rstd), __fadd_rn(gv.x, 1.0f));
+                f[2 * j + 1] = __fmul_rn(__fmul_rn(fv.y, rstd), __fadd_rn(gv.y, 1.0f));
+            }
+            if (rotate) {
+#pragma unroll
+                for (int hh = 1; hh < 8; hh <<= 1)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if ((j & hh) == 0) {
+                            const float a = f[j], b = f[j + hh];
+                            f[j] = __fadd_rn(a, b);
+                            f[j + hh] = __fsub_rn(a, b);
+                        }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fwht_xor_stage(f[j], 1, (t4 & 1) != 0);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fwht_xor_stage(f[j], 2, (t4 & 2) != 0);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __fmul_rn(f[j], qwc_inv_sqrt32());
+            }
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+            yr[u] = o;
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int qwc_rmsnorm_fwht(qwc_hal* hal, qwc_stream stream, const void* x_f16, const void* gamma_f16, void* y_f16,
+                                void* residual_f16, int64_t rows, int64_t hidden, float eps, int32_t rotate) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    // the norm family's contract (EncodeKernels.swift:350-357): rows of 16-byte chunks rotating in groups of 32 halves
+    if (hidden <= 0 || hidden % 256 != 0)
+        return qwc_fail(QWC_ERR_BAD_GEOMETRY, "the norm family needs a hidden that is a multiple of 256, got %lld", (long long)hidden);
+    if (hidden > 8 * kNormMaxChunks * 1024) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "hidden=%lld is above %d", (long long)hidden, 8 * kNormMaxChunks * 1024);
+    if (rows < 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "rows is negative");
+    if (rows == 0) return QWC_OK;
+    if (!x_f16 || !gamma_f16 || !y_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    if ((reinterpret_cast<uintptr_t>(x_f16) | reinterpret_cast<uintptr_t>(gamma_f16) | reinterpret_cast<uintptr_t>(y_f16) |
+         reinterpret_cast<uintptr_t>(residual_f16)) % 16 != 0)
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "buffers must be 16-byte aligned");
+    const int chunks = static_cast<int>(hidden / 8);
+    int threads = (chunks + kNormMaxChunks - 1) / kNormMaxChunks;
+    threads = ((threads + 31) / 32) * 32;
+    if (threads < 32) threads = 32;
+    // more threads than strictly needed (up to one chunk per thread) shorten a row's latency at decode
+    while (threads * 2 <= chunks && threads * 2 <= 1024) threads *= 2;
+    qwc_rmsnorm_fwht_kernel<<<static_cast<unsigned>(rows), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x_f16), static_cast<const __half*>(gamma_f16), static_cast<__half*>(y_f16),
+        static_cast<__half*>(residual_f16), static_cast<int>(hidden), eps, rotate);
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}

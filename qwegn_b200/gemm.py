@@ -207,6 +207,24 @@ class QWGemm:
         _check(_lib.load().qwc_fwht32_f16(hal.handle, _stream_ptr(stream), x.data_ptr(), x.numel()))
 
     @staticmethod
+    def encodeRMSNorm(hal: QWHal, x: torch.Tensor, gamma: torch.Tensor, out: torch.Tensor, eps: float = 1e-6,
+                      residual: Optional[torch.Tensor] = None, rotate: bool = True,
+                      stream: Optional[torch.cuda.Stream] = None) -> None:
+        """RMSNorm with (1 + gamma) and rotated f16 output, optionally fused with residual += x (the driver's
+        encodeRMSNormFast / encodeRMSNormResidualFast, Sources/Runtime/QWEngine/Driver/EncodeKernels.swift:339-404).
+        Feed `out` to encode(..., x_is_rotated=True)."""
+        for t in (x, gamma, out) + ((residual,) if residual is not None else ()):
+            if t.dtype != torch.float16 or not t.is_cuda or not t.is_contiguous():
+                raise QWGemmError(3, "norm tensors must be contiguous CUDA float16")
+        x2 = x if x.dim() == 2 else x.view(1, -1)
+        rows, hidden = x2.shape
+        if gamma.numel() != hidden or out.numel() != x.numel() or (residual is not None and residual.numel() != x.numel()):
+            raise QWGemmError(3, "shape mismatch")
+        _check(_lib.load().qwc_rmsnorm_fwht(hal.handle, _stream_ptr(stream), x.data_ptr(), gamma.data_ptr(), out.data_ptr(),
+                                            None if residual is None else residual.data_ptr(), rows, hidden, float(eps),
+                                            int(rotate)))
+
+    @staticmethod
     def dequant(hal: QWHal, w: QWWeightView, out: torch.Tensor, standard_domain: bool = False,
                 stream: Optional[torch.cuda.Stream] = None) -> None:
         """Device twin of Pack.dequantHQ4Slab / dequantHQBlockSlab (Sources/Foundation/QWQuant/QWPack.swift:205-321)."""
