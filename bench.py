@@ -360,6 +360,9 @@ def run_ours(args):
             t, b, *_ = bench_gemv_point(q, hal, n, k, 1, "HQ4_G32", args.steps, args.warmup, rotated=True)
             extra["c2_gemv_M1_rotated_activations_in"] = {"GBps": b / (t * 1e-3) / 1e9, "us": t * 1e3,
                                                           "note": "x_is_rotated=1: activations rotated by qwc_rmsnorm_fwht outside the timed loop, as in the reference's engine"}
+        if "c1" in sections:
+            extra["lm_head_greedy_N248320_K5120_M1"] = bench_lm_head(q, hal, peaks)
+            torch.cuda.empty_cache()
         if "sweep" in sections:
             sweep = {}
             for cname in ("HQ4_G32", "HQ8_G32", "HQ4_G64"):
@@ -385,6 +388,31 @@ def run_ours(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def bench_lm_head(q, hal, peaks, steps=60):
+    """Greedy LM head (the largest GEMV of a decode step): logits = HQ4_G32 [248320, 5120] x, then the key-ordered argmax.
+    Two banks in rotation (1.6 GB > L2)."""
+    import torch
+    n, k = 248320, 5120
+    cont = q.CONTAINERS["HQ4_G32"]
+    banks = make_banks(q, hal, n, k, cont, 2, seed=5)
+    x = torch.randn((1, k), device="cuda", dtype=torch.float32).to(torch.float16)
+    y = torch.empty((1, n), dtype=torch.float32, device="cuda")
+    tok = torch.empty(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def step(i):
+        q.QWGemm.encode(hal, banks[i % 2], x, y)
+        q.QWGemm.encodeArgmax(hal, y, tok)
+
+    for i in range(4):
+        step(i)
+    ms = time_region(step, steps, None, stream, graph=True) / steps
+    nbytes = gemv_bytes(n, k, 1)
+    ref = int(torch.argmax(y[0]).item())
+    return {"us": ms * 1e3, "GBps": nbytes / (ms * 1e-3) / 1e9, "frac_of_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "token_matches_torch_argmax": bool(int(tok.item()) == ref)}
 
 
 def _time_call(fn, iters, warm=3):

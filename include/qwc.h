@@ -116,6 +116,13 @@ int qwc_fwht32_f16(qwc_hal* hal, qwc_stream stream, void* x_f16, int64_t count);
 int qwc_rmsnorm_fwht(qwc_hal* hal, qwc_stream stream, const void* x_f16, const void* gamma_f16, void* y_f16,
                      void* residual_f16, int64_t rows, int64_t hidden, float eps, int32_t rotate);
 
+/* Greedy head: tokens[r] = argmax_c logits[r, c] in the reference's key order (value, then lower column; NaN lowest, +0
+ * above -0) — the pair encodeHQ4F32V4Argmax + encodeArgmaxFin (Sources/Operators/QWGEMM/QWGemmF32.swift:201-307; kernels
+ * Sources/QWMetal/include/qw_gemm_f32_common.metalh:31-57, Sources/QWMetal/head_sampling/qwhead.metal:241-270) after the
+ * LM-head GEMV: call qwc_gemm with f32 logits [rows, n], then this.  logits f32, row stride ld; tokens i32 [rows]. */
+int qwc_head_argmax(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t ld, int64_t rows, int64_t n,
+                    int32_t* tokens);
+
 /* Host decode twin Pack.dequantHQ4Slab / dequantHQBlockSlab (Sources/Foundation/QWQuant/QWPack.swift:205-321),
  * on the device: blocks -> [n, k] values, bit-exact with the reference decode.  standard_domain != 0 applies the
  * inverse rotation (FWHT-32).  out_dtype QWC_F32, or QWC_F16 (one extra rounding). */

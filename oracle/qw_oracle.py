@@ -182,6 +182,20 @@ def rmsnorm_fwht(x: np.ndarray, gamma: np.ndarray, eps: float = 1e-6, residual: 
     return f.astype(np.float16), new_res
 
 
+def head_argmax(logits: np.ndarray) -> np.ndarray:
+    """Greedy token per row in the reference's key order (qw_sortable_f32_u32, Sources/QWMetal/include/qw_fastmath_safe.metalh:
+    21-25; qwg_gemv_am_fold4, include/qw_gemm_f32_common.metalh:31-47): key = (sortable(value), ~column): NaN lowest,
+    +0 above -0, ties to the lower column."""
+    lg = np.ascontiguousarray(logits, dtype=np.float32)
+    lg = lg.reshape(-1, lg.shape[-1])
+    u = lg.view(np.uint32)
+    s = np.where((u & np.uint32(0x80000000)) != 0, ~u, u ^ np.uint32(0x80000000))
+    s = np.where((u & np.uint32(0x7FFFFFFF)) > np.uint32(0x7F800000), np.uint32(0), s)
+    cols = np.arange(lg.shape[1], dtype=np.uint64)
+    key = (s.astype(np.uint64) << np.uint64(32)) | (np.uint64(0xFFFFFFFF) - cols)
+    return key.argmax(axis=1).astype(np.int32)
+
+
 def router_gemm(x: np.ndarray, w: np.ndarray) -> np.ndarray:
     """Router logits [t, e] = x [t, h] . w [e, h]^T (qwg_router_gemm, Sources/QWMetal/subsystems/qwrouter.metal:457-520):
     plain dot products of the un-rotated hidden states with the raw router plane; accumulated in f64 here, so the device's

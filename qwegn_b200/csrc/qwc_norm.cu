@@ -107,7 +107,73 @@ __global__ void __launch_bounds__(1024) qwc_rmsnorm_fwht_kernel(const __half* __
     }
 }
 
+// Greedy head: token[row] = argmax over the vocabulary of logits[row, :] with the reference's key order
+// (qwg_gemv_am_fold4 / qwg_head_argmax_fin: Sources/QWMetal/include/qw_gemm_f32_common.metalh:31-57,
+// Sources/QWMetal/head_sampling/qwhead.metal:241-270; qw_sortable_f32_u32, include/qw_fastmath_safe.metalh:21-25):
+// key = (sortable(value), ~column): NaN sorts lowest, +0 above -0, ties go to the lower column.
+__device__ __forceinline__ uint32_t sortable_f32(float x) {
+    const uint32_t u = __float_as_uint(x);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return 0u;
+    return (u & 0x80000000u) ? ~u : (u ^ 0x80000000u);
+}
+
+__global__ void __launch_bounds__(1024) qwc_head_argmax_kernel(const float* __restrict__ logits, int64_t ld, int n,
+                                                               int32_t* __restrict__ tokens) {
+    __shared__ unsigned long long s_best[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
+    unsigned long long best = 0ull;
+    const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+    int c0 = 0;
+    if (vec) {
+        const int n4 = n & ~3;
+        for (int c = tid * 4; c < n4; c += 4096) {
+            const float4 v = *reinterpret_cast<const float4*>(row + c);
+            const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const unsigned long long key = (static_cast<unsigned long long>(sortable_f32(f[i])) << 32) | static_cast<uint32_t>(~(c + i));
+                best = key > best ? key : best;
+            }
+        }
+        c0 = n4;
+    }
+    for (int c = c0 + tid; c < n; c += 1024) {
+        const unsigned long long key = (static_cast<unsigned long long>(sortable_f32(row[c])) << 32) | static_cast<uint32_t>(~c);
+        best = key > best ? key : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        best = other > best ? other : best;
+    }
+    if (lane == 0) s_best[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+        best = s_best[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+            best = other > best ? other : best;
+        }
+        if (lane == 0) tokens[blockIdx.x] = static_cast<int32_t>(~static_cast<uint32_t>(best & 0xFFFFFFFFull));
+    }
+}
+
 }  // namespace
+
+extern "C" int qwc_head_argmax(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t ld, int64_t rows, int64_t n,
+                               int32_t* tokens) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (n <= 0 || n >= (int64_t(1) << 31) || ld < n) return qwc_fail(QWC_ERR_BAD_SHAPE, "bad vocabulary extent n=%lld ld=%lld", (long long)n, (long long)ld);
+    if (rows < 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "rows is negative");
+    if (rows == 0) return QWC_OK;
+    if (!logits || !tokens) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    qwc_head_argmax_kernel<<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream)>>>(logits, ld, static_cast<int>(n), tokens);
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
 
 extern "C" int qwc_rmsnorm_fwht(qwc_hal* hal, qwc_stream stream, const void* x_f16, const void* gamma_f16, void* y_f16,
                                 void* residual_f16, int64_t rows, int64_t hidden, float eps, int32_t rotate) {

@@ -207,6 +207,15 @@ class QWGemm:
         _check(_lib.load().qwc_fwht32_f16(hal.handle, _stream_ptr(stream), x.data_ptr(), x.numel()))
 
     @staticmethod
+    def encodeArgmax(hal: QWHal, logits: torch.Tensor, tokens: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Greedy token per row of f32 logits [rows, vocab] in the reference's key order (QWGemmF32.swift:201-307)."""
+        if logits.dtype != torch.float32 or tokens.dtype != torch.int32 or not logits.is_cuda or logits.stride(-1) != 1:
+            raise QWGemmError(3, "logits must be CUDA float32 with contiguous rows, tokens int32")
+        l2 = logits if logits.dim() == 2 else logits.view(1, -1)
+        _check(_lib.load().qwc_head_argmax(hal.handle, _stream_ptr(stream), l2.data_ptr(), l2.stride(0) if l2.shape[0] > 1 else l2.shape[1],
+                                           l2.shape[0], l2.shape[1], tokens.data_ptr()))
+
+    @staticmethod
     def encodeRMSNorm(hal: QWHal, x: torch.Tensor, gamma: torch.Tensor, out: torch.Tensor, eps: float = 1e-6,
                       residual: Optional[torch.Tensor] = None, rotate: bool = True,
                       stream: Optional[torch.cuda.Stream] = None) -> None:

@@ -58,3 +58,25 @@ def test_rmsnorm_refusals(hal):
     with pytest.raises(q.QWGemmError) as e:   # EncodeKernels.swift:350-357: hidden must be a multiple of 256
         q.QWGemm.encodeRMSNorm(hal, x, torch.zeros(1000, dtype=torch.float16, device="cuda"), torch.empty_like(x))
     assert e.value.case == "badGeometry"
+
+
+@pytest.mark.parametrize("rows,n", [(1, 248320), (4, 151936), (3, 1000), (2, 7)])
+def test_head_argmax_matches_the_oracle(hal, oracle, rows, n):
+    import qwegn_b200 as q
+    rng = np.random.default_rng(rows + n)
+    lg = rng.standard_normal((rows, n)).astype(np.float32)
+    lg[0, n // 2] = lg[0].max()          # a tie: the lower column wins
+    lg[0, n // 3] = lg[0].max()
+    if n > 10:
+        lg[-1, 5] = np.nan               # NaN sorts lowest
+        lg[-1, 6] = np.inf
+    tok = torch.full((rows,), -7, dtype=torch.int32, device="cuda")
+    q.QWGemm.encodeArgmax(hal, torch.from_numpy(lg).cuda(), tok)
+    assert np.array_equal(tok.cpu().numpy(), oracle.head_argmax(lg))
+    allnan = torch.full((1, n), float("nan"), dtype=torch.float32, device="cuda")
+    q.QWGemm.encodeArgmax(hal, allnan, tok[:1])
+    assert int(tok[0]) == 0
+    zeros = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    zeros[0, 0] = -0.0
+    q.QWGemm.encodeArgmax(hal, zeros, tok[:1])
+    assert int(tok[0]) == int(oracle.head_argmax(zeros.cpu().numpy())[0])
