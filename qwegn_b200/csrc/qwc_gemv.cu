@@ -717,7 +717,9 @@ bool plan_geometry(int units, int m, int nt, int sub, int jobs, int budget, Stre
     g->red_bytes = kConsumerWarps * sub * nt * 32 * 16;
     const int fixed = g->x_bytes + g->red_bytes + kBarrierBytes;
     int teams = 1;
-    while (teams < jobs && teams < kConsumerWarps) teams <<= 1;
+    // at most 8 teams: 16 single-warp teams need 18 stages, which forces 32-unit chunks, and narrow chunks cost far more
+    // than wide teams (N = 248320: 198 us with 16 x 1 warps and 32-unit chunks, 139 us with 8 x 2 warps and 56-unit chunks)
+    while (teams < jobs && teams < 8) teams <<= 1;
     static const int env_w = getenv("QWC_GEMV_W") ? atoi(getenv("QWC_GEMV_W")) : 0;
     static const int env_chunk = getenv("QWC_GEMV_CHUNK") ? atoi(getenv("QWC_GEMV_CHUNK")) : 0;
     if (env_w == 1 || env_w == 2 || env_w == 4 || env_w == 8 || env_w == 16) teams = kConsumerWarps / env_w;
