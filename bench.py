@@ -491,17 +491,23 @@ def bench_parallel(q, hal, rank, world, dist):
     gen.manual_seed(77)   # the same bank on every rank; each keeps its shard
     gu_plane = q.QWGemm.quantize(hal, torch.randn((2 * inter, hidden), generator=gen, device="cuda") * 0.02, cont)
     dn_plane = q.QWGemm.quantize(hal, torch.randn((hidden, inter), generator=gen, device="cuda") * 0.02, cont)
-    mlp = par.TPMlp(hal, gu_plane, dn_plane, hidden, inter, cont, rank, world)
-    del gu_plane, dn_plane
-    torch.cuda.empty_cache()
     x = torch.randn((1, hidden), generator=gen, device="cuda").to(torch.float16)
-    h_loc = torch.empty((1, mlp.inter_local), dtype=torch.float16, device="cuda")
     y = torch.empty((1, hidden), dtype=torch.float32, device="cuda")
-    dist.barrier()
-    ms = tmax(_time_call(lambda: mlp.forward(x, h_loc, y), 50, warm=5))
     wbytes = (2 * inter * (hidden // 32) + hidden * (inter // 32)) * 20
-    out[f"tp{world}_mlp_decode_M1_H8192_I28672"] = {"us": round(ms * 1e3, 1), "aggregate_weight_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1)}
-    del mlp
+    # the all-reduce by NCCL after the down projection, and fused into the down projection's kernel (peer stores + flags)
+    for label, fused in (("nccl_allreduce", False), ("fused_allreduce", True)):
+        try:
+            mlp = par.TPMlp(hal, gu_plane, dn_plane, hidden, inter, cont, rank, world, fused_allreduce=fused)
+        except Exception as exc:   # symmetric memory unavailable on this box: report, keep the NCCL number
+            out[f"tp{world}_mlp_decode_M1_H8192_I28672_{label}"] = {"unavailable": str(exc)[:120]}
+            continue
+        h_loc = torch.empty((1, mlp.inter_local), dtype=torch.float16, device="cuda")
+        dist.barrier()
+        ms = tmax(_time_call(lambda: mlp.forward(x, h_loc, y), 50, warm=5))
+        out[f"tp{world}_mlp_decode_M1_H8192_I28672_{label}"] = {"us": round(ms * 1e3, 1), "aggregate_weight_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1)}
+        del mlp
+        torch.cuda.empty_cache()
+    del gu_plane, dn_plane
     torch.cuda.empty_cache()
 
     t, e, k, h, it = 2048, 256, 8, 2048, 512

@@ -165,6 +165,32 @@ int qwc_gemm_static_scratch(qwc_hal* hal, qwc_stream stream, const qwc_weight_vi
                             int64_t ldx, void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated);
 size_t qwc_static_scratch_capacity(void);
 
+/* ---- tensor parallel: row-parallel matmul fused with its all-reduce ---------------------------------------------
+ * (No counterpart in the reference, which runs on one device; the format decides the design: a K shard of the bank per
+ * rank, f32 partial sums, one sum over the ranks.)  One kernel does both: every CTA stores its partial sums straight
+ * into the inbox of every rank (ordinary peer stores over NVLink), raises a flag on every rank, waits (bounded) for the
+ * flags of the matching CTAs of the other ranks and sums the world slots of its rows in rank order, so every rank ends
+ * with the same bits.  The caller provides peer-mapped memory (for example torch.distributed._symmetric_memory):
+ *   inbox[r]: rank r's inbox for this call, f32 [world][m][n];  flags[r]: rank r's flags for this call, u32
+ *   [world][qwc_sm_count()], zero before the first call.  epoch: a value that differs from the previous two calls' (a
+ *   call counter); alternate between two inbox/flag buffers from call to call so that a fast rank's next call does not
+ *   overwrite data a slow rank is still summing.  Every rank of the group must make the same call (same shapes). */
+typedef struct {
+    int32_t rank, world;      /* 2 <= world <= 8 */
+    uint32_t epoch;
+    int32_t reserved;
+    void* inbox[8];
+    void* flags[8];
+    int64_t inbox_floats;     /* capacity of one inbox buffer in floats (>= world * m * n) */
+    int64_t flag_words;       /* capacity of one flag buffer in words (>= world * qwc_sm_count()) */
+} qwc_allreduce_ctx;
+
+/* y[m, n] = sum over ranks of rot(x_local[m, k_local]) . W_local^T (no epilogue), m <= 8 (decode / verify), banks with
+ * 16-byte rows.  Returns QWC_ERR_BLOCKED for shapes this form does not take (use qwc_gemm + an all-reduce then). */
+int qwc_gemm_allreduce(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w_local, const void* x_f16, int64_t m,
+                       int64_t ldx, void* y, int32_t y_dtype, int64_t ldy, int32_t x_is_rotated,
+                       const qwc_allreduce_ctx* ctx);
+
 /* ---- mixture of experts ---------------------------------------------------------------------------------------
  * The operator chain of QWMoEOperator.encodeResident (Sources/Operators/QWGEMM/QWMoEOperator.swift:206-442), grouped
  * path: route -> pair sort + tile plan -> gather -> grouped gate/up GEMM -> SwiGLU + FWHT -> grouped down GEMM ->

@@ -15,6 +15,8 @@ int qwc_launch_quantize(const qwc_hal*, cudaStream_t, const float*, int64_t, int
 int qwc_launch_gemv(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int,
                     int64_t, int, int, void*, size_t);
 size_t qwc_gemv_workspace_bytes(const qwc_weight_view*, int64_t);
+int qwc_launch_gemv_ar(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int,
+                       int64_t, int, int, void*, size_t, const qwc_allreduce_ctx*);
 bool qwc_gemm_tc_supported(const qwc_hal*, const qwc_weight_view*, int64_t, int);
 size_t qwc_gemm_tc_workspace_bytes(const qwc_weight_view*, int64_t, int);
 int qwc_launch_gemm_tc(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int, int64_t,
@@ -248,6 +250,30 @@ int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const vo
                                   x_is_rotated, workspace, workspace_bytes);
     return qwc_launch_gemv(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, epilogue,
                            x_is_rotated, workspace, workspace_bytes);
+}
+
+int qwc_gemm_allreduce(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx,
+                       void* y, int32_t y_dtype, int64_t ldy, int32_t x_is_rotated, const qwc_allreduce_ctx* ctx) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (int rc = check_view(w)) return rc;
+    if (!ctx) return qwc_fail(QWC_ERR_BAD_SHAPE, "all-reduce context is null");
+    if (ctx->world < 2 || ctx->world > 8 || ctx->rank < 0 || ctx->rank >= ctx->world)
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "rank %d / world %d: the fused form takes 2..8 ranks", ctx->rank, ctx->world);
+    if (m <= 0) return m == 0 ? QWC_OK : qwc_fail(QWC_ERR_BAD_SHAPE, "m is negative");
+    if (!x_f16 || !y) return qwc_fail(QWC_ERR_BAD_SHAPE, "x or y is null");
+    if (y_dtype != QWC_F16 && y_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "y dtype must be f16 or f32");
+    if (ldx < w->k || ldy < w->n) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldx / ldy too small");
+    const int64_t row_bytes = (w->k / w->group) * qwc_block_bytes(w->kind, w->bits, w->group);
+    if (m > 8 || row_bytes % 16 != 0 || reinterpret_cast<uintptr_t>(w->blocks) % 16 != 0 || qwc_gemv_workspace_bytes(w, m) != 0)
+        return qwc_fail(QWC_ERR_BLOCKED, "the fused all-reduce takes m <= 8, 16-byte bank rows and one K slice");
+    for (int r = 0; r < ctx->world; ++r)
+        if (!ctx->inbox[r] || !ctx->flags[r]) return qwc_fail(QWC_ERR_BAD_SHAPE, "peer buffer %d is null", r);
+    if (ctx->inbox_floats < static_cast<int64_t>(ctx->world) * m * w->n || ctx->flag_words < static_cast<int64_t>(ctx->world) * hal->sm_count)
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "peer buffers too small: need %lld floats and %lld flag words",
+                        (long long)(static_cast<int64_t>(ctx->world) * m * w->n), (long long)(static_cast<int64_t>(ctx->world) * hal->sm_count));
+    return qwc_launch_gemv_ar(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, QWC_EPI_NONE, x_is_rotated,
+                              nullptr, 0, ctx);
 }
 
 }  // extern "C"

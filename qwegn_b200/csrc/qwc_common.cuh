@@ -49,7 +49,7 @@ template <> struct FmtTraits<FMT_HQ4_G64> {
 
 // Kernel status codes written to qwc_hal::status[0].
 enum { QWC_DEV_OK = 0, QWC_DEV_WAIT_FULL_TIMEOUT = 101, QWC_DEV_WAIT_EMPTY_TIMEOUT = 102,
-       QWC_DEV_WAIT_MMA_TIMEOUT = 103, QWC_DEV_WAIT_TMEM_TIMEOUT = 104, QWC_DEV_NONFINITE_WEIGHT = 201 };
+       QWC_DEV_WAIT_MMA_TIMEOUT = 103, QWC_DEV_WAIT_TMEM_TIMEOUT = 104, QWC_DEV_WAIT_PEER_TIMEOUT = 105, QWC_DEV_NONFINITE_WEIGHT = 201 };
 
 #ifdef __CUDACC__
 

@@ -71,6 +71,11 @@ struct GemvParams {
     int red_bytes;    // smem bytes of the team reduction region
     int pdl;          // launched with programmatic stream serialization: weights prefetch before the dependency wait
     int use_tmap;     // full 16-row tiles arrive by one 2-D tensor copy instead of 16 row copies
+    // fused one-shot all-reduce over peer memory (row-parallel shards of a tensor-parallel group; ar_world > 1):
+    int ar_world, ar_rank;
+    uint32_t ar_epoch;        // call number: the flag value that marks this call's data as complete
+    float* ar_inbox[8];       // rank r's inbox for this call: [world][m][n] f32; slot [s] is written by rank s
+    uint32_t* ar_flags[8];    // rank r's flags for this call: [world][grid]; word [s][cta] is written by CTA cta of rank s
 };
 
 // Shared-memory loads by 32-bit shared-window address (no 64-bit pointer arithmetic in the inner loop).
@@ -593,6 +598,10 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                         if (SUB > 1) v = (v / (1.0f + expf(-v))) * u;
                         if (SUB == 4) {
                             hval[ot][nt][i] = __half2float(__float2half_rn(v));
+                        } else if (SUB == 1 && p.ar_world > 1) {
+                            // the partial sum goes straight into every rank's inbox (peer stores over NVLink), its own too
+                            const int64_t o = (static_cast<int64_t>(p.ar_rank) * p.m + tok) * p.n + row;
+                            for (int r = 0; r < p.ar_world; ++r) p.ar_inbox[r][o] = v;
                         } else {
                             const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
                             if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(v);
@@ -627,6 +636,42 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             }
         }
         if (W > 1) named_bar_sync(1 + team, team_threads); else __syncwarp();  // red is reused by the next job
+    }
+
+    if (SUB == 1 && p.ar_world > 1) {
+        // ---- fused one-shot all-reduce: CTA c of every rank owns the same output rows, so CTA c only has to meet the
+        // CTAs c of the other ranks.  Pushes (above) -> system fence -> flag to every rank -> wait for every rank's flag
+        // -> sum the world slots of this CTA's rows in rank order (same bits on every rank).  All waits are bounded.
+        __threadfence_system();
+        named_bar_sync(11, kConsumerWarps * 32);
+        const int cta = static_cast<int>(blockIdx.x), grid = static_cast<int>(gridDim.x);
+        if (threadIdx.x < static_cast<unsigned>(p.ar_world)) {
+            uint32_t* f = p.ar_flags[threadIdx.x] + p.ar_rank * grid + cta;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ar_epoch) : "memory");
+            const uint32_t* mine = p.ar_flags[p.ar_rank] + threadIdx.x * grid + cta;
+            bool got = false;
+            for (uint32_t spin = 0; spin < (1u << 22); ++spin) {   // ~1 s at worst
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+                if (v == p.ar_epoch) {
+                    got = true;
+                    break;
+                }
+                __nanosleep(spin < 256 ? 40 : 250);
+            }
+            if (!got) atomicCAS(p.status, 0, QWC_DEV_WAIT_PEER_TIMEOUT);
+        }
+        named_bar_sync(11, kConsumerWarps * 32);
+        const int rows_cta = re - rb;
+        const float* inbox = p.ar_inbox[p.ar_rank];
+        for (int i = threadIdx.x; i < rows_cta * p.m; i += kConsumerWarps * 32) {
+            const int tok = i / rows_cta, row = rb + (i - tok * rows_cta);
+            float sum = 0.0f;
+            for (int r = 0; r < p.ar_world; ++r) sum += __ldcg(inbox + (static_cast<int64_t>(r) * p.m + tok) * p.n + row);
+            const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
+            if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(sum);
+            else static_cast<float*>(p.y)[o] = sum;
+        }
     }
 }
 
@@ -897,10 +942,30 @@ size_t qwc_gemv_workspace_bytes(const qwc_weight_view* w, int64_t m) {
 }
 
 // Host entry used by qwc_gemm.  All arguments were validated by the caller.
+int qwc_launch_gemv_ar(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
+                       void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace,
+                       size_t workspace_bytes, const qwc_allreduce_ctx* ar);
+
 int qwc_launch_gemv(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
                     void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace,
                     size_t workspace_bytes) {
+    return qwc_launch_gemv_ar(hal, st, w, x, m, ldx, y, y_dtype, ldy, epilogue, x_is_rotated, workspace, workspace_bytes, nullptr);
+}
+
+// ar != null: the fused all-reduce form (validated by the caller: one K slice, <= 8 tokens, no epilogue, 16-byte rows).
+int qwc_launch_gemv_ar(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
+                       void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace,
+                       size_t workspace_bytes, const qwc_allreduce_ctx* ar) {
     GemvParams p{};
+    if (ar != nullptr) {
+        p.ar_world = ar->world;
+        p.ar_rank = ar->rank;
+        p.ar_epoch = ar->epoch;
+        for (int r = 0; r < ar->world && r < 8; ++r) {
+            p.ar_inbox[r] = static_cast<float*>(ar->inbox[r]);
+            p.ar_flags[r] = static_cast<uint32_t*>(ar->flags[r]);
+        }
+    }
     const int fmt = qwc_fmt_of(*w);
     const int64_t bb = qwc_block_bytes(w->kind, w->bits, w->group);
     const int group = fmt == FMT_HQ4_G64 ? 64 : 32;

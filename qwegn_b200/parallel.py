@@ -18,6 +18,7 @@ can be tested with the gloo backend.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from dataclasses import dataclass
 from typing import Callable, Optional, Tuple
@@ -25,8 +26,9 @@ from typing import Callable, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from .gemm import ContainerKind, QWGemm, QWGemmError, QWHal, QWWeightView
-from ._lib import EPI_NONE, EPI_SILU_PAIR_FWHT
+from . import _lib
+from .gemm import ContainerKind, QWGemm, QWGemmError, QWHal, QWWeightView, _check, _stream_ptr
+from ._lib import EPI_NONE, EPI_SILU_PAIR_FWHT, WeightViewC
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -105,11 +107,76 @@ class RowParallelLinear:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
 
 
+class AllReduceCtxC(ctypes.Structure):
+    """qwc_allreduce_ctx (include/qwc.h)."""
+    _fields_ = [("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_int32),
+                ("inbox", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8), ("inbox_floats", ctypes.c_int64),
+                ("flag_words", ctypes.c_int64)]
+
+
+_lib.register("qwc_gemm_allreduce", ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(WeightViewC), ctypes.c_void_p,
+                                                   ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64,
+                                                   ctypes.c_int32, ctypes.POINTER(AllReduceCtxC)])
+
+
+class FusedRowParallelLinear(RowParallelLinear):
+    """Row-parallel matmul whose kernel also does the all-reduce (decode / verify, m <= 8): every CTA pushes its partial
+    sums into all ranks' inboxes over NVLink, flags, waits for the matching CTAs of the other ranks and sums in rank
+    order.  The inboxes and flags live in torch symmetric memory (two buffers, alternated per call).  Shapes the fused
+    form does not take fall back to the matmul + NCCL all-reduce of the base class."""
+
+    def __init__(self, hal: QWHal, shard: torch.Tensor, n: int, k_local: int, cont: ContainerKind,
+                 group: Optional[dist.ProcessGroup] = None, max_m: int = 8):
+        super().__init__(hal, shard, n, k_local, cont, group)
+        import torch.distributed._symmetric_memory as symm_mem
+        grp = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(grp), dist.get_rank(grp)
+        dev = torch.device("cuda", hal.device.index)
+        self.max_m, self.sms = max_m, hal.sm_count
+        self.inbox = symm_mem.empty((2, self.world, max_m, n), dtype=torch.float32, device=dev)
+        self.flags = symm_mem.empty((2, self.world, self.sms), dtype=torch.int32, device=dev)
+        self.flags.zero_()
+        torch.cuda.synchronize(dev)
+        self.h_inbox = symm_mem.rendezvous(self.inbox, grp)
+        self.h_flags = symm_mem.rendezvous(self.flags, grp)
+        dist.barrier(grp)   # every rank's flags are zero before anyone's first call
+        self.epoch = 0
+
+    def forward(self, x_local: torch.Tensor, y: torch.Tensor, x_is_rotated: bool = False,
+                workspace: Optional[torch.Tensor] = None, reduce: bool = True):
+        x2 = x_local if x_local.dim() == 2 else x_local.view(1, -1)
+        m = x2.shape[0]
+        if not reduce or m > self.max_m or self.world < 2 or self.world > 8:
+            return super().forward(x_local, y, x_is_rotated, workspace, reduce)
+        self.epoch += 1
+        buf = self.epoch & 1
+        ctx = AllReduceCtxC()
+        ctx.rank, ctx.world, ctx.epoch = self.rank, self.world, self.epoch
+        in_bytes = self.world * self.max_m * self.view.n * 4
+        fl_bytes = self.world * self.sms * 4
+        for r in range(self.world):
+            ctx.inbox[r] = int(self.h_inbox.buffer_ptrs[r]) + buf * in_bytes
+            ctx.flags[r] = int(self.h_flags.buffer_ptrs[r]) + buf * fl_bytes
+        ctx.inbox_floats = self.world * self.max_m * self.view.n
+        ctx.flag_words = self.world * self.sms
+        y2 = y if y.dim() == 2 else y.view(1, -1)
+        rc = _lib.load().qwc_gemm_allreduce(self.hal.handle, _stream_ptr(None), ctypes.byref(self.view.c), x2.data_ptr(), m,
+                                            x2.stride(0) if m > 1 else max(x2.stride(0), self.view.k), y2.data_ptr(),
+                                            0 if y.dtype == torch.float16 else 1,
+                                            y2.stride(0) if m > 1 else max(y2.stride(0), self.view.n), int(x_is_rotated),
+                                            ctypes.byref(ctx))
+        if rc == 1:   # QWC_ERR_BLOCKED: a shape the fused form does not take
+            self.epoch -= 1
+            return super().forward(x_local, y, x_is_rotated, workspace, reduce)
+        _check(rc)
+
+
 class TPMlp:
     """Gate||up column parallel with the fused SwiGLU + FWHT epilogue, down row parallel, one all-reduce."""
 
     def __init__(self, hal: QWHal, gu_plane: torch.Tensor, dn_plane: torch.Tensor, hidden: int, inter: int,
-                 cont: ContainerKind, rank: int, world: int, group: Optional[dist.ProcessGroup] = None):
+                 cont: ContainerKind, rank: int, world: int, group: Optional[dist.ProcessGroup] = None,
+                 fused_allreduce: bool = False):
         gu, n_local = column_shard(gu_plane, 2 * inter, hidden, cont, rank, world, paired=True, quantum=math.lcm(32, cont.group))
         self.inter_local = n_local // 2
         dn, k_local = row_shard(dn_plane, hidden, inter, cont, rank, world)
@@ -117,7 +184,8 @@ class TPMlp:
             raise QWGemmError(4, "gate/up and down shards disagree on the local intermediate size")
         dev = torch.device("cuda", hal.device.index)
         self.gate_up = ColumnParallelLinear(hal, gu.to(dev), n_local, hidden, cont, epi=EPI_SILU_PAIR_FWHT)
-        self.down = RowParallelLinear(hal, dn.to(dev), hidden, k_local, cont, group)
+        fused = fused_allreduce and world > 1 and dist.is_initialized() and dist.get_backend(group) == "nccl"
+        self.down = (FusedRowParallelLinear if fused else RowParallelLinear)(hal, dn.to(dev), hidden, k_local, cont, group)
 
     def forward(self, x: torch.Tensor, h_local: torch.Tensor, y: torch.Tensor, ws_gu=None, ws_dn=None, x_is_rotated=False):
         """x f16 [m, hidden]; h_local f16 [m, inter_local] (rotated, scratch); y f32 [m, hidden] (all-reduced)."""

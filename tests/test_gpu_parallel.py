@@ -47,6 +47,25 @@ def _worker(rank, world, port, results):
             err = np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max()
             assert err < 3e-3, ("tp mlp", m, err)
 
+        # ---- the same MLP with the all-reduce fused into the down projection's kernel (peer stores + flags over symmetric
+        # memory): same answer as the oracle, identical bits on every rank, and stable over many calls (two buffers in turn)
+        mlp_f = par.TPMlp(hal, torch.from_numpy(gu.reshape(-1)), torch.from_numpy(dn.reshape(-1)), hidden, inter, cont, rank, world,
+                          fused_allreduce=True)
+        assert isinstance(mlp_f.down, par.FusedRowParallelLinear)
+        for it_ in range(6):
+            m = (1, 8, 3)[it_ % 3]
+            x = rng.standard_normal((m, hidden)).astype(np.float16)
+            h_loc = torch.empty((m, mlp_f.inter_local), dtype=torch.float16, device="cuda")
+            y = torch.full((m, hidden), float("nan"), dtype=torch.float32, device="cuda")
+            mlp_f.forward(torch.from_numpy(x).cuda(), h_loc, y)
+            ref = qo.matmul(dn, fmt, qo.swiglu_f16(qo.matmul(gu, fmt, x), rotate=True), x_is_rotated=True)
+            err = np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max()
+            assert err < 3e-3, ("tp mlp fused", m, err)
+            gathered = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(gathered, y)
+            assert all(torch.equal(gathered[0], g) for g in gathered), "ranks disagree bitwise"
+        assert hal.device_status() == 0
+
         # ---- expert-parallel MoE: tokens sharded over ranks, experts sharded over ranks
         e, k, hid, it, t_total = 16, 4, 256, 128, 96
         bgu = qo.quantize(rng.normal(0, 0.05, (e * 2 * it, hid)).astype(np.float32), fmt)
