@@ -116,6 +116,9 @@ int qwc_fwht32_f16(qwc_hal* hal, qwc_stream stream, void* x_f16, int64_t count);
 int qwc_rmsnorm_fwht(qwc_hal* hal, qwc_stream stream, const void* x_f16, const void* gamma_f16, void* y_f16,
                      void* residual_f16, int64_t rows, int64_t hidden, float eps, int32_t rotate);
 
+/* QWGemm.encodeCast (QWGemm.swift:302-320): the f32 -> f16 cast seam after an f32-emitting GEMV; count % 8 == 0. */
+int qwc_cast_f32_to_f16(qwc_hal* hal, qwc_stream stream, const float* x_f32, void* y_f16, int64_t count);
+
 /* Greedy head: tokens[r] = argmax_c logits[r, c] in the reference's key order (value, then lower column; NaN lowest, +0
  * above -0) — the pair encodeHQ4F32V4Argmax + encodeArgmaxFin (Sources/Operators/QWGEMM/QWGemmF32.swift:201-307; kernels
  * Sources/QWMetal/include/qw_gemm_f32_common.metalh:31-57, Sources/QWMetal/head_sampling/qwhead.metal:241-270) after the

@@ -42,6 +42,7 @@ SIGNATURES = {
     "qwc_block_bytes": (_i64, [_i32, _i32, _i32]),
     "qwc_gemm_plan": (ctypes.c_int, [_i64, _i64, _i64, _i32, _i32, _i32, _i32, _i64, ctypes.POINTER(PlanC)]),
     "qwc_fwht32_f16": (ctypes.c_int, [_vp, _vp, _vp, _i64]),
+    "qwc_cast_f32_to_f16": (ctypes.c_int, [_vp, _vp, _vp, _vp, _i64]),
     "qwc_head_argmax": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "qwc_rmsnorm_fwht": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _i32]),
     "qwc_dequant": (ctypes.c_int, [_vp, _vp, _WV, _vp, _i32, _i32]),

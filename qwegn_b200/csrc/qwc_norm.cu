@@ -107,6 +107,21 @@ __global__ void __launch_bounds__(1024) qwc_rmsnorm_fwht_kernel(const __half* __
     }
 }
 
+// The explicit f32 -> f16 cast seam between the f32-emitting GEMV doors and the f16 engine storage
+// (QWGemm.encodeCast, Sources/Operators/QWGEMM/QWGemm.swift:302-320): 8 elements per thread, round to nearest even.
+__global__ void __launch_bounds__(256) qwc_cast_f32_to_f16_kernel(const float4* __restrict__ x, uint4* __restrict__ y, int64_t n8) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const float4 a = x[2 * i], b = x[2 * i + 1];
+        uint4 o;
+        __half2* h = reinterpret_cast<__half2*>(&o);
+        h[0] = __floats2half2_rn(a.x, a.y);
+        h[1] = __floats2half2_rn(a.z, a.w);
+        h[2] = __floats2half2_rn(b.x, b.y);
+        h[3] = __floats2half2_rn(b.z, b.w);
+        y[i] = o;
+    }
+}
+
 // Greedy head: token[row] = argmax over the vocabulary of logits[row, :] with the reference's key order
 // (qwg_gemv_am_fold4 / qwg_head_argmax_fin: Sources/QWMetal/include/qw_gemm_f32_common.metalh:31-57,
 // Sources/QWMetal/head_sampling/qwhead.metal:241-270; qw_sortable_f32_u32, include/qw_fastmath_safe.metalh:21-25):
@@ -161,6 +176,24 @@ __global__ void __launch_bounds__(1024) qwc_head_argmax_kernel(const float* __re
 }
 
 }  // namespace
+
+extern "C" int qwc_cast_f32_to_f16(qwc_hal* hal, qwc_stream stream, const float* x_f32, void* y_f16, int64_t count) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    // QWGemm.swift:308-311: the count must be positive and divide 8 (badWeights there)
+    if (count <= 0 || count % 8 != 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "cast f32->f16: n=%lld must be positive and divide 8", (long long)count);
+    if (!x_f32 || !y_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    if ((reinterpret_cast<uintptr_t>(x_f32) | reinterpret_cast<uintptr_t>(y_f16)) % 16 != 0)
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "buffers must be 16-byte aligned");
+    const int64_t n8 = count / 8;
+    int64_t blocks = (n8 + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(hal->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    qwc_cast_f32_to_f16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(x_f32), static_cast<uint4*>(y_f16), n8);
+    QWC_CUDA_TRY(cudaGetLastError());
+    return QWC_OK;
+}
 
 extern "C" int qwc_head_argmax(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t ld, int64_t rows, int64_t n,
                                int32_t* tokens) {

@@ -207,6 +207,15 @@ class QWGemm:
         _check(_lib.load().qwc_fwht32_f16(hal.handle, _stream_ptr(stream), x.data_ptr(), x.numel()))
 
     @staticmethod
+    def encodeCast(hal: QWHal, x32: torch.Tensor, y16: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """f32 -> f16 cast seam (QWGemm.swift:302-320)."""
+        if x32.dtype != torch.float32 or y16.dtype != torch.float16 or not x32.is_contiguous() or not y16.is_contiguous():
+            raise QWGemmError(2, "cast takes contiguous f32 in, f16 out")
+        if y16.numel() < x32.numel():
+            raise QWGemmError(2, "cast output too small")
+        _check(_lib.load().qwc_cast_f32_to_f16(hal.handle, _stream_ptr(stream), x32.data_ptr(), y16.data_ptr(), x32.numel()))
+
+    @staticmethod
     def encodeArgmax(hal: QWHal, logits: torch.Tensor, tokens: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
         """Greedy token per row of f32 logits [rows, vocab] in the reference's key order (QWGemmF32.swift:201-307)."""
         if logits.dtype != torch.float32 or tokens.dtype != torch.int32 or not logits.is_cuda or logits.stride(-1) != 1:

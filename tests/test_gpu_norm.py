@@ -80,3 +80,16 @@ def test_head_argmax_matches_the_oracle(hal, oracle, rows, n):
     zeros[0, 0] = -0.0
     q.QWGemm.encodeArgmax(hal, zeros, tok[:1])
     assert int(tok[0]) == int(oracle.head_argmax(zeros.cpu().numpy())[0])
+
+
+def test_cast_seam(hal):
+    import qwegn_b200 as q
+    x = torch.randn(4096 + 8, device="cuda") * 300.0
+    x[:4] = torch.tensor([65504.0, 70000.0, -1e-8, float("nan")], device="cuda")
+    y = torch.empty(x.numel(), dtype=torch.float16, device="cuda")
+    q.QWGemm.encodeCast(hal, x, y)
+    ref = x.to(torch.float16)
+    assert torch.equal(y[:3], ref[:3]) and torch.equal(y[4:], ref[4:]) and bool(torch.isnan(y[3]))
+    with pytest.raises(q.QWGemmError) as e:   # QWGemm.swift:308-311
+        q.QWGemm.encodeCast(hal, x[:12].contiguous(), y[:12].contiguous())
+    assert e.value.case == "badWeights"
