@@ -196,10 +196,11 @@ def test_decode_gemv_bench_shape_properties(hal, oracle):
 
 
 def test_k_sliced_call_needs_and_uses_the_workspace(hal, oracle):
-    # 16 tokens x K = 5120: the staged activations exceed their shared-memory share, K is processed in slices
-    # and the raw sums travel through the caller's workspace.
+    # 15 tokens x K = 5120 (the largest batch of the stream kernel; 16 and up take the tensor path): the staged
+    # activations exceed their shared-memory share, K is processed in slices and the raw sums travel through the
+    # caller's workspace.
     import qwegn_b200 as q
-    n, k, m = 200, 5120, 16
+    n, k, m = 200, 5120, 15
     fmt = oracle.HQ4_G32
     rng = np.random.default_rng(8)
     blocks = oracle.quantize(rng.normal(0.0, 0.02, (n, k)).astype(np.float32), fmt)

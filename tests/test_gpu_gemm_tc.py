@@ -24,7 +24,7 @@ def _run(q, hal, view, x, out_dtype=torch.float16, rotated=False):
 
 
 @pytest.mark.parametrize("name", ["HQ4_G32", "HQ8_G32"])
-@pytest.mark.parametrize("shape", [(17, 128, 128), (64, 200, 512), (256, 128, 1024), (300, 1000, 640), (1024, 384, 2560)])
+@pytest.mark.parametrize("shape", [(16, 128, 128), (17, 128, 128), (64, 200, 512), (256, 128, 1024), (300, 1000, 640), (1024, 384, 2560)])
 def test_prefill_vs_oracle(hal, oracle, name, shape):
     import qwegn_b200 as q
     m, n, k = shape
