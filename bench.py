@@ -468,7 +468,11 @@ def bench_moe(q, hal):
     ms = _time_call(lambda: op.encodeResident(x, lg, outp, sc), 20)
     flops = 2.0 * t * k * (2 * inter * h + h * inter)
     wbytes = e * (2 * inter * (h // 32) * 20 + h * (inter // 32) * 20)
+    # the decode / verify size of the same block (8 tokens = 64 pairs, up to 64 experts touched): served by the grouped path
+    x8, lg8, out8 = x[:8].contiguous(), lg[:8].contiguous(), torch.empty((8, h), device="cuda")
+    ms8 = _time_call(lambda: op.encodeResident(x8, lg8, out8, sc), 20)
     return {"us": round(ms * 1e3, 1), "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 1), "weight_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1),
+            "decode_T8_us": round(ms8 * 1e3, 1),
             "bound": "per-K-tile hand-offs between converter warps, MMA issue and epilogue at 64 rows per expert: neither the HBM roof (~80 us) nor the tensor roof binds yet"}
 
 
