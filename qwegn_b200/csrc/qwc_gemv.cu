@@ -41,6 +41,12 @@ template <> struct StreamCfg<FMT_HQ4_G32_M5> { static constexpr int kUnitBytes =
 template <> struct StreamCfg<FMT_HQ8_G32> { static constexpr int kUnitBytes = 36, kGroupUnits = 4; };
 template <> struct StreamCfg<FMT_HQ4_G64> { static constexpr int kUnitBytes = 18, kGroupUnits = 4; };
 
+// One unit of work of the segment mode: output columns [col0, col0 + cols) of one expert (weight rows w_row0 + col,
+// plus n_out for the up half of a paired bank), for the m expert-sorted rows starting at x_row0 (same rows of y).
+struct qwc_gemv_seg {
+    int32_t w_row0, col0, cols, x_row0, m, pad0, pad1, pad2;
+};
+
 struct GemvParams {
     const uint8_t* blocks;
     int64_t row_bytes;
@@ -71,6 +77,10 @@ struct GemvParams {
     int red_bytes;    // smem bytes of the team reduction region
     int pdl;          // launched with programmatic stream serialization: weights prefetch before the dependency wait
     int use_tmap;     // full 16-row tiles arrive by one 2-D tensor copy instead of 16 row copies
+    // segment mode (see the kernel): null in the ordinary one-bank form
+    const qwc_gemv_seg* segs;
+    const int32_t* seg_count;
+    int seg_grid, seg_cols;   // host side: capacity of the list (= grid) and output columns per entry
     // fused one-shot all-reduce over peer memory (row-parallel shards of a tensor-parallel group; ar_world > 1):
     int ar_world, ar_rank;
     uint32_t ar_epoch;        // call number: the flag value that marks this call's data as complete
@@ -201,6 +211,7 @@ template <int FMT, int NT, int SUB>
 __global__ void __launch_bounds__(kThreads, 1)
 qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) {
     using C = StreamCfg<FMT>;
+    if (p.segs != nullptr && static_cast<int>(blockIdx.x) >= *p.seg_count) return;   // whole CTA: nothing is set up yet
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: [x region][reduction region][barriers][stages...]
     uint8_t* xs = smem;
@@ -235,8 +246,23 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     // SUB weight sub-tiles of 16 rows.  Job i goes to team i % T in round i / T.  The row quanta are dealt evenly,
     // the first q_rem CTAs taking one more.
     const int bq = static_cast<int>(blockIdx.x);
-    const int rb = (p.q_lo * bq + min(bq, p.q_rem)) * p.row_quantum;
-    const int re = rb + (p.q_lo + (bq < p.q_rem ? 1 : 0)) * p.row_quantum;
+    int rb = (p.q_lo * bq + min(bq, p.q_rem)) * p.row_quantum;
+    int re = rb + (p.q_lo + (bq < p.q_rem ? 1 : 0)) * p.row_quantum;
+    // Segment mode (decode-time mixture of experts): CTA b serves entry b of a device-side list, each entry one expert's
+    // weight rows [w_row0 + col0, ...) of a stacked bank, that expert's few tokens, and its own rows of x and y.
+    int M_ = p.m;
+    const __half* X_ = p.x;
+    void* Y_ = p.y;
+    int64_t wbase = 0;   // weight row of output column 0
+    if (p.segs != nullptr) {
+        const qwc_gemv_seg sg = p.segs[bq];   // the host launches exactly *seg_count CTAs' worth or more; extra CTAs left above
+        rb = sg.col0;
+        re = sg.col0 + sg.cols;
+        M_ = sg.m;
+        X_ = p.x + static_cast<int64_t>(sg.x_row0) * p.ldx;
+        Y_ = static_cast<char*>(p.y) + static_cast<int64_t>(sg.x_row0) * p.ldy * (p.y_f16 ? 2 : 4);
+        wbase = sg.w_row0;
+    }
     constexpr int kJobRows = SUB == 4 ? 32 : 16;
     const int njobs = (re - rb + kJobRows - 1) / kJobRows;
     const int E = SUB * p.nchunks;  // stage fills per job
@@ -247,7 +273,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         const int out0 = rb + job * kJobRows + (SUB == 4 ? (sub & 1) * 16 : 0);
         valid = min(kTileRows, re - out0);
         const bool up = SUB == 2 ? sub == 1 : (SUB == 4 ? sub >= 2 : false);
-        return static_cast<int64_t>(out0) + (up ? p.n_out : 0);
+        return wbase + static_cast<int64_t>(out0) + (up ? p.n_out : 0);
     };
 
     if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -338,7 +364,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     int xsw[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const int tok = min(nt * 8 + gid, p.m - 1);
+        const int tok = min(nt * 8 + gid, M_ - 1);
         xtok[nt] = xs_a + static_cast<uint32_t>(tok) * p.units * 64;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) xsw[nt][cc] = (cc ^ t ^ (tok & 1)) << 4;
@@ -368,8 +394,8 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     // h = 1, 2, 4, 8, 16 order), and writes one 16-byte chunk.  Items are taken two at a time so that both global
     // loads are in flight together.
     const int t4 = lane & 3, sub8 = lane >> 2;
-    const int items = p.m * p.units;  // (token, unit) pairs
-    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.ldx % 8 == 0);
+    const int items = M_ * p.units;  // (token, unit) pairs
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(X_) % 16 == 0) && (p.ldx % 8 == 0);
     struct StageItem {
         const __half* src;
         int tok, unit;
@@ -380,7 +406,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         si.live = it < items;
         si.tok = si.live ? it / p.units : 0;
         si.unit = si.live ? it - si.tok * p.units : 0;
-        si.src = p.x + si.tok * p.ldx + static_cast<int64_t>(p.unit0 + si.unit) * 32 + 8 * t4;
+        si.src = X_ + si.tok * p.ldx + static_cast<int64_t>(p.unit0 + si.unit) * 32 + 8 * t4;
         return si;
     };
     auto load_item = [&](const StageItem& si) {
@@ -585,7 +611,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                 for (int i = 0; i < 4; ++i) {
                     const int row = out0 + ot * 16 + gid + 8 * (i >> 1);
                     const int tok = nt * 8 + 2 * t + (i & 1);
-                    const bool live = row < re && tok < p.m;
+                    const bool live = row < re && tok < M_;
                     float v = g4[i], u = u4[i];
                     if (live && p.acc_in) {
                         v += p.partial[static_cast<int64_t>(tok) * p.n + row];
@@ -600,12 +626,12 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                             hval[ot][nt][i] = __half2float(__float2half_rn(v));
                         } else if (SUB == 1 && p.ar_world > 1) {
                             // the partial sum goes straight into every rank's inbox (peer stores over NVLink), its own too
-                            const int64_t o = (static_cast<int64_t>(p.ar_rank) * p.m + tok) * p.n + row;
+                            const int64_t o = (static_cast<int64_t>(p.ar_rank) * M_ + tok) * p.n + row;
                             for (int r = 0; r < p.ar_world; ++r) p.ar_inbox[r][o] = v;
                         } else {
                             const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
-                            if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(v);
-                            else static_cast<float*>(p.y)[o] = v;
+                            if (p.y_f16) static_cast<__half*>(Y_)[o] = __float2half_rn(v);
+                            else static_cast<float*>(Y_)[o] = v;
                         }
                     }
                 }
@@ -621,18 +647,18 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int lrow = ot * 16 + gid + 8 * (i >> 1), tok = nt * 8 + 2 * t + (i & 1);
-                        if (tok < p.m) hbuf[tok * 32 + lrow] = hval[ot][nt][i];
+                        if (tok < M_) hbuf[tok * 32 + lrow] = hval[ot][nt][i];
                     }
                 }
             if (W > 1) named_bar_sync(1 + team, team_threads); else __syncwarp();
-            for (int tok = wj; tok < p.m; tok += W) {
+            for (int tok = wj; tok < M_; tok += W) {
                 float v = hbuf[tok * 32 + lane];
 #pragma unroll
                 for (int h = 1; h < 32; h <<= 1) v = fwht_xor_stage(v, h, (lane & h) != 0);
                 v = __fmul_rn(v, qwc_inv_sqrt32());
                 const int64_t o = static_cast<int64_t>(tok) * p.ldy + out0 + lane;
-                if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(v);
-                else static_cast<float*>(p.y)[o] = __half2float(__float2half_rn(v));
+                if (p.y_f16) static_cast<__half*>(Y_)[o] = __float2half_rn(v);
+                else static_cast<float*>(Y_)[o] = __half2float(__float2half_rn(v));
             }
         }
         if (W > 1) named_bar_sync(1 + team, team_threads); else __syncwarp();  // red is reused by the next job
@@ -664,13 +690,13 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         named_bar_sync(11, kConsumerWarps * 32);
         const int rows_cta = re - rb;
         const float* inbox = p.ar_inbox[p.ar_rank];
-        for (int i = threadIdx.x; i < rows_cta * p.m; i += kConsumerWarps * 32) {
+        for (int i = threadIdx.x; i < rows_cta * M_; i += kConsumerWarps * 32) {
             const int tok = i / rows_cta, row = rb + (i - tok * rows_cta);
             float sum = 0.0f;
-            for (int r = 0; r < p.ar_world; ++r) sum += __ldcg(inbox + (static_cast<int64_t>(r) * p.m + tok) * p.n + row);
+            for (int r = 0; r < p.ar_world; ++r) sum += __ldcg(inbox + (static_cast<int64_t>(r) * M_ + tok) * p.n + row);
             const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
-            if (p.y_f16) static_cast<__half*>(p.y)[o] = __float2half_rn(sum);
-            else static_cast<float*>(p.y)[o] = sum;
+            if (p.y_f16) static_cast<__half*>(Y_)[o] = __float2half_rn(sum);
+            else static_cast<float*>(Y_)[o] = sum;
         }
     }
 }
@@ -765,6 +791,8 @@ bool plan_geometry(int units, int m, int nt, int sub, int jobs, int budget, Stre
     // at most 8 teams: 16 single-warp teams need 18 stages, which forces 32-unit chunks, and narrow chunks cost far more
     // than wide teams (N = 248320: 198 us with 16 x 1 warps and 32-unit chunks, 139 us with 8 x 2 warps and 56-unit chunks)
     while (teams < jobs && teams < 8) teams <<= 1;
+    // short rows (K <= 1024): a job is a handful of groups, so a warp takes a whole job alone and there is no team reduction
+    if (units <= 32 && jobs >= 16) teams = 16;
     static const int env_w = getenv("QWC_GEMV_W") ? atoi(getenv("QWC_GEMV_W")) : 0;
     static const int env_chunk = getenv("QWC_GEMV_CHUNK") ? atoi(getenv("QWC_GEMV_CHUNK")) : 0;
     if (env_w == 1 || env_w == 2 || env_w == 4 || env_w == 8 || env_w == 16) teams = kConsumerWarps / env_w;
@@ -841,6 +869,10 @@ int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_u
     int grid = hal->sm_count;
     if (grid > quanta) grid = quanta;
     if (grid < 1) grid = 1;
+    if (p.segs != nullptr) {   // segment mode: one CTA per list entry, the list's capacity is the grid
+        if (slices > 1) return qwc_fail(QWC_ERR_BLOCKED, "segment mode takes one K slice (tokens x K x 2 B <= 112 KB)");
+        grid = p.seg_grid;
+    }
     for (int s = 0; s < slices; ++s) {
         GemvParams q = p;
         q.q_lo = quanta / grid;
@@ -851,7 +883,7 @@ int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_u
         q.acc_in = s > 0;
         q.acc_out = s + 1 < slices;
         StreamGeom g;
-        const int rows_per_cta = (p.n_out + grid - 1) / grid;
+        const int rows_per_cta = p.segs != nullptr ? p.seg_cols : (p.n_out + grid - 1) / grid;
         const int job_rows = sub == 4 ? 32 : 16;
         const int jobs = (rows_per_cta + job_rows - 1) / job_rows;
         if (!plan_geometry<FMT>(q.units, q.m, NT, sub, jobs, kSmemBudget, &g))
@@ -995,6 +1027,46 @@ int qwc_launch_gemv_ar(const qwc_hal* hal, cudaStream_t st, const qwc_weight_vie
         case FMT_HQ4_G32_M5: return launch_fmt<FMT_HQ4_G32_M5>(hal, st, p, m, stream_ok, total_units, ws);
         case FMT_HQ8_G32: return launch_fmt<FMT_HQ8_G32>(hal, st, p, m, stream_ok, total_units, ws);
         case FMT_HQ4_G64: return launch_fmt<FMT_HQ4_G64>(hal, st, p, m, stream_ok, total_units, ws);
+        default: return qwc_fail(QWC_ERR_BAD_WEIGHTS, "unsupported container");
+    }
+}
+
+// Segment mode of the stream kernel (decode-time mixture of experts): `bank` is the stacked expert bank, xs the
+// expert-sorted (rotated) activation rows, y the expert-sorted outputs [pairs, n_out]; entry i of the device-side list
+// `segs` (at most max_segs entries, *seg_count valid) names one expert's column range and its <= 8 rows.
+int qwc_launch_gemv_segments(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* bank, const void* xs, int64_t ldx,
+                             void* y, int y_dtype, int64_t ldy, int epilogue, int64_t n_out, int seg_cols, const void* segs,
+                             const int32_t* seg_count, int64_t max_segs) {
+    GemvParams p{};
+    const int fmt = qwc_fmt_of(*bank);
+    const int64_t bb = qwc_block_bytes(bank->kind, bank->bits, bank->group);
+    const int group = fmt == FMT_HQ4_G64 ? 64 : 32;
+    p.blocks = static_cast<const uint8_t*>(bank->blocks);
+    p.row_bytes = (bank->k / group) * bb;
+    p.x = static_cast<const __half*>(xs);
+    p.ldx = ldx;
+    p.y = y;
+    p.ldy = ldy;
+    p.status = hal->status;
+    p.n = static_cast<int>(bank->n);
+    p.n_out = static_cast<int>(n_out);
+    p.m = 8;   // sizes the activation region; a CTA stages only its entry's rows
+    p.y_f16 = y_dtype == QWC_F16;
+    p.epilogue = epilogue;
+    p.x_is_rotated = 1;
+    p.row_quantum = epilogue == QWC_EPI_SILU_PAIR_FWHT ? 32 : 1;
+    p.pdl = hal->static_weights;
+    p.segs = static_cast<const qwc_gemv_seg*>(segs);
+    p.seg_count = seg_count;
+    p.seg_grid = static_cast<int>(max_segs);
+    p.seg_cols = seg_cols;
+    if (p.row_bytes % 16 != 0 || reinterpret_cast<uintptr_t>(bank->blocks) % 16 != 0)
+        return qwc_fail(QWC_ERR_BLOCKED, "segment mode needs 16-byte aligned bank rows");
+    const int total_units = static_cast<int>(bank->k / 32);
+    switch (fmt) {
+        case FMT_HQ4_G32_M5: return launch_stream<FMT_HQ4_G32_M5, 1>(hal, st, p, total_units, nullptr);
+        case FMT_HQ8_G32: return launch_stream<FMT_HQ8_G32, 1>(hal, st, p, total_units, nullptr);
+        case FMT_HQ4_G64: return launch_stream<FMT_HQ4_G64, 1>(hal, st, p, total_units, nullptr);
         default: return qwc_fail(QWC_ERR_BAD_WEIGHTS, "unsupported container");
     }
 }

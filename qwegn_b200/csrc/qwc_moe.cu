@@ -13,6 +13,8 @@
 int qwc_launch_gemm_tc_grouped(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, const qwc_moe_tile*,
                                const int32_t*, int64_t, void*, int, int64_t, int, int);
 bool qwc_gemm_tc_supported(const qwc_hal*, const qwc_weight_view*, int64_t, int);
+int qwc_launch_gemv_segments(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, void*, int, int64_t, int,
+                             int64_t, int, const void*, const int32_t*, int64_t);
 
 namespace {
 
@@ -62,6 +64,7 @@ __global__ void __launch_bounds__(128) qwc_moe_route_kernel(const float* __restr
     float total = 0.0f;
 #pragma unroll
     for (int j = 0; j < kMaxPer; ++j) {
+        if (j >= per) break;   // warp-uniform: slices beyond the expert count hold nothing
         float ex = valid[j] ? expf(pv[j] - max_logit) : 0.0f;
         pv[j] = ex;
         float s = ex;
@@ -82,6 +85,7 @@ __global__ void __launch_bounds__(128) qwc_moe_route_kernel(const float* __restr
         int bi = 0x7FFFFFFF;
 #pragma unroll
         for (int j = 0; j < kMaxPer; ++j) {
+            if (j >= per) break;
             const int id = lane + 32 * j;
             if (valid[j] && (pv[j] > bv || (pv[j] == bv && id < bi))) {
                 bv = pv[j];
@@ -375,7 +379,7 @@ __global__ void __launch_bounds__(kSortCta) qwc_moe_sort_kernel(const int32_t* _
         }
     }
     // tile lists: weight tiles fastest inside an activation tile, so consecutive tiles re-read the same activations
-    for (int ex = blockIdx.x; ex < e; ex += gridDim.x) {
+    for (int ex = blockIdx.x; ex < e && (tiles_gu != nullptr || tiles_dn != nullptr); ex += gridDim.x) {
         const int cnt = s_cnt[ex], ntx = s_tx[ex + 1] - s_tx[ex];
         for (int which = 0; which < 2; ++which) {
             const int rows = which == 0 ? gu_rows : dn_rows;
@@ -416,6 +420,45 @@ __global__ void __launch_bounds__(kSortCta) qwc_moe_sort_kernel(const int32_t* _
         } else {
             inv_perm[p] = -1;
         }
+    }
+}
+
+// Decode-time plan (at most 8 tokens, so an expert holds at most 8 sorted rows): one list entry per (active expert,
+// block of output columns) for the gate/up and for the down matmul, each entry served by one CTA of the streaming GEMV
+// in segment mode (the twin of the reference's per-(token, route) GEMVs with expert de-duplication,
+// Sources/Operators/QWGEMM/QWGemmMoE.swift:117-199).  Entry layout = qwc_gemv_seg of qwc_gemv.cu.
+struct MoeSeg {
+    int32_t w_row0, col0, cols, x_row0, m, pad0, pad1, pad2;
+};
+
+__global__ void __launch_bounds__(512) qwc_moe_decode_plan_kernel(const int32_t* __restrict__ expert_off, int e, int inter, int h,
+                                                                  int cols_gu, int cols_dn, MoeSeg* __restrict__ segs_gu,
+                                                                  MoeSeg* __restrict__ segs_dn, int32_t* __restrict__ seg_counts) {
+    __shared__ int s_warp[16];
+    const int ex = threadIdx.x, lane = ex & 31, warp = ex >> 5;
+    const int cnt = ex < e ? expert_off[ex + 1] - expert_off[ex] : 0;
+    const unsigned act = __ballot_sync(0xFFFFFFFFu, cnt > 0);
+    if (lane == 0) s_warp[warp] = __popc(act);
+    __syncthreads();
+    int before = __popc(act & ((1u << lane) - 1u)), total = 0;
+    for (int w = 0; w < 16; ++w) {
+        if (w < warp) before += s_warp[w];
+        total += s_warp[w];
+    }
+    const int ngu = (inter + cols_gu - 1) / cols_gu, ndn = (h + cols_dn - 1) / cols_dn;
+    if (ex == 0) {
+        seg_counts[0] = total * ngu;
+        seg_counts[1] = total * ndn;
+    }
+    if (cnt <= 0) return;
+    const int x0 = expert_off[ex];
+    for (int j = 0; j < ngu; ++j) {
+        MoeSeg sg{ex * 2 * inter, j * cols_gu, min(cols_gu, inter - j * cols_gu), x0, min(cnt, 8), 0, 0, 0};
+        segs_gu[before * ngu + j] = sg;
+    }
+    for (int j = 0; j < ndn; ++j) {
+        MoeSeg sg{ex * h, j * cols_dn, min(cols_dn, h - j * cols_dn), x0, min(cnt, 8), 0, 0, 0};
+        segs_dn[before * ndn + j] = sg;
     }
 }
 
@@ -650,7 +693,9 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (pairs <= (int64_t(1) << 18)) {
         // one launch: every CTA reads the whole pair list (<= 1 MB, L2-resident)
-        const int grid = static_cast<int>(pairs > 0 ? (pairs + kSortCta - 1) / kSortCta : 1);
+        int grid = static_cast<int>(pairs > 0 ? (pairs + kSortCta - 1) / kSortCta : 1);
+        // the tile lists are written expert by expert, experts dealt over the CTAs: a short pair list still gets 32 CTAs for that
+        if ((tiles_gu != nullptr || tiles_dn != nullptr) && grid < 32) grid = static_cast<int>(e < 32 ? e : 32);
         qwc_moe_sort_kernel<<<grid, kSortCta, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e), static_cast<int>(k),
                                                        moe_tile_rows(pairs, e), static_cast<int>(gu_rows), static_cast<int>(dn_rows),
                                                        paired, expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn, tile_counts);
@@ -780,6 +825,43 @@ int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank
     int32_t* tile_counts = reinterpret_cast<int32_t*>(sc + L.tile_counts);
     int rc;
     if ((rc = qwc_moe_route(hal, stream, logits, t, e, k, norm_topk, routed_scale, idx, wts))) return rc;
+    // ---- decode / verify sizes: per-expert streaming GEMVs over a device-side segment list
+    const int64_t rb_gu = (h / bank_gu->group) * qwc_block_bytes(bank_gu->kind, bank_gu->bits, bank_gu->group);
+    const int64_t rb_dn = (inter / bank_dn->group) * qwc_block_bytes(bank_dn->kind, bank_dn->bits, bank_dn->group);
+    static const bool no_decode_path = getenv("QWC_MOE_NO_DECODE_PATH") != nullptr;
+    if (t <= 8 && !no_decode_path && inter % 32 == 0 && rb_gu % 16 == 0 && rb_dn % 16 == 0 && 8 * h * 2 <= 112 * 1024 &&
+        8 * inter * 2 <= 112 * 1024 && reinterpret_cast<uintptr_t>(bank_gu->blocks) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(bank_dn->blocks) % 16 == 0) {
+        // as many column blocks per expert as keep one wave of CTAs busy when every pair names a different expert
+        // (whole 32-column blocks; the floors keep the lists inside the tile-list regions of the scratch)
+        const int64_t act = pairs < e ? pairs : e;
+        auto pick_cols = [&](int64_t n_out, int64_t floor_cols) {
+            const int64_t nseg = hal->sm_count / act > 1 ? hal->sm_count / act : 1;
+            int64_t c = ((n_out + nseg - 1) / nseg + 31) / 32 * 32;
+            if (c < floor_cols) c = floor_cols;
+            return static_cast<int>(c);
+        };
+        const int cols_gu = pick_cols(inter, 64), cols_dn = pick_cols(h, 128);
+        const int64_t active_max = pairs < e ? pairs : e;
+        const int64_t max_gu = active_max * ((inter + cols_gu - 1) / cols_gu), max_dn = active_max * ((h + cols_dn - 1) / cols_dn);
+        if (static_cast<size_t>(max_gu) * sizeof(MoeSeg) <= static_cast<size_t>(qwc_moe_max_tiles(pairs, e, 2 * inter)) * sizeof(qwc_moe_tile) &&
+            static_cast<size_t>(max_dn) * sizeof(MoeSeg) <= static_cast<size_t>(qwc_moe_max_tiles(pairs, e, h)) * sizeof(qwc_moe_tile)) {
+            cudaStream_t st = static_cast<cudaStream_t>(stream);
+            if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h,
+                                          QWC_EPI_NONE, nullptr, nullptr, tile_counts))) return rc;
+            MoeSeg* segs_gu = reinterpret_cast<MoeSeg*>(tiles_gu);
+            MoeSeg* segs_dn = reinterpret_cast<MoeSeg*>(tiles_dn);
+            qwc_moe_decode_plan_kernel<<<1, 512, 0, st>>>(expert_off, static_cast<int>(e), static_cast<int>(inter), static_cast<int>(h),
+                                                          cols_gu, cols_dn, segs_gu, segs_dn, tile_counts + 2);
+            QWC_CUDA_TRY(cudaGetLastError());
+            if ((rc = qwc_moe_gather(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs))) return rc;
+            if ((rc = qwc_launch_gemv_segments(hal, st, bank_gu, sc + L.xs, h, sc + L.hs, QWC_F16, inter, QWC_EPI_SILU_PAIR_FWHT, inter,
+                                               cols_gu, segs_gu, tile_counts + 2, max_gu))) return rc;
+            if ((rc = qwc_launch_gemv_segments(hal, st, bank_dn, sc + L.hs, inter, sc + L.dn, QWC_F16, h, QWC_EPI_NONE, h, cols_dn,
+                                               segs_dn, tile_counts + 3, max_dn))) return rc;
+            return qwc_moe_combine(hal, stream, sc + L.dn, QWC_F16, inv_perm, wts, t, k, h, out, out_dtype);
+        }
+    }
     // SwiGLU + FWHT run in the gate/up GEMM's epilogue when the tiles can pair 64 gate rows with their up rows
     const int32_t gu_epi = inter % 64 == 0 ? QWC_EPI_SILU_PAIR_FWHT : QWC_EPI_NONE;
     if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h, gu_epi,
