@@ -813,6 +813,33 @@ bool plan_geometry(int units, int m, int nt, int sub, int jobs, int budget, Stre
         }
         if (best_per == 0) continue;
         if (best_per / C::kGroupUnits < w && teams > 1 && env_w == 0) continue;  // fewer groups than warps: idle warps
+        // narrow chunks cost more than wide teams: if half as many teams allow a chunk of 48 units or more, take them
+        if (best_per < 48 && teams >= 4 && env_w == 0 && env_chunk == 0 && units >= 48) {
+            const int want2 = teams / 2 + 2;
+            for (int nch = 1; nch <= (units + quantum - 1) / quantum; ++nch) {
+                int per = (units + nch - 1) / nch;
+                per = ((per + quantum - 1) / quantum) * quantum;
+                if (per > max_chunk) continue;
+                if (per < 48) break;
+                const int stage_bytes = kTileRows * (per * C::kUnitBytes + kRowPad);
+                int stages = (budget - fixed) / stage_bytes;
+                if (stages > kMaxStages) stages = kMaxStages;
+                if (stages >= want2) {
+                    best_per = per;
+                    best_stages = stages;
+                    break;
+                }
+            }
+            if (best_per >= 48) {
+                g->chunk_units = best_per;
+                g->nchunks = (units + best_per - 1) / best_per;
+                g->stride = best_per * C::kUnitBytes + kRowPad;
+                g->team_warps = kConsumerWarps / (teams / 2);
+                g->stages = best_stages;
+                g->smem_bytes = fixed + best_stages * kTileRows * g->stride;
+                return true;
+            }
+        }
         g->chunk_units = best_per;
         g->nchunks = (units + best_per - 1) / best_per;
         g->stride = best_per * C::kUnitBytes + kRowPad;
