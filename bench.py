@@ -473,7 +473,7 @@ def bench_moe(q, hal):
     ms8 = _time_call(lambda: op.encodeResident(x8, lg8, out8, sc), 20)
     return {"us": round(ms * 1e3, 1), "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 1), "weight_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1),
             "decode_T8_us": round(ms8 * 1e3, 1),
-            "bound": "per-K-tile hand-offs between converter warps, MMA issue and epilogue at 64 rows per expert: neither the HBM roof (~80 us) nor the tensor roof binds yet"}
+            "bound": "about 100 cycles per tcgen05.mma instruction whatever its N: 64-token expert tiles use a third of the tensor rate; neither the HBM roof (~80 us) nor the tensor roof binds yet"}
 
 
 def bench_parallel(q, hal, rank, world, dist):
