@@ -4,17 +4,20 @@
 //
 //   Y[m, n] = sum_k Xrot[m, k] * Wrot[n, k],   f16 operands, f32 accumulate in tensor memory.
 //
-// One persistent CTA per SM walks (weight tile, token tile) pairs.  Per 64-wide K tile:
-//   * two TMA warps bring the packed weight rows, unchanged, into shared memory (2-D tensor copy, 128 rows x one
-//     raw step of 128 k) and the rotated activations (256 tokens x 64 k, 128-byte swizzle);
-//   * eight converter warps decode the packed blocks to f16 in registers (magic-bias form, one f16 FMA with scale
-//     and bias: the reference's in-register decode, qw_gemm_nax.metalh:114-127) and store them as the K-major,
-//     128-byte-swizzled operand tile the tensor core reads;
-//   * one thread issues tcgen05.mma (M = 128 weight rows, N = 256 tokens, K = 16) into a TMEM accumulator;
-//     tcgen05.commit releases the stage, and after the last K tile hands the accumulator to the epilogue;
-//   * four epilogue warps read the accumulator with tcgen05.ld (lane = weight row), round to the output type and
-//     store; two accumulators alternate so the epilogue of one tile overlaps the main loop of the next.
-// Weights are the M operand so that 256 tokens share every decoded weight (one decode per 256 FMAs per weight).
+// One persistent CTA per SM walks (weight tile, token tile) pairs.  Two variants share the roles and the pipeline:
+//   * qwc_gemm_ts_kernel (the default): converter threads own one weight row each, decode it in registers (magic-bias
+//     form, one f16 FMA with scale and bias: the reference's in-register decode, qw_gemm_nax.metalh:114-127) and write
+//     the f16 pairs into TENSOR memory with tcgen05.st; the MMAs take A from tensor memory and B (the activations) from
+//     shared memory; tiles of up to 192 tokens;
+//   * qwc_gemm_tc_kernel (QWC_TC_SS=1): the converters store a K-major, 128-byte-swizzled operand tile in shared memory
+//     (proxy fence before the hand-off); tiles of up to 256 tokens.
+// In both, per 64-wide K tile: two TMA warps bring the packed weight rows, unchanged, into shared memory (2-D tensor
+// copy, 128 rows x one raw step of 128 k) and the rotated activations (128-byte swizzle); one warp issues tcgen05.mma
+// (M = 128 weight rows, N = tokens, K = 16) into a TMEM accumulator; tcgen05.commit releases the stage and, after the
+// last K tile, hands the accumulator to four epilogue warps (tcgen05.ld, lane = weight row; plain store or the fused
+// SwiGLU (+ FWHT) epilogue); two accumulators alternate so the epilogue of one tile overlaps the main loop of the next.
+// Weights are the M operand so that all tokens of a tile share every decoded weight.  The grouped (mixture-of-experts)
+// door runs the same kernels over a device-side tile list.
 // Every mbarrier wait is bounded; a wait that gives up sets the device status word and the CTA winds down.
 #include <cuda.h>
 
