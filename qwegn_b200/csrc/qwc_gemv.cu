@@ -4,8 +4,10 @@
 //
 // The path is bound by HBM: every weight byte is read exactly once.  Design:
 //  * one persistent CTA per SM owns a contiguous range of output rows.  A producer warp streams the packed rows,
-//    unchanged, into a ring of shared-memory stages with 1-D bulk async copies (cp.async.bulk + mbarrier tx
-//    counts): 16 rows x one K chunk per stage, rows padded by 16 B so per-lane word reads hit 32 distinct banks;
+//    unchanged, into a ring of shared-memory stages: 16 rows x one K chunk per stage, one 2-D tensor copy (TMA) per
+//    stage with an mbarrier transaction count (per-row 1-D bulk copies for ragged tail tiles); rows are padded by 16 B
+//    and chunks are multiples of 8 units so per-lane word reads hit 32 distinct banks.  A slot of the ring is shared
+//    by the teams, so a fill counter published by the producer guards the parity waits (see the consumer loop);
 //  * the activations are rotated (FWHT-32, f32 butterflies, one rounding to f16) once per CTA into shared memory,
 //    stored in the k order and 16-byte-chunk swizzle the fragment loads want;
 //  * the 16 consumer warps form T teams of W warps.  A team owns one 16-row tile at a time (all K chunks), so the
@@ -18,6 +20,10 @@
 //    accumulate.  A SIMT FMA dot needs > 3 issue slots per weight and cannot keep up with the copy stream.  The k
 //    slots of an MMA are permuted (4 k from each of the 4 units a quad holds), which A and B share, so no shuffle
 //    is needed between the packed layout and the fragment layout.
+// Three optional forms of the same kernel: static-weights mode (programmatic dependent launch: the producer streams
+// weights while the previous kernel of the stream finishes), segment mode (CTA b serves entry b of a device-side list
+// of (expert bank rows, tokens) — the decode-time mixture of experts), and the fused all-reduce epilogue (row-parallel
+// shards of a tensor-parallel group: peer stores into every rank's inbox, flags, rank-ordered sum).
 #include <cuda.h>
 
 #include <cstdio>
