@@ -156,6 +156,18 @@ int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const vo
 size_t qwc_gemm_workspace_bytes(const qwc_hal* hal, const qwc_weight_view* w, int64_t m, int32_t epilogue,
                                 int32_t x_is_rotated);
 
+/* The f32-activation matmul door: QWGemmF32.encodeHQ4F32V4 / encodeHQ4F32BM (Sources/Operators/QWGEMM/QWGemmF32.swift:
+ * 143-199, 309-350; bodies Sources/QWMetal/include/qw_gemm_f32_common.metalh:59-225) with the f32 rotation
+ * encodeH32F32 (QWGemmF32.swift:46-54) folded in when x_is_rotated == 0.
+ *   y[m, n] = epi( x_rot[m, k] . W_rot[n, k]^T ),  x f32 rows ldx apart, rounded once to f16 after the (f32) rotation.
+ * epilogue, the reference's codes (qw_gemm_f32_common.metalh:15-20, 131-133): 0 none, 1 silu(y / scale), 2 sigmoid(y),
+ * 3 silu(y / scale) then FWHT-32 along n (n % 32 == 0).  y: f16 or f32 [m, n] rows ldy apart.  workspace: 256-byte
+ * aligned, qwc_gemm_f32_workspace_bytes() bytes.  Activations beyond the f16 range (|x_rot| > 65504) become infinite. */
+int qwc_gemm_f32(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const float* x_f32, int64_t m, int64_t ldx,
+                 void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, float scale, int32_t x_is_rotated,
+                 void* workspace, size_t workspace_bytes);
+size_t qwc_gemm_f32_workspace_bytes(const qwc_hal* hal, const qwc_weight_view* w, int64_t m, int32_t epilogue);
+
 /* No counterpart in the reference.  The small-M matmul door (m <= 16, same arguments and results as qwc_gemm) for
  * callers that cannot allocate device memory where they call it -- an operator inside an engine whose arena was
  * frozen at load time, a thread that must not risk the device-wide synchronisation of cudaMalloc, a host running

@@ -156,6 +156,27 @@ def matmul(blocks: np.ndarray, fmt: Format, x: np.ndarray, x_is_rotated: bool = 
     return y
 
 
+def matmul_f32(blocks: np.ndarray, fmt: Format, x: np.ndarray, epi: int = 0, scale: float = 1.0,
+               x_is_rotated: bool = True) -> np.ndarray:
+    """The f32-activation matmul (Sources/Operators/QWGEMM/QWGemmF32.swift:143-199, 309-350; kernel bodies
+    Sources/QWMetal/include/qw_gemm_f32_common.metalh:59-225 with the f32 decode of include/qw_dequant_f32.metalh:9-56):
+    y = epi(x_rot . W_rot^T), x f32 (rotated by encodeH32F32, QWGemmF32.swift:46-54, when it is not yet), weights
+    decoded in f32, epi 0 none / 1 silu(y/scale) / 2 sigmoid(y) / 3 silu(y/scale) then FWHT-32 along n
+    (qw_gemm_f32_common.metalh:15-20, 131-133)."""
+    w = dequant(blocks, fmt, f16_round=False, standard=False).astype(np.float64)
+    x = _c(x, np.float32).reshape(-1, w.shape[1])
+    xr = x if x_is_rotated else fwht32(x)
+    y = (xr.astype(np.float64) @ w.T).astype(np.float32)
+    if epi in (1, 3):
+        z = (y / np.float32(scale)).astype(np.float32)
+        y = (z / (np.float32(1.0) + np.exp(-z, dtype=np.float32))).astype(np.float32)
+    elif epi == 2:
+        y = (np.float32(1.0) / (np.float32(1.0) + np.exp(-y, dtype=np.float32))).astype(np.float32)
+    if epi == 3:
+        y = fwht32(y)
+    return y
+
+
 def swiglu_f16(gu: np.ndarray, rotate: bool = False) -> np.ndarray:
     gu = _c(gu, np.float32)
     m, two_i = gu.shape

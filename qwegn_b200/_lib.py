@@ -49,6 +49,8 @@ SIGNATURES = {
     "qwc_quantize": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp]),
     "qwc_gemm": (ctypes.c_int, [_vp, _vp, _WV, _vp, _i64, _i64, _vp, _i32, _i64, _i32, _i32, _vp, _sz]),
     "qwc_gemm_workspace_bytes": (_sz, [_vp, _WV, _i64, _i32, _i32]),
+    "qwc_gemm_f32": (ctypes.c_int, [_vp, _vp, _WV, _vp, _i64, _i64, _vp, _i32, _i64, _i32, ctypes.c_float, _i32, _vp, _sz]),
+    "qwc_gemm_f32_workspace_bytes": (_sz, [_vp, _WV, _i64, _i32]),
 }
 
 _lib = None

@@ -200,6 +200,35 @@ class QWGemm:
         return int(_lib.load().qwc_gemm_workspace_bytes(hal.handle, ctypes.byref(w.c), m, epi, int(x_is_rotated)))
 
     @staticmethod
+    def f32WorkspaceBytes(hal: QWHal, w: QWWeightView, m: int, epi: int = 0) -> int:
+        return int(_lib.load().qwc_gemm_f32_workspace_bytes(hal.handle, ctypes.byref(w.c), m, epi))
+
+    @staticmethod
+    def encodeHQ4F32V4(hal: QWHal, w: QWWeightView, x: torch.Tensor, y: torch.Tensor, rows: int = 1, epi: int = 0,
+                       scale: float = 1.0, x_is_rotated: bool = True, workspace: Optional[torch.Tensor] = None,
+                       stream: Optional[torch.cuda.Stream] = None) -> None:
+        """f32-activation matmul (QWGemmF32.swift:143-199; encodeHQ4F32BM :309-350 is the same call with more rows).
+        x f32 [rows, k] in the rotated basis (the reference's dataflow; x_is_rotated=False rotates here in f32);
+        epi 0 none, 1 silu(y/scale), 2 sigmoid, 3 silu(y/scale) + FWHT-32; y f16/f32 [rows, n]."""
+        if x.dtype != torch.float32 or not x.is_cuda or y.dtype not in (torch.float16, torch.float32) or not y.is_cuda:
+            raise QWGemmError(3, "x must be CUDA float32, y CUDA float16/float32")
+        x2 = x if x.dim() == 2 else x.view(1, -1)
+        y2 = y if y.dim() == 2 else y.view(1, -1)
+        if x2.stride(1) != 1 or y2.stride(1) != 1 or x2.shape[0] != rows or y2.shape[0] != rows:
+            raise QWGemmError(3, "x and y must hold `rows` contiguous rows")
+        if x2.shape[1] != w.k or y2.shape[1] != w.n:
+            raise QWGemmError(3, f"x is {tuple(x2.shape)}, y {tuple(y2.shape)}; the bank is n={w.n}, k={w.k}")
+        if workspace is None:
+            raise QWGemmError(3, "the f32 door needs a workspace of f32WorkspaceBytes() bytes")
+        _check(_lib.load().qwc_gemm_f32(hal.handle, _stream_ptr(stream), ctypes.byref(w.c), x2.data_ptr(), rows,
+                                        x2.stride(0) if rows > 1 else w.k, y2.data_ptr(),
+                                        F16 if y.dtype == torch.float16 else F32, y2.stride(0) if rows > 1 else w.n,
+                                        epi, float(scale), int(x_is_rotated), workspace.data_ptr(),
+                                        workspace.numel() * workspace.element_size()))
+
+    encodeHQ4F32BM = encodeHQ4F32V4
+
+    @staticmethod
     def encodeFwht32(hal: QWHal, x: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
         """In-place activation rotation (QWGemm.swift:285-300)."""
         if x.dtype != torch.float16 or not x.is_cuda or not x.is_contiguous():

@@ -135,3 +135,24 @@ def test_group_pairs_is_a_stable_counting_sort(oracle):
     te, tr = oracle.moe_tile_plan(off)
     cover = sum({1: 16, 2: 32, 3: 64}[int(r) >> 24] for r in tr)
     assert cover >= order.size and len(te) <= 8 + order.size // 64 + 1
+
+
+def test_f32_matmul_restatement_agrees_with_the_f16_one(oracle):
+    # same bank, f16-exact rotated activations: the f32 restatement (f32 decode) and the f16 one (f16-rounded decode)
+    # differ only by the weight rounding; and rotating inside equals rotating first
+    rng = np.random.default_rng(3)
+    n, k = 96, 512
+    for fmt in (oracle.HQ4_G32, oracle.HQ8_G32, oracle.HQ4_G64):
+        blocks = oracle.quantize(rng.normal(0.0, 0.05, (n, k)).astype(np.float32), fmt)
+        x = rng.standard_normal((3, k)).astype(np.float16)
+        a = oracle.matmul(blocks, fmt, x, x_is_rotated=True)
+        b = oracle.matmul_f32(blocks, fmt, x.astype(np.float32), 0, 1.0, True)
+        assert np.abs(a - b).max() <= 2e-3 * np.abs(a).max()
+        c = oracle.matmul_f32(blocks, fmt, x.astype(np.float32), 0, 1.0, False)
+        d = oracle.matmul_f32(blocks, fmt, oracle.fwht32(x.astype(np.float32)), 0, 1.0, True)
+        assert np.array_equal(c, d)
+        s = oracle.matmul_f32(blocks, fmt, x.astype(np.float32), 2, 1.0, True)
+        assert np.allclose(s, 1.0 / (1.0 + np.exp(-b.astype(np.float64))), atol=1e-6)
+        e3 = oracle.matmul_f32(blocks, fmt, x.astype(np.float32), 3, 2.0, True)
+        e1 = oracle.matmul_f32(blocks, fmt, x.astype(np.float32), 1, 2.0, True)
+        assert np.allclose(oracle.fwht32(e3), e1, atol=1e-5)   # the rotation is an involution
