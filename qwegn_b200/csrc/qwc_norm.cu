@@ -6,6 +6,8 @@
 // raw).  This is the step before every GEMM of the reference's engine: with it the matmuls are called with
 // x_is_rotated = 1 and do not rotate activations themselves.
 #include "qwc_common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -132,17 +134,26 @@ __device__ __forceinline__ uint32_t sortable_f32(float x) {
     return (u & 0x80000000u) ? ~u : (u ^ 0x80000000u);
 }
 
-__global__ void __launch_bounds__(1024) qwc_head_argmax_kernel(const float* __restrict__ logits, int64_t ld, int n,
+// A cluster of kArgmaxCluster CTAs shares one row: CTA r scans columns [r * per, (r + 1) * per), the winners meet in
+// the shared memory of CTA 0 of the cluster (distributed shared memory), which writes the token.
+constexpr int kArgmaxCluster = 8;
+
+__global__ void __launch_bounds__(1024) qwc_head_argmax_kernel(const float* __restrict__ logits, int64_t ld, int n_total,
                                                                int32_t* __restrict__ tokens) {
     __shared__ unsigned long long s_best[32];
+    __shared__ unsigned long long s_cluster[kArgmaxCluster];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int crank = static_cast<int>(cluster.block_rank());
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
+    const float* row = logits + static_cast<int64_t>(blockIdx.y) * ld;
+    const int per = (((n_total + kArgmaxCluster - 1) / kArgmaxCluster) + 3) & ~3;
+    const int lo = min(n_total, crank * per), n = min(n_total, lo + per);
     unsigned long long best = 0ull;
     const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
-    int c0 = 0;
+    int c0 = lo;
     if (vec) {
-        const int n4 = n & ~3;
-        for (int c = tid * 4; c < n4; c += 4096) {
+        const int n4 = lo + ((n - lo) & ~3);
+        for (int c = lo + tid * 4; c < n4; c += 4096) {
             const float4 v = *reinterpret_cast<const float4*>(row + c);
             const float f[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -171,7 +182,14 @@ __global__ void __launch_bounds__(1024) qwc_head_argmax_kernel(const float* __re
             const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
             best = other > best ? other : best;
         }
-        if (lane == 0) tokens[blockIdx.x] = static_cast<int32_t>(~static_cast<uint32_t>(best & 0xFFFFFFFFull));
+        if (lane == 0) *cluster.map_shared_rank(&s_cluster[crank], 0) = best;
+    }
+    cluster.sync();
+    if (crank == 0 && tid == 0) {
+        best = s_cluster[0];
+#pragma unroll
+        for (int r = 1; r < kArgmaxCluster; ++r) best = s_cluster[r] > best ? s_cluster[r] : best;
+        tokens[blockIdx.y] = static_cast<int32_t>(~static_cast<uint32_t>(best & 0xFFFFFFFFull));
     }
 }
 
@@ -203,8 +221,21 @@ extern "C" int qwc_head_argmax(qwc_hal* hal, qwc_stream stream, const float* log
     if (rows < 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "rows is negative");
     if (rows == 0) return QWC_OK;
     if (!logits || !tokens) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
-    qwc_head_argmax_kernel<<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream)>>>(logits, ld, static_cast<int>(n), tokens);
-    QWC_CUDA_TRY(cudaGetLastError());
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kArgmaxCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    for (int64_t r0 = 0; r0 < rows; r0 += 32768) {   // grid.y carries the rows
+        const int64_t r = rows - r0 < 32768 ? rows - r0 : 32768;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kArgmaxCluster, static_cast<unsigned>(r), 1);
+        cfg.blockDim = dim3(1024, 1, 1);
+        cfg.stream = static_cast<cudaStream_t>(stream);
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        QWC_CUDA_TRY(cudaLaunchKernelEx(&cfg, qwc_head_argmax_kernel, logits + r0 * ld, ld, static_cast<int>(n), tokens + r0));
+    }
     return QWC_OK;
 }
 
