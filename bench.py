@@ -363,6 +363,9 @@ def run_ours(args):
         if "c1" in sections:
             extra["lm_head_greedy_N248320_K5120_M1"] = bench_lm_head(q, hal, peaks)
             torch.cuda.empty_cache()
+        if "c1" in sections:
+            extra["f32_activation_door_N17408_K5120"] = bench_f32_door(q, hal, n, k, args.warmup)
+            torch.cuda.empty_cache()
         if "sweep" in sections:
             sweep = {}
             for cname in ("HQ4_G32", "HQ8_G32", "HQ4_G64"):
@@ -413,6 +416,35 @@ def bench_lm_head(q, hal, peaks, steps=60):
     ref = int(torch.argmax(y[0]).item())
     return {"us": ms * 1e3, "GBps": nbytes / (ms * 1e-3) / 1e9, "frac_of_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "token_matches_torch_argmax": bool(int(tok.item()) == ref)}
+
+
+def bench_f32_door(q, hal, n, k, warmup, steps=400):
+    """The f32-activation door (rotated f32 rows in, f32 out) at the headline shape: stage kernel + GEMV (+ epilogue
+    kernel for the silu + FWHT epilogue).  Banks in rotation, larger than L2 together."""
+    import torch
+    cont = q.CONTAINERS["HQ4_G32"]
+    nb = max(2, -(-3 * L2_BYTES // (n * (k // 32) * 20)))
+    banks = make_banks(q, hal, n, k, cont, nb, seed=11)
+    stream = torch.cuda.current_stream()
+    out = {}
+    torch.cuda.synchronize()
+    hal.set_static_weights(True)   # the banks are complete
+    for m, epi in ((1, 0), (1, 3), (4, 0)):
+        x = torch.randn((m, k), device="cuda")
+        y = torch.empty((m, n), device="cuda")
+        ws = torch.empty(q.QWGemm.f32WorkspaceBytes(hal, banks[0], m, epi) + 256, dtype=torch.uint8, device="cuda")
+
+        def step(i):
+            q.QWGemm.encodeHQ4F32V4(hal, banks[i % nb], x, y, rows=m, epi=epi, scale=1.0, workspace=ws)
+
+        for i in range(max(3, warmup)):
+            step(i)
+        ms = time_region(step, steps, None, stream, graph=True) / steps
+        b = gemv_bytes(n, k, m)
+        out[f"M{m}_epi{epi}"] = {"us": round(ms * 1e3, 2), "GBps": round(b / (ms * 1e-3) / 1e9, 1)}
+    torch.cuda.synchronize()
+    hal.set_static_weights(False)
+    return out
 
 
 def _time_call(fn, iters, warm=3):

@@ -14,6 +14,12 @@ namespace {
 __global__ void __launch_bounds__(256) qwc_f32_stage_kernel(const float* __restrict__ x, int64_t ldx, __half* __restrict__ y,
                                                             int k8, int64_t total, int rotate) {
     const int lane = threadIdx.x & 31, t4 = lane & 3;
+    // Let a matmul launched with programmatic stream serialization start its weight prefetch now; it still waits for
+    // this whole grid (and its stores) before it reads the staged activations.  A no-op for ordinary launches.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // When this kernel was itself launched that way: wait for the grid before it (which may have produced x, or may
+    // still be reading the staging buffer of the previous call).  Returns at once for an ordinary launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // the loop bound is per warp (i - lane), so that all 32 lanes reach the shuffles together
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i - lane < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -55,6 +61,8 @@ template <typename OutT>
 __global__ void __launch_bounds__(256) qwc_f32_epilogue_kernel(const float* __restrict__ t, int64_t ldt, OutT* __restrict__ y,
                                                                int64_t ldy, int n, int64_t total, int epi, float scale) {
     const int lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // as in the stage kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i - lane < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const bool ok = i < total;
@@ -119,8 +127,16 @@ extern "C" int qwc_gemm_f32(qwc_hal* hal, qwc_stream stream, const qwc_weight_vi
         const int64_t total = m * k8;
         int64_t blocks = (total + 255) / 256;
         if (blocks > cap) blocks = cap;
-        qwc_f32_stage_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(x_f32, ldx, x16, k8, total, x_is_rotated ? 0 : 1);
-        QWC_CUDA_TRY(cudaGetLastError());
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+        cfg.blockDim = dim3(256);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = hal->static_weights ? 1 : 0;   // the decode-loop promise: kernels may be launched ahead of their predecessors' end
+        QWC_CUDA_TRY(cudaLaunchKernelEx(&cfg, qwc_f32_stage_kernel, x_f32, ldx, x16, k8, total, x_is_rotated ? 0 : 1));
     }
     int rc;
     if (epilogue == 0) rc = qwc_gemm(hal, stream, w, x16, m, w->k, y, y_dtype, ldy, QWC_EPI_NONE, 1, ws + off, workspace_bytes - off);
@@ -129,12 +145,23 @@ extern "C" int qwc_gemm_f32(qwc_hal* hal, qwc_stream stream, const qwc_weight_vi
     const int64_t total = m * w->n;
     int64_t blocks = (total + 255) / 256;
     if (blocks > cap) blocks = cap;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = hal->static_weights ? 1 : 0;
+    const float* tmp_c = tmp;
+    const int64_t ldt = w->n;
+    const int n_i = static_cast<int>(w->n);
     if (y_dtype == QWC_F16)
-        qwc_f32_epilogue_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, st>>>(tmp, w->n, static_cast<__half*>(y), ldy,
-                                                                                      static_cast<int>(w->n), total, epilogue, scale);
+        QWC_CUDA_TRY(cudaLaunchKernelEx(&cfg, qwc_f32_epilogue_kernel<__half>, tmp_c, ldt, static_cast<__half*>(y), ldy, n_i, total,
+                                        static_cast<int>(epilogue), scale));
     else
-        qwc_f32_epilogue_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(tmp, w->n, static_cast<float*>(y), ldy,
-                                                                                     static_cast<int>(w->n), total, epilogue, scale);
-    QWC_CUDA_TRY(cudaGetLastError());
+        QWC_CUDA_TRY(cudaLaunchKernelEx(&cfg, qwc_f32_epilogue_kernel<float>, tmp_c, ldt, static_cast<float*>(y), ldy, n_i, total,
+                                        static_cast<int>(epilogue), scale));
     return QWC_OK;
 }

@@ -73,3 +73,36 @@ def test_f32_door_refusals(hal, oracle):
         q.QWGemm.encodeHQ4F32V4(hal, view, x, y, workspace=ws[:64])
     with pytest.raises(q.QWGemmError):
         q.QWGemm.encodeHQ4F32V4(hal, view, x.half(), y, workspace=ws)
+
+
+def test_f32_door_back_to_back_with_static_weights(hal, oracle):
+    # the decode-loop promise lets the library launch kernels ahead of their predecessors' end: a chain of calls that
+    # share one workspace and feed each other must give the bits of the same chain run one call at a time
+    import qwegn_b200 as q
+    n = k = 1024
+    rng = np.random.default_rng(12)
+    blocks = oracle.quantize(rng.normal(0.0, 0.03, (n, k)).astype(np.float32), oracle.HQ4_G32)
+    view = q.QWWeightView(torch.from_numpy(blocks.reshape(-1)).cuda(), n, k, q.CONTAINERS["HQ4_G32"])
+    x0 = torch.from_numpy(rng.standard_normal((2, k)).astype(np.float32)).cuda()
+    ws = torch.empty(q.QWGemm.f32WorkspaceBytes(hal, view, 2, 3) + 256, dtype=torch.uint8, device="cuda")
+
+    def chain(sync):
+        a, b = x0.clone(), torch.empty_like(x0)
+        for _ in range(6):
+            q.QWGemm.encodeHQ4F32V4(hal, view, a, b, rows=2, epi=3, scale=0.5, workspace=ws)
+            if sync:
+                torch.cuda.synchronize()
+            a, b = b, a
+        torch.cuda.synchronize()
+        return a.clone()
+
+    ref = chain(True)
+    torch.cuda.synchronize()
+    hal.set_static_weights(True)
+    try:
+        got = chain(False)
+    finally:
+        torch.cuda.synchronize()
+        hal.set_static_weights(False)
+    assert torch.isfinite(ref).all() and torch.equal(ref, got)
+    assert hal.device_status() == 0
