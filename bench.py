@@ -501,8 +501,17 @@ def bench_moe(q, hal):
     flops = 2.0 * t * k * (2 * inter * h + h * inter)
     wbytes = e * (2 * inter * (h // 32) * 20 + h * (inter // 32) * 20)
     # the decode / verify size of the same block (8 tokens = 64 pairs, up to 64 experts touched): served by the grouped path
-    x8, lg8, out8 = x[:8].contiguous(), lg[:8].contiguous(), torch.empty((8, h), device="cuda")
-    ms8 = _time_call(lambda: op.encodeResident(x8, lg8, out8, sc), 20)
+    # timed the way a decode loop runs it: CUDA-graph replay, weights declared static, router logits that change from
+    # step to step (16 sets) so that the experts touched, and with them the weights read, differ between steps
+    x8, out8 = x[:8].contiguous(), torch.empty((8, h), device="cuda")
+    lg8 = [torch.randn((8, e), device="cuda") for _ in range(16)]
+    torch.cuda.synchronize()
+    hal.set_static_weights(True)
+    for i in range(3):
+        op.encodeResident(x8, lg8[i], out8, sc)
+    ms8 = time_region(lambda i: op.encodeResident(x8, lg8[i % 16], out8, sc), 320, None, torch.cuda.current_stream(), graph=True) / 320
+    torch.cuda.synchronize()
+    hal.set_static_weights(False)
     return {"us": round(ms * 1e3, 1), "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 1), "weight_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1),
             "decode_T8_us": round(ms8 * 1e3, 1),
             "bound": "about 100 cycles per tcgen05.mma instruction whatever its N: 64-token expert tiles use a third of the tensor rate; neither the HBM roof (~80 us) nor the tensor roof binds yet"}
