@@ -217,7 +217,12 @@ template <int FMT, int NT, int SUB>
 __global__ void __launch_bounds__(kThreads, 1)
 qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) {
     using C = StreamCfg<FMT>;
-    if (p.segs != nullptr && static_cast<int>(blockIdx.x) >= *p.seg_count) return;   // whole CTA: nothing is set up yet
+    if (p.segs != nullptr) {
+        // The segment list is the work of a kernel earlier in the stream: a programmatic launch must wait for it
+        // before the first read (nothing can be prefetched without the list anyway).
+        if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (static_cast<int>(blockIdx.x) >= *p.seg_count) return;   // whole CTA: nothing is set up yet
+    }
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: [x region][reduction region][barriers][stages...]
     uint8_t* xs = smem;

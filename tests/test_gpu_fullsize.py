@@ -128,3 +128,40 @@ def test_moe_block_t2048_e256_top8(hal, tokens):
         ref.index_add_(0, rows, dn * wts.reshape(-1)[sel].unsqueeze(1))
     _close(out, ref, 8e-3)
     assert hal.device_status() == 0
+
+
+def test_decode_moe_under_static_weights_matches_plain_launches(hal):
+    # the decode loop's promise (weights never written by in-flight work) lets kernels be launched ahead of their
+    # predecessors' end; back-to-back steps with changing routings must give the bits of steps run one at a time
+    import qwegn_b200 as q
+    t, e, k, hid, inter = 8, 256, 8, 2048, 512
+    bgu, _ = _bank(q, hal, e * 2 * inter, hid, "HQ4_G32", seed=17)
+    bdn, _ = _bank(q, hal, e * hid, inter, "HQ4_G32", seed=18)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(19)
+    x = torch.randn((t, hid), generator=gen, device="cuda").to(torch.float16)
+    lgs = [torch.randn((t, e), generator=gen, device="cuda") for _ in range(12)]
+    op = q.QWMoEOperator(hal, bgu, bdn, e, inter, k, norm_topk=True)
+    sc = torch.empty(op.scratchBytes(t), dtype=torch.uint8, device="cuda")
+
+    def run(sync):
+        outs = []
+        for lg in lgs:
+            o = torch.full((t, hid), float("nan"), device="cuda")
+            op.encodeResident(x, lg, o, sc)
+            if sync:
+                torch.cuda.synchronize()
+            outs.append(o)
+        torch.cuda.synchronize()
+        return outs
+
+    ref = run(True)
+    hal.set_static_weights(True)
+    try:
+        got = run(False)
+    finally:
+        torch.cuda.synchronize()
+        hal.set_static_weights(False)
+    for a, b in zip(ref, got):
+        assert torch.isfinite(a).all() and torch.equal(a, b)
+    assert hal.device_status() == 0
