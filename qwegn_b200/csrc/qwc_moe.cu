@@ -552,19 +552,38 @@ __global__ void __launch_bounds__(256) qwc_moe_combine_kernel(const DnT* __restr
         const int t = static_cast<int>(it / (h / 2));
         const int c = static_cast<int>(it % (h / 2)) * 2;
         float a0 = 0.0f, a1 = 0.0f;
-        for (int j = 0; j < k; ++j) {
-            const int pos = inv_perm[static_cast<int64_t>(t) * k + j];
-            if (pos < 0) continue;
-            const float w = wts[static_cast<int64_t>(t) * k + j];
-            if (sizeof(DnT) == 2) {
-                const __half2 v = *reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(dn) + static_cast<int64_t>(pos) * h + c);
-                a0 = fmaf(w, __low2float(v), a0);
-                a1 = fmaf(w, __high2float(v), a1);
-            } else {
-                const float2 v = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(dn) + static_cast<int64_t>(pos) * h + c);
-                a0 = fmaf(w, v.x, a0);
-                a1 = fmaf(w, v.y, a1);
+        // eight routes at a time: all positions and weights first, then all rows, then the sums in route order, so the
+        // loads of a batch are in flight together instead of one dependent pair after the other
+        constexpr int kBatch = 8;
+        for (int j0 = 0; j0 < k; j0 += kBatch) {
+            int pos[kBatch];
+            float w[kBatch], v0[kBatch], v1[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const bool in = j0 + u < k;
+                pos[u] = in ? inv_perm[static_cast<int64_t>(t) * k + j0 + u] : -1;
+                w[u] = in ? wts[static_cast<int64_t>(t) * k + j0 + u] : 0.0f;
             }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                v0[u] = v1[u] = 0.0f;
+                if (pos[u] < 0) continue;
+                if (sizeof(DnT) == 2) {
+                    const __half2 v = *reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(dn) + static_cast<int64_t>(pos[u]) * h + c);
+                    v0[u] = __low2float(v);
+                    v1[u] = __high2float(v);
+                } else {
+                    const float2 v = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(dn) + static_cast<int64_t>(pos[u]) * h + c);
+                    v0[u] = v.x;
+                    v1[u] = v.y;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u)
+                if (pos[u] >= 0) {
+                    a0 = fmaf(w[u], v0[u], a0);
+                    a1 = fmaf(w[u], v1[u], a1);
+                }
         }
         if (sizeof(OutT) == 2) {
             *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(out) + static_cast<int64_t>(t) * h + c) = __floats2half2_rn(a0, a1);
