@@ -92,16 +92,13 @@ __global__ void __launch_bounds__(128) qwc_moe_route_kernel(const float* __restr
                 bi = id;
             }
         }
-        // warp argmax with ties to the lower id
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
-            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
-            if (oi != 0x7FFFFFFF && (bi == 0x7FFFFFFF || ov > bv || (ov == bv && oi < bi))) {
-                bv = ov;
-                bi = oi;
-            }
-        }
+        // warp argmax with ties to the lower id.  Valid weights are softmax outputs (finite, >= 0), so their bit patterns
+        // order like the values: one integer max over the warp, then the lowest id among the lanes that hold it.
+        const uint32_t key = bi != 0x7FFFFFFF ? __float_as_uint(bv) + 1u : 0u;   // 0: this lane has no candidate
+        const uint32_t kmax = __reduce_max_sync(0xFFFFFFFFu, key);
+        const uint32_t cand = (kmax != 0u && key == kmax) ? static_cast<uint32_t>(bi) : 0x7FFFFFFFu;
+        bi = static_cast<int>(__reduce_min_sync(0xFFFFFFFFu, cand));
+        bv = kmax != 0u ? __uint_as_float(kmax - 1u) : -3.4e38f;
         const bool found = bi != 0x7FFFFFFF;
         if (found && (bi & 31) == lane) {
 #pragma unroll
