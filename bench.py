@@ -619,6 +619,56 @@ def cpu_baseline(q, hal, n, k, m):
             "device_vs_cpu_max_rel_err": err}
 
 
+def run_case(args):
+    """A small named case of one kernel for profiler captures (few launches, a few hundred MB on the device at most):
+         gemv:<container>:<n>:<k>:<m>     the matmul door over four banks in rotation (static-weights mode)
+         moe:<experts>:<tokens>            the sparse-MoE chain, hidden 2048, intermediate 512, top-8, HQ4_G32
+    Prints one JSON line with the mean time per call (CUDA events; not a bench value)."""
+    import torch
+    import qwegn_b200 as q
+    torch.cuda.set_device(0)
+    hal = q.QWHal(0)
+    parts = args.case.split(":")
+    iters = max(1, min(args.steps, 20))
+    stream = torch.cuda.current_stream()
+    if parts[0] == "gemv":
+        cname, n, k, m = parts[1], int(parts[2]), int(parts[3]), int(parts[4])
+        cont = q.CONTAINERS[cname]
+        banks = make_banks(q, hal, n, k, cont, 4, seed=3)
+        x = torch.randn((m, k), device="cuda").to(torch.float16)
+        y = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        nws = q.QWGemm.workspaceBytes(hal, banks[0], m)
+        ws = torch.empty(nws, dtype=torch.uint8, device="cuda") if nws else None
+        torch.cuda.synchronize()
+        hal.set_static_weights(True)
+        fn = lambda i: q.QWGemm.encode(hal, banks[i % 4], x, y, workspace=ws)
+    elif parts[0] == "moe":
+        e, t = int(parts[1]), int(parts[2])
+        k, h, inter = 8, 2048, 512
+        cont = q.CONTAINERS["HQ4_G32"]
+        gu = q.QWGemm.quantize(hal, torch.randn((e * 2 * inter, h), device="cuda") * 0.02, cont)
+        dn = q.QWGemm.quantize(hal, torch.randn((e * h, inter), device="cuda") * 0.02, cont)
+        op = q.QWMoEOperator(hal, q.QWWeightView(gu, e * 2 * inter, h, cont), q.QWWeightView(dn, e * h, inter, cont), e, inter, k)
+        x = torch.randn((t, h), device="cuda").to(torch.float16)
+        lg = torch.randn((t, e), device="cuda")
+        outp = torch.empty((t, h), device="cuda")
+        sc = torch.empty(op.scratchBytes(t), dtype=torch.uint8, device="cuda")
+        fn = lambda i: op.encodeResident(x, lg, outp, sc)
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(iters):
+        fn(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "calls": iters, "us_per_call": e0.elapsed_time(e1) / iters * 1e3,
+                      "device_status": hal.device_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -626,7 +676,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sections", default="", help="comma list of extra sections at N=1: sweep,c1,cpu")
+    ap.add_argument("--case", default="", help="run one small named case instead of the bench (profiler captures): see run_case")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

@@ -12,7 +12,8 @@
  *   - the caller owns every buffer, scratch included;
  *   - no encode-class call allocates, synchronises or copies host<->device;
  *   - every refusal happens before the first launch and leaves the stream
- *     untouched; the status code mirrors QWGemmError
+ *     untouched (the orchestrating doors check, up front, everything the
+ *     doors they call would check); the status code mirrors QWGemmError
  *     (Sources/Operators/QWGEMM/QWGemm.swift:66-80) and qwc_last_error()
  *     returns the message (thread-local).
  *
@@ -193,7 +194,7 @@ size_t qwc_static_scratch_capacity(void);
 typedef struct {
     int32_t rank, world;      /* 2 <= world <= 8 */
     uint32_t epoch;
-    int32_t reserved;
+    int32_t reserved;         /* > 0: limit of the wait for the peers' flags in microseconds (0: the library's default, 1 s) */
     void* inbox[8];
     void* flags[8];
     int64_t inbox_floats;     /* capacity of one inbox buffer in floats (>= world * m * n) */
@@ -250,7 +251,8 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
                         int64_t gu_rows, int64_t dn_rows, int32_t gu_epilogue, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
                         int32_t* tile_counts);
 int64_t qwc_moe_max_tiles(int64_t pairs, int64_t e, int64_t rows_per_expert);
-/* Activation rows per tile the plan uses for this problem size (192 today; the kernel also takes 64 and 256). */
+/* Activation rows per tile the plan uses for this problem size (128 while an expert holds up to ~85 rows on average, else
+ * 192; the kernel also takes 64). */
 int32_t qwc_moe_tile_rows(int64_t pairs, int64_t e);
 
 /* Gather + rotate: xs[p, :] = f16(fwht32(x[sorted_tok[p], :])) for the sorted pairs (x_is_rotated != 0: plain copy).
@@ -278,6 +280,11 @@ int qwc_moe_silu_mul(qwc_hal* hal, qwc_stream stream, const void* gu_f16, int64_
  * out[t, :] = sum_k wts[t, k] * dn[inv_perm[t * k_top + k], :] (dropped pairs skipped), f32 accumulate. */
 int qwc_moe_combine(qwc_hal* hal, qwc_stream stream, const void* dn, int32_t dn_dtype, const int32_t* inv_perm,
                     const float* wts, int64_t t, int64_t k, int64_t h, void* out, int32_t out_dtype);
+/* The same with the reference kernel's shared-expert term (Sources/QWMetal/gemm/qwgemm_moe_nax_f16.metal:7-126):
+ * out[t, :] += gate[t] * shared[t, :], shared f32 [t, h] (the shared expert's output), gate f32 [t].  Both NULL: as above. */
+int qwc_moe_combine_shared(qwc_hal* hal, qwc_stream stream, const void* dn, int32_t dn_dtype, const int32_t* inv_perm,
+                           const float* wts, const float* shared_f32, const float* gate_f32, int64_t t, int64_t k, int64_t h,
+                           void* out, int32_t out_dtype);
 
 /* QWMoEOperator.encodeResident (QWMoEOperator.swift:206-442), grouped path with no shared expert: the whole chain
  * above on one stream.  x f16 [t, h] (standard basis unless x_is_rotated); logits f32 [t, e]; bank_gu = stacked

@@ -53,7 +53,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     for src in sources():
         obj = os.path.join(obj_dir, os.path.basename(src).replace(".cu", ".o"))
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]
+        # QWC_NVCC_EXTRA (build time only): extra compiler flags, e.g. -DQWC_TUNING for a build whose launch code reads
+        # its tuning knobs from the environment
+        cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("QWC_NVCC_EXTRA", "").split(), "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -16,11 +16,13 @@ int qwc_launch_gemv(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const 
                     int64_t, int, int, void*, size_t);
 size_t qwc_gemv_workspace_bytes(const qwc_weight_view*, int64_t);
 int qwc_launch_gemv_ar(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int,
-                       int64_t, int, int, void*, size_t, const qwc_allreduce_ctx*);
+                       int64_t, int, int, void*, size_t, const qwc_allreduce_ctx*, bool dry = false);
 bool qwc_gemm_tc_supported(const qwc_hal*, const qwc_weight_view*, int64_t, int);
 size_t qwc_gemm_tc_workspace_bytes(const qwc_weight_view*, int64_t, int);
 int qwc_launch_gemm_tc(const qwc_hal*, cudaStream_t, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int, int64_t,
                        int, int, void*, size_t);
+int qwc_gemm_tc_check(const qwc_weight_view*, const void*, int64_t, int64_t, int, const void*, size_t);
+int qwc_gemv_check(const qwc_hal*, const qwc_weight_view*, const void*, int64_t, int64_t, void*, int, int64_t, int, int, void*, size_t);
 
 static thread_local char g_err[512] = "";
 
@@ -163,11 +165,10 @@ int qwc_gemm_plan(int64_t m, int64_t n, int64_t k, int32_t kind, int32_t bits, i
         out->backend = QWC_BACKEND_ROWWISE;
         out->threads_per_cta = 256;
         snprintf(out->kernel, sizeof(out->kernel), "qwc_gemv_rowwise_%s", fname);
-    } else if (m >= 16 && (epilogue == QWC_EPI_NONE || (n % 2 == 0 && (n / 2) % 64 == 0)) &&
-               (fmt == FMT_HQ4_G32_M5 || fmt == FMT_HQ8_G32) && k % 128 == 0) {
+    } else if (m >= 16 && (epilogue == QWC_EPI_NONE || (n % 2 == 0 && (n / 2) % 64 == 0)) && k % (fmt == FMT_HQ4_G64 ? 256 : 128) == 0) {
         out->backend = QWC_BACKEND_TCGEN05;
         out->threads_per_cta = 24 * 32;
-        snprintf(out->kernel, sizeof(out->kernel), "qwc_gemm_ts_%s_128x192x64", fname);
+        snprintf(out->kernel, sizeof(out->kernel), "qwc_gemm_ts_%s_128x%dx64", fname, m <= 64 ? 64 : (m <= 128 ? 128 : 192));
     } else {
         out->backend = QWC_BACKEND_STREAM_MMA;
         out->threads_per_cta = 17 * 32;
@@ -184,7 +185,10 @@ int qwc_fwht32_f16(qwc_hal* hal, qwc_stream stream, void* x_f16, int64_t count) 
     return qwc_launch_fwht32_f16(hal, static_cast<cudaStream_t>(stream), x_f16, count);
 }
 
-static int check_view(const qwc_weight_view* w) {
+}  // extern "C"
+
+// Library-internal (C++ linkage, declared in qwc_common.cuh).
+int qwc_check_view(const qwc_weight_view* w) {
     if (!w || !w->blocks) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "weight view is null");
     if (w->n <= 0 || w->k <= 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "empty weight view");
     if (qwc_fmt_of(*w) == FMT_UNSUPPORTED)
@@ -196,11 +200,13 @@ static int check_view(const qwc_weight_view* w) {
     return QWC_OK;
 }
 
+extern "C" {
+
 int qwc_dequant(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, void* out, int32_t out_dtype,
                 int32_t standard_domain) {
     qwc_clear_error();
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
-    if (int rc = check_view(w)) return rc;
+    if (int rc = qwc_check_view(w)) return rc;
     if (!out) return qwc_fail(QWC_ERR_BAD_SHAPE, "out is null");
     if (out_dtype != QWC_F16 && out_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "out dtype must be f16 or f32");
     return qwc_launch_dequant(hal, static_cast<cudaStream_t>(stream), w, out, out_dtype, standard_domain);
@@ -212,7 +218,7 @@ int qwc_quantize(qwc_hal* hal, qwc_stream stream, const float* w_f32, int64_t n,
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
     qwc_weight_view v{blocks_out, n, k, kind, bits, group};
     if (kind == QWC_KIND_HQ4_G32_M5) { v.bits = 4; v.group = 32; }
-    if (int rc = check_view(&v)) return rc;
+    if (int rc = qwc_check_view(&v)) return rc;
     if (!w_f32) return qwc_fail(QWC_ERR_BAD_SHAPE, "w is null");
     return qwc_launch_quantize(hal, static_cast<cudaStream_t>(stream), w_f32, n, k, qwc_fmt_of(v), blocks_out);
 }
@@ -224,12 +230,15 @@ size_t qwc_gemm_workspace_bytes(const qwc_hal* hal, const qwc_weight_view* w, in
     return qwc_gemv_workspace_bytes(w, m);
 }
 
-int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx,
-             void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace,
-             size_t workspace_bytes) {
-    qwc_clear_error();
+}  // extern "C"
+
+// Every argument check of the matmul door in one place, shared by qwc_gemm, qwc_gemm_static_scratch and qwc_gemm_f32 so
+// that none of them can drift: QWC_OK means that a launch with these arguments cannot be refused any more.  The order
+// follows QWGemm.encode (QWGemm.swift:135-283): weights, shape, geometry, then scratch.
+static int gemm_args_common(const qwc_hal* hal, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx, void* y,
+                            int32_t y_dtype, int64_t ldy, int32_t epilogue) {
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
-    if (int rc = check_view(w)) return rc;
+    if (int rc = qwc_check_view(w)) return rc;
     if (m < 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "m=%lld is negative", (long long)m);
     if (m == 0) return QWC_OK;
     if (!x_f16 || !y) return qwc_fail(QWC_ERR_BAD_SHAPE, "x or y is null");
@@ -246,6 +255,35 @@ int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const vo
     if (ldx < w->k) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldx=%lld < k=%lld", (long long)ldx, (long long)w->k);
     if (ldy < n_out) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldy=%lld < output width %lld", (long long)ldy, (long long)n_out);
     if (reinterpret_cast<uintptr_t>(x_f16) % 2 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "x must be 2-byte aligned");
+    if (reinterpret_cast<uintptr_t>(y) % (y_dtype == QWC_F16 ? 2 : 4) != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "y is not aligned to its element size");
+    return QWC_OK;
+}
+
+int qwc_gemm_check(const qwc_hal* hal, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx, void* y,
+                   int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace, size_t workspace_bytes) {
+    if (int rc = gemm_args_common(hal, w, x_f16, m, ldx, y, y_dtype, ldy, epilogue)) return rc;
+    if (m == 0) return QWC_OK;
+    if (qwc_gemm_tc_supported(hal, w, m, epilogue)) return qwc_gemm_tc_check(w, x_f16, ldx, m, x_is_rotated, workspace, workspace_bytes);
+    return qwc_gemv_check(hal, w, x_f16, m, ldx, y, y_dtype, ldy, epilogue, x_is_rotated, workspace, workspace_bytes);
+}
+
+// The same for a caller that always takes the streaming kernel (the scratch-free door).
+int qwc_gemm_args_check_stream(const qwc_hal* hal, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx, void* y,
+                               int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace,
+                               size_t workspace_bytes) {
+    if (int rc = gemm_args_common(hal, w, x_f16, m, ldx, y, y_dtype, ldy, epilogue)) return rc;
+    if (m == 0) return QWC_OK;
+    return qwc_gemv_check(hal, w, x_f16, m, ldx, y, y_dtype, ldy, epilogue, x_is_rotated, workspace, workspace_bytes);
+}
+
+extern "C" {
+
+int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx,
+             void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace,
+             size_t workspace_bytes) {
+    qwc_clear_error();
+    if (int rc = qwc_gemm_check(hal, w, x_f16, m, ldx, y, y_dtype, ldy, epilogue, x_is_rotated, workspace, workspace_bytes)) return rc;
+    if (m == 0) return QWC_OK;
     if (qwc_gemm_tc_supported(hal, w, m, epilogue))
         return qwc_launch_gemm_tc(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, epilogue,
                                   x_is_rotated, workspace, workspace_bytes);
@@ -257,7 +295,7 @@ int qwc_gemm_allreduce(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w
                        void* y, int32_t y_dtype, int64_t ldy, int32_t x_is_rotated, const qwc_allreduce_ctx* ctx) {
     qwc_clear_error();
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
-    if (int rc = check_view(w)) return rc;
+    if (int rc = qwc_check_view(w)) return rc;
     if (!ctx) return qwc_fail(QWC_ERR_BAD_SHAPE, "all-reduce context is null");
     if (ctx->world < 2 || ctx->world > 8 || ctx->rank < 0 || ctx->rank >= ctx->world)
         return qwc_fail(QWC_ERR_BAD_SHAPE, "rank %d / world %d: the fused form takes 2..8 ranks", ctx->rank, ctx->world);

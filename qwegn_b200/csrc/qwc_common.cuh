@@ -25,6 +25,45 @@ void qwc_clear_error();
         if (e__ != cudaSuccess) return qwc_fail(QWC_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
     } while (0)
 
+// Tuning knobs read from the environment exist only in builds made with -DQWC_TUNING (parameter sweeps); the shipped
+// library takes every choice from the shape of the call.
+#ifdef QWC_TUNING
+#include <cstdlib>
+inline int tune_env(const char* name, int fallback) {
+    const char* v = getenv(name);
+    return v ? atoi(v) : fallback;
+}
+#else
+inline int tune_env(const char*, int fallback) { return fallback; }
+#endif
+
+#ifdef __CUDACC__
+// Launch with programmatic stream serialization (see pdl_enter): the kernel must call pdl_enter() (or the two
+// griddepcontrol instructions) before it touches global memory.
+template <typename... KArgs, typename... Args>
+inline cudaError_t qwc_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
+// Argument checks shared by the doors (qwc_api.cu): every refusal a later launch could make, without launching.
+int qwc_check_view(const qwc_weight_view* w);
+int qwc_gemm_check(const qwc_hal* hal, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx, void* y, int32_t y_dtype,
+                   int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace, size_t workspace_bytes);
+int qwc_gemm_args_check_stream(const qwc_hal* hal, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx, void* y,
+                               int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace,
+                               size_t workspace_bytes);
+
 // The three containers this library decodes.
 enum QwcFmt : int { FMT_HQ4_G32_M5 = 0, FMT_HQ8_G32 = 1, FMT_HQ4_G64 = 2, FMT_UNSUPPORTED = -1 };
 
@@ -61,6 +100,15 @@ __device__ __forceinline__ float fwht_xor_stage(float v, int lane_mask, bool upp
     return upper ? __fsub_rn(o, v) : __fadd_rn(v, o);
 }
 
+// Programmatic dependent launch, used between the kernels of one operator chain: a kernel lets its successor be
+// scheduled at once (the successor's launch latency and set-up then overlap this kernel) and waits for its predecessor
+// -- the whole grid, memory flushed -- before its first global access.  Both are no-ops in an ordinary launch.  The wait
+// comes before any early return, so that "this grid completed" always implies "the grid before it completed".
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---- mbarrier / bulk-copy helpers (all waits bounded) ----------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -79,6 +127,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 // spinning through the issue slots; measured to matter (spinning waiters slowed the tensor-core kernel by 15 %).
 #ifndef QWC_TRY_WAIT_HINT_NS
 #define QWC_TRY_WAIT_HINT_NS 20000
+#endif
+#ifndef QWC_RELAXED_SLEEP_NS
+#define QWC_RELAXED_SLEEP_NS 512
 #endif
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -113,24 +164,70 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2^22 polls (several seconds at worst) and reports false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Device wall clock in nanoseconds (the bounded waits measure elapsed time, not poll counts).
+__device__ __forceinline__ uint64_t qwc_globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// How long a wait may last before the kernel gives up, sets its status word and winds down.  A healthy pipeline
+// never waits longer than a few microseconds; the limit only has to be far above that and short enough that a stuck
+// kernel frees the GPU quickly.
+#ifndef QWC_WAIT_LIMIT_NS
+#define QWC_WAIT_LIMIT_NS 1000000000ull
+#endif
+// Bounded wait: true when the phase completed; false when QWC_WAIT_LIMIT_NS passed or another role of the CTA raised
+// `abort_flag` (so that after one role fails the others leave at once instead of running out their own limits).  The
+// clock is first read after 32 failed polls and then every 32nd poll (a poll may itself sleep up to the suspend hint):
+// reading it on every miss put a timer read on the pipeline's critical path.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag = nullptr) {
     if (mbar_test(bar, parity)) return true;   // the phase is often complete already: skip the suspending form
-    for (uint32_t i = 0; i < (1u << 22); ++i) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 31u) == 31u) {
+            if (abort_flag != nullptr && *abort_flag) return false;
+            const uint64_t now = qwc_globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > QWC_WAIT_LIMIT_NS) return false;
+        }
         if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
     }
-    return false;
 }
 // Bounded wait for the roles whose waits are long (an epilogue waiting for a whole main loop, a producer waiting for
 // a free stage): sleeps between polls from the first miss on, so that the waiting warps leave the issue slots to the
-// warps that do the decoding.  Gives up after ~1 s.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 21); ++i) {
+// warps that do the decoding.  Same limit and abort rule as mbar_wait.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, const volatile int* abort_flag = nullptr) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(i < 16 ? 128 : 512);
+        if ((i & 31u) == 31u) {
+            if (abort_flag != nullptr && *abort_flag) return false;
+            const uint64_t now = qwc_globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > QWC_WAIT_LIMIT_NS) return false;
+        }
+        __nanosleep(i < 16 ? QWC_RELAXED_SLEEP_NS / 4 : QWC_RELAXED_SLEEP_NS);
     }
-    return false;
+}
+// Bounded wait until a CTA-scope counter in shared memory (published with a release store) exceeds `q`.
+__device__ __forceinline__ uint32_t ld_acquire_cta_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool wait_counter_above(const uint32_t* ctr, uint32_t q, const volatile int* abort_flag) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (ld_acquire_cta_u32(ctr) > q) return true;
+        if ((i & 63u) == 63u) {
+            if (abort_flag != nullptr && *abort_flag) return false;
+            const uint64_t now = qwc_globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > QWC_WAIT_LIMIT_NS) return false;
+        }
+        __nanosleep(i < 64 ? 20 : 200);
+    }
 }
 // 1-D bulk async copy global -> this CTA's shared memory, completion counted on an mbarrier.
 // dst, src 16-byte aligned; bytes a multiple of 16.

@@ -104,6 +104,7 @@ extern "C" int qwc_gemm_f32(qwc_hal* hal, qwc_stream stream, const qwc_weight_vi
                             int32_t x_is_rotated, void* workspace, size_t workspace_bytes) {
     qwc_clear_error();
     if (!hal || !w) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal or weight view is null");
+    if (int rc0 = qwc_check_view(w)) return rc0;
     if (m <= 0 || !x_f32 || !y) return qwc_fail(QWC_ERR_BAD_SHAPE, "f32 matmul: m=%lld and the buffers must be non-null", (long long)m);
     if (epilogue < 0 || epilogue > 3) return qwc_fail(QWC_ERR_BAD_SHAPE, "f32 matmul: epilogue %d (0 none, 1 silu, 2 sigmoid, 3 silu+fwht)", epilogue);
     if (y_dtype != QWC_F16 && y_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "y must be f16 or f32");
@@ -121,6 +122,10 @@ extern "C" int qwc_gemm_f32(qwc_hal* hal, qwc_stream stream, const qwc_weight_vi
     size_t off = f32_align(static_cast<size_t>(m) * w->k * 2);
     float* tmp = nullptr;
     if (epilogue != 0) { tmp = reinterpret_cast<float*>(ws + off); off += f32_align(static_cast<size_t>(m) * w->n * 4); }
+    // every refusal of the f16 door (weight view, geometry, its share of the workspace) before the stage kernel runs
+    if (int rc0 = qwc_gemm_check(hal, w, x16, m, w->k, epilogue == 0 ? y : static_cast<void*>(tmp), epilogue == 0 ? y_dtype : QWC_F32,
+                                 epilogue == 0 ? ldy : w->n, QWC_EPI_NONE, 1, ws + off, workspace_bytes - off))
+        return rc0;
     const int64_t cap = static_cast<int64_t>(hal->sm_count) * 8;
     {
         const int k8 = static_cast<int>(w->k / 8);

@@ -1,26 +1,37 @@
-// Prefill GEMM over packed HQ blocks on the 5th-generation tensor cores: the CUDA twin of the reference's
-// qwg_gemm_q4g_h16 / qwg_gemm_q4g_nax_f32 / qwg_gemm_aq*_h16 kernels (Sources/QWMetal/gemm/qwgemm_batched.metal:24-36,
-// 266-277; tile loop Sources/QWMetal/include/qw_gemm_nax.metalh:153-423).
+// Prefill GEMM and grouped expert GEMM over packed HQ blocks on the 5th-generation tensor cores: the CUDA twin of the
+// reference's qwg_gemm_q4g_h16 / qwg_gemm_q4g_nax_f32 / qwg_gemm_aq*_h16 kernels
+// (Sources/QWMetal/gemm/qwgemm_batched.metal:24-36, 266-277; qwgemm_aq_batched.metal:8-60; tile loop
+// Sources/QWMetal/include/qw_gemm_nax.metalh:153-423).
 //
 //   Y[m, n] = sum_k Xrot[m, k] * Wrot[n, k],   f16 operands, f32 accumulate in tensor memory.
 //
-// One persistent CTA per SM walks (weight tile, token tile) pairs.  Two variants share the roles and the pipeline:
-//   * qwc_gemm_ts_kernel (the default): converter threads own one weight row each, decode it in registers (magic-bias
-//     form, one f16 FMA with scale and bias: the reference's in-register decode, qw_gemm_nax.metalh:114-127) and write
-//     the f16 pairs into TENSOR memory with tcgen05.st; the MMAs take A from tensor memory and B (the activations) from
-//     shared memory; tiles of up to 192 tokens;
-//   * qwc_gemm_tc_kernel (QWC_TC_SS=1): the converters store a K-major, 128-byte-swizzled operand tile in shared memory
-//     (proxy fence before the hand-off); tiles of up to 256 tokens.
-// In both, per 64-wide K tile: two TMA warps bring the packed weight rows, unchanged, into shared memory (2-D tensor
-// copy, 128 rows x one raw step of 128 k) and the rotated activations (128-byte swizzle); one warp issues tcgen05.mma
-// (M = 128 weight rows, N = tokens, K = 16) into a TMEM accumulator; tcgen05.commit releases the stage and, after the
-// last K tile, hands the accumulator to four epilogue warps (tcgen05.ld, lane = weight row; plain store or the fused
-// SwiGLU (+ FWHT) epilogue); two accumulators alternate so the epilogue of one tile overlaps the main loop of the next.
+// One persistent CTA per SM walks (weight tile, token tile) pairs.  Roles: warp 0 activation TMA, warp 1 MMA issue
+// (+ TMEM allocation), warp 2 packed-weight TMA, 16 converter warps, 4 epilogue warps.
+//   * Per raw step a TMA copy brings 128 packed weight rows, unchanged, into a shared-memory ring (2-D tensor copy;
+//     one raw step = 128 k for the 20- and 36-byte blocks of 32, 256 k for the 36-byte blocks of 64, so that a row of a
+//     step is a multiple of 16 bytes); per 64-wide K tile another TMA copy brings the rotated activations (128-byte
+//     swizzle).
+//   * A converter thread owns one weight row = one TMEM lane: it reads its row's 64 k of the raw step, decodes them in
+//     registers (magic-bias form and one f16 FMA with scale and bias: the reference's in-register decode,
+//     qw_gemm_nax.metalh:114-127) and only then waits for the operand stage to be free and writes 32 TMEM columns
+//     with tcgen05.st, so the decode of K tile j + S overlaps the MMAs of K tile j.  Converter warp c serves lane
+//     quarter c % 4 and the K tiles j with j % 4 == c / 4.
+//   * The MMAs take A from tensor memory and B (the activations) from shared memory: tcgen05.mma, M = 128 weight rows,
+//     N = tokens, K = 16, into a TMEM accumulator; tcgen05.commit releases the stage and, after the last K tile, hands
+//     the accumulator to the epilogue warps (tcgen05.ld, lane = weight row; plain store or the fused SwiGLU (+ FWHT)
+//     epilogue); two accumulators alternate so the epilogue of one tile overlaps the main loop of the next.
+//   * TMEM budget (512 columns): tiles of up to 192 tokens use two 192-column accumulators and 4 operand stages of 32
+//     columns; tiles of up to 128 tokens (expert tiles, verify-sized calls) use two 128-column accumulators and 8
+//     operand stages, because with few tokens an MMA is short and the hand-off latencies, not the tensor pipe, set the
+//     pace: more stages in flight hide them.
 // Weights are the M operand so that all tokens of a tile share every decoded weight.  The grouped (mixture-of-experts)
-// door runs the same kernels over a device-side tile list.
-// Every mbarrier wait is bounded; a wait that gives up sets the device status word and the CTA winds down.
+// door runs the same kernel over a device-side tile list.  The kernel is launched with programmatic stream
+// serialization and waits for the grid before it (griddepcontrol.wait) after its own set-up, before any global access.
+// Every wait is bounded in time; a wait that gives up sets the device status word, raises the CTA's abort flag (which
+// the other roles poll) and the CTA winds down and frees its tensor memory.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -29,22 +40,21 @@
 namespace {
 
 constexpr int kBM = 128;        // weight rows per tile (UMMA M)
-constexpr int kBN = 256;        // tokens per tile (UMMA N)
-constexpr int kBK = 64;         // k per operand tile (one 128-byte swizzle atom of f16)
-constexpr int kRawK = 128;      // k per raw weight step (two operand tiles)
-#ifndef QWC_TC_CONV_WARPS
-#define QWC_TC_CONV_WARPS 16
-#endif
-constexpr int kConvWarps = QWC_TC_CONV_WARPS;   // 8 rows x 4 units per warp step: 16 warps decode a raw step in one step
+constexpr int kBK = 64;         // k per operand stage (one 128-byte swizzle atom of f16)
+constexpr int kConvWarps = 16;
 constexpr int kEpiWarps = 4;
-constexpr int kConvGroups = 2;                         // groups of converter warps that alternate raw steps
-constexpr int kGroupWarps = kConvWarps / kConvGroups;
-constexpr int kFirstConvWarp = 3;   // warps 0, 1, 2: activation TMA, MMA issue, weight TMA
-constexpr int kWarps = kFirstConvWarp + kConvWarps + kEpiWarps;
-constexpr int kTcThreads = kWarps * 32;
-constexpr int kWTileBytes = kBM * kBK * 2;   // 16 KB
-constexpr int kStages = 4;    // operand stages (one decoded weight tile + one activation tile each)
-constexpr int kMaxRaw = 4;    // raw (packed weight) stages
+constexpr int kMaxStages = 8;   // operand stages (one decoded weight tile in TMEM + one activation tile in shared memory each)
+constexpr int kTsFirstConvWarp = 4;   // warps 0..2 as above, warp 3 idle so that converter warp c serves quarter c % 4
+constexpr int kTsWarps = kTsFirstConvWarp + kConvWarps + kEpiWarps;
+constexpr int kTsThreads = kTsWarps * 32;
+constexpr int kTsMaxRaw = 8;    // raw (packed weight) stages
+constexpr int kTsBN = 192;      // most tokens per tile (UMMA N)
+
+// Packed geometry of one 64-wide K tile of one row, and K tiles per raw step.
+template <int FMT> struct TcFmt;
+template <> struct TcFmt<FMT_HQ4_G32_M5> { static constexpr int kTileBytes = 40, kTilesPerRaw = 2; };
+template <> struct TcFmt<FMT_HQ8_G32> { static constexpr int kTileBytes = 72, kTilesPerRaw = 2; };
+template <> struct TcFmt<FMT_HQ4_G64> { static constexpr int kTileBytes = 36, kTilesPerRaw = 4; };
 
 struct TcParams {
     void* y;
@@ -53,9 +63,12 @@ struct TcParams {
     int m, n, k;
     int y_f16;
     int raw_stages;
-    int x_tile_rows;     // activation rows per tile: 256 (192 for the 36-byte containers, to fit shared memory), 64 for small expert tiles
-    int x_slot_bytes;    // bytes of one activation stage: 256 rows x 128 B, or 64 x 128 B when every tile has <= 64 rows
-    int raw_row_bytes;   // packed bytes of 128 k of one row: 80 (HQ4_G32_M5) or 144 (HQ8_G32)
+    int stages;          // operand stages: 4 (tiles of up to 192 tokens) or 8 (tiles of up to 128 tokens); a power of two
+    int stage_shift;     // log2(stages): stage of K tile j = j & (stages - 1), its use count = j >> stage_shift
+    int acc_stride;      // TMEM columns per accumulator: 192 or 128; the operand stages start at column 2 * acc_stride
+    int x_tile_rows;     // activation rows per tile: 192, 128 or 64
+    int x_slot_bytes;    // bytes of one activation stage: x_tile_rows x 128 B
+    int raw_row_bytes;   // packed bytes of one raw step of one row: 80 (HQ4_G32_M5) or 144 (HQ8_G32, HQ4_G64)
     int m_tiles, n_tiles;
     int epilogue;        // QWC_EPI_NONE, or a SwiGLU epilogue: a tile is then 64 gate rows + the 64 matching up rows
     int up_delta;        // dense SwiGLU mode: row distance gate -> up (= n / 2)
@@ -65,17 +78,15 @@ struct TcParams {
     const int32_t* tile_count;   // device: number of valid entries of `tiles`
 };
 
-// One unit of work of the kernel: 128 weight rows x up to 256 activation rows.
+// One unit of work of the kernel: 128 weight rows x up to 192 activation rows.
 struct TileInfo {
     int w_row0;     // first weight row (row coordinate of the weight tensor map)
     int w_row1;     // SwiGLU epilogues: first up row (rows 64..127 of the tile); unused otherwise
     int w_rows;     // valid weight rows in the tile (<= 128)
     int x_row0;     // first activation row (row coordinate of the activation tensor map)
-    int x_rows;     // valid activation rows (<= 256)
+    int x_rows;     // valid activation rows
     int y_col0;     // output column of weight row 0 of the tile
 };
-
-__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
@@ -116,13 +127,6 @@ __device__ __forceinline__ uint32_t make_idesc(int n_tokens) {
     return (1u << 4) | (static_cast<uint32_t>(n_tokens >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -165,36 +169,10 @@ __device__ __forceinline__ uint32_t hsub2_1024(uint32_t a) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-// Decode one 32-element unit of one row into four 16-byte chunks (8 consecutive k each, natural order).
-template <int FMT>
-__device__ __forceinline__ void decode_unit_natural(const uint8_t* blk, uint4 out[4]) {
-    const uint32_t hdr = lds32(blk);
-    const __half2 h = *reinterpret_cast<const __half2*>(&hdr);
-    const __half2 s2 = __half2half2(__low2half(h)), b2 = __half2half2(__high2half(h));
-    if (FMT == FMT_HQ4_G32_M5) {
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const uint32_t v = lds32(blk + 4 + 4 * w);
-            out[w].x = hfma2_u32(nib2_f16x2(v), s2, b2);
-            out[w].y = hfma2_u32(nib2_f16x2(v >> 4), s2, b2);
-            out[w].z = hfma2_u32(nib2_f16x2(v >> 8), s2, b2);
-            out[w].w = hfma2_u32(nib2_f16x2(v >> 12), s2, b2);
-        }
-    } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const uint32_t v0 = lds32(blk + 4 + 8 * c), v1 = lds32(blk + 8 + 8 * c);
-            out[c].x = hfma2_u32(hsub2_1024(__byte_perm(v0, 0x64646464u, 0x4140)), s2, b2);
-            out[c].y = hfma2_u32(hsub2_1024(__byte_perm(v0, 0x64646464u, 0x4342)), s2, b2);
-            out[c].z = hfma2_u32(hsub2_1024(__byte_perm(v1, 0x64646464u, 0x4140)), s2, b2);
-            out[c].w = hfma2_u32(hsub2_1024(__byte_perm(v1, 0x64646464u, 0x4342)), s2, b2);
-        }
-    }
-}
-
 // Latency-critical wait of the MMA-issuing thread: a plain spin on try_wait (no suspend hint, no sleep); bounded.
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 26); ++i) {
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -204,8 +182,12 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
             : "r"(smem_u32(bar)), "r"(parity)
             : "memory");
         if (ok) return true;
+        if ((i & 1023u) == 1023u) {   // the clock is read rarely: the loop stays a plain poll
+            const uint64_t now = qwc_globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (*abort_flag || now - t0 > QWC_WAIT_LIMIT_NS) return false;
+        }
     }
-    return false;
 }
 
 // Tile number `tile` of the launch: from the device-side list (grouped mode) or the dense (weight tile, token tile) grid.
@@ -337,263 +319,6 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& p, const TileIn
     }
 }
 
-template <int FMT>
-__global__ void __launch_bounds__(kTcThreads, 1)
-qwc_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                   const __grid_constant__ CUtensorMap xmap128, const __grid_constant__ CUtensorMap xmap64,
-                   const __grid_constant__ CUtensorMap wmap64) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    // layout (1024-byte aligned base): [W tiles][X tiles][raw stages][barriers]
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* wt = smem;
-    uint8_t* xt = wt + kStages * kWTileBytes;
-    uint8_t* raw = xt + kStages * p.x_slot_bytes;
-    const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + p.raw_stages * raw_stage_bytes);
-    uint64_t* full = bars;                       // [kStages]  activations landed (tx) + the group's converters arrived
-    uint64_t* empty = bars + kStages;            // [kStages]  tcgen05.commit: the MMAs have read both operand tiles
-    uint64_t* raw_full = bars + 2 * kStages;     // [kMaxRaw]
-    uint64_t* raw_empty = raw_full + kMaxRaw;    // [kMaxRaw]
-    uint64_t* acc_full = raw_empty + kMaxRaw;    // [2]
-    uint64_t* acc_empty = acc_full + 2;          // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint32_t* raw_issued = tmem_slot + 2;   // raw steps the weight producer has started
-    uint8_t* xch = reinterpret_cast<uint8_t*>(bars) + 512;   // SwiGLU epilogues: up values of 64 rows x 16 tokens (f16)
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full[s], 1 + kGroupWarps);
-            mbar_init(&empty[s], 1);
-        }
-        for (int s = 0; s < p.raw_stages; ++s) {
-            mbar_init(&raw_full[s], 1);
-            mbar_init(&raw_empty[s], kGroupWarps);
-        }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&acc_full[s], 1);
-            mbar_init(&acc_empty[s], kEpiWarps);
-        }
-        *abort_flag = 0;
-        *raw_issued = 0;
-        fence_barrier_init();
-    }
-    if (warp == 1) {
-        // 512 columns: two 128 x 256 f32 accumulators.  One CTA per SM, so the allocation cannot contend.
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    const int total_tiles = p.tiles != nullptr ? *p.tile_count : p.m_tiles * p.n_tiles;
-    auto get_tile = [&](int tile) { return tc_get_tile(p, tile); };
-    const int ktiles = p.k / kBK;
-    const int raw_steps = p.k / kRawK;
-
-    auto fail = [&](int code) {
-        if (!*abort_flag) atomicCAS(p.status, 0, code);
-        *abort_flag = 1;
-    };
-
-    // K tile number j of the kernel (all tiles) uses stage j % kStages in phase (j / kStages) & 1; raw step r covers
-    // K tiles 2r and 2r + 1 and belongs to converter group r % kConvGroups, which therefore always owns the same two
-    // stages (kStages == 2 * kConvGroups).
-    if (warp == 0) {
-        // ---------------- TMA producer: rotated activations (one tile per K tile) ----------------
-        if (lane == 0) {
-            uint32_t j = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileInfo ti = get_tile(tile);
-                // the narrowest activation box that covers the tile's tokens
-                const CUtensorMap* xm = ti.x_rows <= 64 ? &xmap64 : (ti.x_rows <= 128 ? &xmap128 : &xmap);
-                const uint32_t xbytes = (ti.x_rows <= 64 ? 64u : (ti.x_rows <= 128 ? 128u : static_cast<uint32_t>(p.x_tile_rows))) * kBK * 2u;
-                for (int kt = 0; kt < ktiles; ++kt, ++j) {
-                    const uint32_t s = j % kStages;
-                    if (j >= kStages && !mbar_wait_relaxed(&empty[s], ((j / kStages) - 1) & 1u)) {
-                        fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_expect_tx(&full[s], xbytes);
-                    tma_load_2d(xt + s * p.x_slot_bytes, xm, kt * kBK, ti.x_row0, &full[s]);
-                }
-            }
-        }
-        __syncwarp();
-    } else if (warp == 2) {
-        // ---------------- TMA producer: packed weight rows (one raw step = two K tiles) ----------------
-        // A warp of its own so the weight stream runs ahead by the whole raw ring: the packed rows come from HBM / L2
-        // with the longest latency of the pipeline.
-        if (lane == 0) {
-            uint32_t r = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileInfo ti = get_tile(tile);
-                for (int rs = 0; rs < raw_steps; ++rs, ++r) {
-                    const uint32_t s = r % p.raw_stages;
-                    if (r >= static_cast<uint32_t>(p.raw_stages) && !mbar_wait_relaxed(&raw_empty[s], ((r / p.raw_stages) - 1) & 1u)) {
-                        fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_expect_tx(&raw_full[s], static_cast<uint32_t>(kBM * p.raw_row_bytes));
-                    if (p.epilogue == QWC_EPI_NONE) {
-                        tma_load_2d(raw + s * raw_stage_bytes, &wmap, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[s]);
-                    } else {   // 64 gate rows, then the 64 up rows that pair with them
-                        tma_load_2d(raw + s * raw_stage_bytes, &wmap64, rs * (p.raw_row_bytes / 8), ti.w_row0, &raw_full[s]);
-                        tma_load_2d(raw + s * raw_stage_bytes + (kBM / 2) * p.raw_row_bytes, &wmap64, rs * (p.raw_row_bytes / 8),
-                                    ti.w_row1, &raw_full[s]);
-                    }
-                    asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(raw_issued)), "r"(r + 1) : "memory");
-                }
-            }
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------- MMA issuer -------------------------------
-        // The whole warp runs the loop in lockstep and one elected lane issues: control flow and the descriptor
-        // arithmetic stay warp-uniform (uniform registers feed tcgen05.mma directly), and the issuing warp, which shares
-        // its scheduler with converter warps that are always ready, executes as few instructions per K tile as possible.
-        {
-            uint32_t j = 0, tiles_done = 0;
-            bool ok = true;
-            const uint64_t a_d0 = umma_desc_sw128(smem_u32(wt)), b_d0 = umma_desc_sw128(smem_u32(xt));
-            const uint32_t a_lo0 = static_cast<uint32_t>(a_d0), a_hi = static_cast<uint32_t>(a_d0 >> 32);
-            const uint32_t b_lo0 = static_cast<uint32_t>(b_d0), b_hi = static_cast<uint32_t>(b_d0 >> 32);
-            const uint32_t a_step = kWTileBytes >> 4, b_step = static_cast<uint32_t>(p.x_slot_bytes) >> 4;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tiles_done) {
-                const int as = tiles_done & 1;
-                if (tiles_done >= 2 && !mbar_wait_spin(&acc_empty[as], ((tiles_done >> 1) - 1) & 1)) {
-                    if (lane == 0) fail(QWC_DEV_WAIT_TMEM_TIMEOUT);
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * kBN);
-                const uint32_t idesc = make_idesc(min(kBN, (get_tile(tile).x_rows + 15) & ~15));
-                for (int kt = 0; kt < ktiles; ++kt, ++j) {
-                    const uint32_t s = j % kStages;
-                    if (!mbar_wait_spin(&full[s], (j / kStages) & 1u)) {   // all lanes poll: measured faster than one polling lane
-                        if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
-                        ok = false;
-                        break;
-                    }
-                    // descriptors differ from the stage-0 ones only in the 14-bit start-address field (16-byte units)
-                    const uint32_t a_lo = a_lo0 + s * a_step, b_lo = b_lo0 + s * b_step;
-                    if (elect_one()) {
-#pragma unroll
-                        for (int q = 0; q < kBK / 16; ++q)
-                            umma_f16(d_tmem, pack_desc(a_lo + 2 * q, a_hi), pack_desc(b_lo + 2 * q, b_hi), idesc, (kt > 0 || q > 0) ? 1u : 0u);
-                        umma_commit(&empty[s]);   // the stage is free once these MMAs have read it
-                    }
-                    __syncwarp();
-                }
-                if (ok && elect_one()) umma_commit(&acc_full[as]);
-                __syncwarp();
-            }
-        }
-        __syncwarp();
-    } else if (warp < kFirstConvWarp + kConvWarps) {
-        // ------------------------------- converters -------------------------------
-        // The converter warps form kConvGroups groups that take the raw steps in turn.  A step costs a warp its decode
-        // plus a proxy fence of several hundred cycles; with every warp on the same step those latencies lie on the
-        // tensor core's critical path, with alternating groups they overlap with the other group's MMAs.
-        const int cw = warp - kFirstConvWarp;
-        const int grp = cw / kGroupWarps, cwl = cw % kGroupWarps;
-        const int r8 = lane & 7, u = lane >> 3;   // 8 rows x 4 units per warp step; a quarter warp = 8 rows of one unit, so its 16-byte stores fall in 8 distinct bank groups of the swizzled tile
-        const int unit_bytes = p.raw_row_bytes / 4;
-        const uint32_t s0 = 2 * grp, s1 = 2 * grp + 1;   // this group's operand stages
-        uint8_t* wdst = wt + ((u >> 1) ? s1 : s0) * kWTileBytes;
-        bool ok = true;
-        uint32_t r = 0;   // raw steps since the kernel started (all tiles)
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            for (int rs = 0; rs < raw_steps; ++rs, ++r) {
-                if (static_cast<int>(r % kConvGroups) != grp) continue;
-                const uint32_t rslot = r % p.raw_stages, rpar = (r / p.raw_stages) & 1u;
-                const uint32_t use = r / kConvGroups;   // how often this group has filled its stages before
-                // With an odd ring depth successive phases of a raw slot go to different groups, and a parity wait
-                // cannot tell phase k from phase k - 2: wait first until the producer has started step r (which it
-                // does only after phase k - 1 was consumed); from then on the parity wait is exact.
-                bool started = false;
-                for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
-                    uint32_t v;
-                    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(raw_issued)) : "memory");
-                    if (v > r) {
-                        started = true;
-                        break;
-                    }
-                    __nanosleep(spin < 64 ? 20 : 200);
-                }
-                if (!started || !mbar_wait(&raw_full[rslot], rpar) ||
-                    (use > 0 && (!mbar_wait(&empty[s0], (use - 1) & 1u) || !mbar_wait(&empty[s1], (use - 1) & 1u)))) {
-                    if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
-                    ok = false;
-                    break;
-                }
-                const uint8_t* rbase = raw + rslot * raw_stage_bytes;
-#pragma unroll
-                for (int it = 0; it < kBM / (kGroupWarps * 8); ++it) {
-                    const int row = cwl * (kBM / kGroupWarps) + it * 8 + r8;
-                    uint4 ch[4];
-                    decode_unit_natural<FMT>(rbase + row * p.raw_row_bytes + u * unit_bytes, ch);
-                    uint8_t* rowp = wdst + (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        *reinterpret_cast<uint4*>(rowp + ((((u & 1) * 4 + c) ^ (row & 7)) << 4)) = ch[c];
-                }
-                fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async-proxy reads
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&full[s0]);
-                    mbar_arrive(&full[s1]);
-                    mbar_arrive(&raw_empty[rslot]);
-                }
-            }
-        }
-    } else {
-        // ------------------------------- epilogue -------------------------------
-        const int quarter = warp & 3;   // TMEM lanes [32 * quarter, 32 * quarter + 32)
-        uint32_t tiles_done = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tiles_done) {
-            const TileInfo ti = get_tile(tile);
-            const int as = tiles_done & 1;
-            if (!mbar_wait_relaxed(&acc_full[as], (tiles_done >> 1) & 1)) {
-                if (lane == 0) fail(QWC_DEV_WAIT_MMA_TIMEOUT);
-                break;
-            }
-            tc_fence_after();
-            tc_epilogue_tile(p, ti, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * kBN), xch,
-                             quarter, lane);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[as]);
-        }
-    }
-
-    // teardown: everyone meets, then the allocating warp returns the tensor memory
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-}
-
-// ---------------------------------------------------------------------------------------------------------------
-// Variant with the decoded weights staged in TENSOR memory (tcgen05.mma with the A operand in TMEM) instead of a
-// swizzled shared-memory tile: the converters write their f16 pairs with tcgen05.st, so the decoded tile never crosses
-// shared memory (16 KB written + 16 KB read per K tile less on the unit that bounds the kernel) and no generic-to-async
-// proxy fence (several hundred cycles per converter step) is needed.  TMEM budget: two 128 x 192 f32 accumulators
-// (columns 0..383) + four A stages of 32 columns (128 lanes x 64 k of f16 pairs; columns 384..511), so a tile holds at
-// most 192 tokens.  Converter thread = one weight row (TMEM lane); warp w serves lane quarter w % 4.
-constexpr int kTsBN = 192;                 // tokens per tile (UMMA N) and accumulator stride in TMEM columns
-constexpr int kTsAccCols = 2 * kTsBN;      // A stages start here
-constexpr int kTsFirstConvWarp = 4;        // warps 0..2 as above, warp 3 idle so that converter warp c serves quarter c % 4
-constexpr int kTsWarps = kTsFirstConvWarp + kConvWarps + kEpiWarps;
-constexpr int kTsThreads = kTsWarps * 32;
-constexpr int kTsMaxRaw = 8;
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t r[32]) {
     asm volatile(
@@ -616,13 +341,32 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         : "memory");
 }
 
-// Decode UNITS consecutive 32-element units held in registers (header word + payload words each) into f16 pairs in
-// natural k order: out[16 u + c] = elements (2c, 2c + 1) of unit u.
-template <int FMT, int UNITS>
-__device__ __forceinline__ void decode_regs_natural(const uint32_t* w, uint32_t* out) {
+// Decode the 64 k of one K tile of one row, held in registers as packed words, into 32 f16 pairs in natural k order:
+// out[c] = elements (2c, 2c + 1).
+//   HQ4_G32_M5: two blocks of (header, 4 words of interleaved nibbles); HQ8_G32: two blocks of (header, 8 words of code
+//   bytes); HQ4_G64: one block of (header, 8 words of linear nibbles: byte c holds elements 2c (low nibble), 2c + 1).
+template <int FMT>
+__device__ __forceinline__ void decode_tile_natural(const uint32_t* w, uint32_t* out) {
+    if (FMT == FMT_HQ4_G64) {
+        const uint32_t hdr = w[0];
+        const __half2 h = *reinterpret_cast<const __half2*>(&hdr);
+        const __half2 s2 = __half2half2(__low2half(h)), b2 = __half2half2(__high2half(h));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t v = w[1 + i];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                // byte b -> (low nibble, high nibble) in the two halves: x * 0x1001 = x | x << 12 puts the high nibble
+                // at bits 16..19 (x < 256, so the two copies do not overlap); the multiply runs on the FMA pipe
+                const uint32_t x = __byte_perm(v, 0u, 0x4440u + b);
+                out[4 * i + b] = hfma2_u32(hsub2_1024(nib2_f16x2(x * 0x1001u)), s2, b2);
+            }
+        }
+        return;
+    }
     constexpr int kWordsPerUnit = FMT == FMT_HQ4_G32_M5 ? 5 : 9;
 #pragma unroll
-    for (int u = 0; u < UNITS; ++u) {
+    for (int u = 0; u < 2; ++u) {
         const uint32_t hdr = w[u * kWordsPerUnit];
         const __half2 h = *reinterpret_cast<const __half2*>(&hdr);
         const __half2 s2 = __half2half2(__low2half(h)), b2 = __half2half2(__high2half(h));
@@ -646,38 +390,86 @@ __device__ __forceinline__ void decode_regs_natural(const uint32_t* w, uint32_t*
     }
 }
 
+// The packed words of K tile `sub` of a raw step of one row (src = the row's bytes of the raw step in shared memory).
+// Rows of a raw step are 80 or 144 bytes apart, so a quarter warp's 16-byte loads fall in 8 distinct bank groups.
+template <int FMT>
+__device__ __forceinline__ void load_tile_words(const uint8_t* src, int sub, uint32_t* w) {
+    if (FMT == FMT_HQ4_G32_M5) {
+        // 40 bytes at offset 0 (16-byte aligned) or 40 (8-byte aligned)
+        if (sub == 0) {
+            const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + 16);
+            const uint2 d = *reinterpret_cast<const uint2*>(src + 32);
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w; w[8] = d.x; w[9] = d.y;
+        } else {
+            const uint2 d = *reinterpret_cast<const uint2*>(src + 40);
+            const uint4 a = *reinterpret_cast<const uint4*>(src + 48), b = *reinterpret_cast<const uint4*>(src + 64);
+            w[0] = d.x; w[1] = d.y; w[2] = a.x; w[3] = a.y; w[4] = a.z; w[5] = a.w; w[6] = b.x; w[7] = b.y; w[8] = b.z; w[9] = b.w;
+        }
+    } else if (FMT == FMT_HQ8_G32) {
+        // 72 bytes at offset 0 (16-byte aligned) or 72 (8-byte aligned)
+        if (sub == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 a = *reinterpret_cast<const uint4*>(src + 16 * i);
+                w[4 * i] = a.x; w[4 * i + 1] = a.y; w[4 * i + 2] = a.z; w[4 * i + 3] = a.w;
+            }
+            const uint2 d = *reinterpret_cast<const uint2*>(src + 64);
+            w[16] = d.x; w[17] = d.y;
+        } else {
+            const uint2 d = *reinterpret_cast<const uint2*>(src + 72);
+            w[0] = d.x; w[1] = d.y;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 a = *reinterpret_cast<const uint4*>(src + 80 + 16 * i);
+                w[2 + 4 * i] = a.x; w[3 + 4 * i] = a.y; w[4 + 4 * i] = a.z; w[5 + 4 * i] = a.w;
+            }
+        }
+    } else {
+        // 36 bytes at offset 36 * sub (4-byte aligned)
+        const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src + 36 * sub);
+#pragma unroll
+        for (int i = 0; i < 9; ++i) w[i] = s32[i];
+    }
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(kTsThreads, 1)
 qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    const __grid_constant__ CUtensorMap xmap128, const __grid_constant__ CUtensorMap xmap64,
                    const __grid_constant__ CUtensorMap wmap64) {
+    using F = TcFmt<FMT>;
+    constexpr int KPR = F::kTilesPerRaw;
+    constexpr int kTileWords = F::kTileBytes / 4;
+    // Let the next kernel of the stream be scheduled as early as its resources allow (it waits for this grid itself).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // layout (1024-byte aligned base): [X tiles][raw stages][barriers][SwiGLU exchange]
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* xt = smem;
-    uint8_t* raw = xt + kStages * p.x_slot_bytes;
+    uint8_t* raw = xt + p.stages * p.x_slot_bytes;
     const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
     uint64_t* bars = reinterpret_cast<uint64_t*>(raw + p.raw_stages * raw_stage_bytes);
-    uint64_t* full = bars;                        // [kStages]  activations landed (tx) + the four quarter warps stored A
-    uint64_t* empty = bars + kStages;             // [kStages]  tcgen05.commit: the MMAs have read both operands of the stage
-    uint64_t* raw_full = bars + 2 * kStages;      // [kTsMaxRaw]
-    uint64_t* raw_empty = raw_full + kTsMaxRaw;   // [kTsMaxRaw]
-    uint64_t* acc_full = raw_empty + kTsMaxRaw;   // [2]
-    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint64_t* full = bars;                         // [kMaxStages]  activations landed (tx) + the four quarter warps stored A
+    uint64_t* empty = bars + kMaxStages;           // [kMaxStages]  tcgen05.commit: the MMAs have read both operands of the stage
+    uint64_t* raw_full = bars + 2 * kMaxStages;    // [kTsMaxRaw]
+    uint64_t* raw_empty = raw_full + kTsMaxRaw;    // [kTsMaxRaw]
+    uint64_t* acc_full = raw_empty + kTsMaxRaw;    // [2]
+    uint64_t* acc_empty = acc_full + 2;            // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint32_t* raw_issued = tmem_slot + 2;
+    uint32_t* raw_issued = tmem_slot + 2;          // raw steps the weight producer has started
+    volatile int* epi_ok = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [2][4] the epilogue warps' verdicts on a tile
     uint8_t* xch = reinterpret_cast<uint8_t*>(bars) + 512;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1 + 4);
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < p.raw_stages; ++s) {
             mbar_init(&raw_full[s], 1);
-            mbar_init(&raw_empty[s], kGroupWarps);
+            mbar_init(&raw_empty[s], 4 * KPR);   // every K tile of the step: four quarter warps
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
@@ -688,6 +480,7 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         fence_barrier_init();
     }
     if (warp == 1) {
+        // 512 columns.  One CTA per SM, so the allocation cannot contend.
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -695,15 +488,22 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above needed no global data.  From here on the kernel reads what earlier kernels of the stream wrote
+    // (tile list, activations, possibly the weights) and writes y: wait for the grid before this one.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int total_tiles = p.tiles != nullptr ? *p.tile_count : p.m_tiles * p.n_tiles;
     const int ktiles = p.k / kBK;
-    const int raw_steps = p.k / kRawK;
+    const int raw_steps = ktiles / KPR;
+    const uint32_t a_col0 = static_cast<uint32_t>(2 * p.acc_stride);
+    const uint32_t smask = static_cast<uint32_t>(p.stages - 1);
     auto fail = [&](int code) {
         if (!*abort_flag) atomicCAS(p.status, 0, code);
         *abort_flag = 1;
     };
 
+    // K tile number j of the kernel (all tiles) uses operand stage j % stages in phase (j / stages) & 1 and belongs to
+    // raw step j / KPR, which uses raw slot r % raw_stages in phase (r / raw_stages) & 1.
     if (warp == 0) {
         // ---------------- TMA producer: rotated activations (one tile per K tile) ----------------
         if (lane == 0) {
@@ -714,8 +514,9 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                 const CUtensorMap* xm = ti.x_rows <= 64 ? &xmap64 : (ti.x_rows <= 128 ? &xmap128 : &xmap);
                 const uint32_t xbytes = (ti.x_rows <= 64 ? 64u : (ti.x_rows <= 128 ? 128u : static_cast<uint32_t>(p.x_tile_rows))) * kBK * 2u;
                 for (int kt = 0; kt < ktiles; ++kt, ++j) {
-                    const uint32_t s = j % kStages;
-                    if (j >= kStages && !mbar_wait_relaxed(&empty[s], ((j / kStages) - 1) & 1u)) {
+                    const uint32_t s = j & smask;
+                    const bool got_x = j < static_cast<uint32_t>(p.stages) || mbar_wait_relaxed(&empty[s], ((j >> p.stage_shift) - 1) & 1u, abort_flag);
+                    if (!got_x) {
                         fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
                         ok = false;
                         break;
@@ -727,17 +528,18 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         }
         __syncwarp();
     } else if (warp == 2) {
-        // ---------------- TMA producer: packed weight rows (one raw step = two K tiles) ----------------
-        if (lane == 0) {
-            uint32_t r = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        // ---------------- TMA producer: packed weight rows (one raw step = KPR K tiles) ----------------
+        uint32_t r = 0;
+        int ok = 1;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            if (lane == 0) {
                 const TileInfo ti = tc_get_tile(p, tile);
                 for (int rs = 0; rs < raw_steps; ++rs, ++r) {
                     const uint32_t s = r % p.raw_stages;
-                    if (r >= static_cast<uint32_t>(p.raw_stages) && !mbar_wait_relaxed(&raw_empty[s], ((r / p.raw_stages) - 1) & 1u)) {
+                    const bool got_w = r < static_cast<uint32_t>(p.raw_stages) || mbar_wait_relaxed(&raw_empty[s], ((r / p.raw_stages) - 1) & 1u, abort_flag);
+                    if (!got_w) {
                         fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
-                        ok = false;
+                        ok = 0;
                         break;
                     }
                     mbar_arrive_expect_tx(&raw_full[s], static_cast<uint32_t>(kBM * p.raw_row_bytes));
@@ -751,8 +553,8 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                     asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(raw_issued)), "r"(r + 1) : "memory");
                 }
             }
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
         }
-        __syncwarp();
     } else if (warp == 1) {
         // ------------------------------- MMA issuer (whole warp in lockstep, one elected lane issues) ----------------
         uint32_t j = 0, tiles_done = 0;
@@ -762,23 +564,24 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         const uint32_t b_step = static_cast<uint32_t>(p.x_slot_bytes) >> 4;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tiles_done) {
             const int as = tiles_done & 1;
-            if (tiles_done >= 2 && !mbar_wait_spin(&acc_empty[as], ((tiles_done >> 1) - 1) & 1)) {
+            if (tiles_done >= 2 && !mbar_wait_spin(&acc_empty[as], ((tiles_done >> 1) - 1) & 1, abort_flag)) {
                 if (lane == 0) fail(QWC_DEV_WAIT_TMEM_TIMEOUT);
                 break;
             }
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * kTsBN);
-            const uint32_t idesc = make_idesc(min(kTsBN, (tc_get_tile(p, tile).x_rows + 15) & ~15));
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * p.acc_stride);
+            const uint32_t idesc = make_idesc(min(p.acc_stride, (tc_get_tile(p, tile).x_rows + 15) & ~15));
             for (int kt = 0; kt < ktiles; ++kt, ++j) {
-                const uint32_t s = j % kStages;
-                if (!mbar_wait_spin(&full[s], (j / kStages) & 1u)) {
+                const uint32_t s = j & smask;
+                const bool got_full = mbar_wait_spin(&full[s], (j >> p.stage_shift) & 1u, abort_flag);   // all lanes poll: measured faster than one polling lane
+                if (!got_full) {
                     if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
                     ok = false;
                     break;
                 }
                 tc_fence_after();   // the converters' tcgen05.st happen-before these MMAs
                 const uint32_t b_lo = b_lo0 + s * b_step;
-                const uint32_t a_tmem = tmem_base + static_cast<uint32_t>(kTsAccCols + s * 32);
+                const uint32_t a_tmem = tmem_base + a_col0 + s * 32;
                 if (elect_one()) {
 #pragma unroll
                     for (int q = 0; q < kBK / 16; ++q)
@@ -793,79 +596,52 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         __syncwarp();
     } else if (warp >= kTsFirstConvWarp && warp < kTsFirstConvWarp + kConvWarps) {
         // ------------------------------- converters -------------------------------
-        // Converter warp c: lane quarter c & 3, group (c >> 3) takes every other raw step, and inside a step the warp
-        // decodes K tile (c >> 2) & 1 of the two.  A thread owns one weight row: it reads that row's half of the raw
-        // step (two units) with 16-byte loads (the lane stride of 80 / 144 bytes puts a quarter warp's 16-byte chunks in
-        // 8 distinct bank groups), decodes, and stores 32 columns of f16 pairs into its TMEM lane.
+        // Converter warp c: TMEM lane quarter c & 3, K tiles j with j % 4 == c >> 2.  A thread owns one weight row.
         const int c = warp - kTsFirstConvWarp;
-        const int qd = c & 3, kt2 = (c >> 2) & 1, grp = c >> 3;
-        constexpr int kHalfWords = FMT == FMT_HQ4_G32_M5 ? 10 : 18;   // words of two units
+        const int qd = c & 3, cl = c >> 2;
+        const int sub = cl % KPR;   // which K tile of its raw step this warp decodes (constant: 4 % KPR == 0)
+        const uint32_t row_ofs = static_cast<uint32_t>(qd * 32 + lane) * p.raw_row_bytes;
+        const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + a_col0;
         bool ok = true;
-        uint32_t r = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            for (int rs = 0; rs < raw_steps; ++rs, ++r) {
-                if (static_cast<int>(r & 1u) != grp) continue;
+        uint32_t jbase = 0;   // K tiles of the tiles already done
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, jbase += ktiles) {
+            // first K tile of this tile that belongs to this warp's class
+            for (uint32_t j = jbase + ((cl + 4u - (jbase & 3u)) & 3u); j < jbase + ktiles; j += 4) {
+                const uint32_t r = j / KPR;
                 const uint32_t rslot = r % p.raw_stages, rpar = (r / p.raw_stages) & 1u;
-                const uint32_t j = 2 * r + kt2, s = j % kStages, use = j / kStages;
-                bool started = false;
-                for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
-                    uint32_t v;
-                    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(raw_issued)) : "memory");
-                    if (v > r) {
-                        started = true;
-                        break;
-                    }
-                    __nanosleep(spin < 64 ? 20 : 200);
-                }
-                if (!started || !mbar_wait(&raw_full[rslot], rpar) || (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1u))) {
+                const uint32_t s = j & smask, use = j >> p.stage_shift;
+                // A raw slot's successive phases are consumed by different warps, and a parity wait cannot tell phase k
+                // from phase k - 2: wait first until the producer has started step r (which it does only after phase
+                // k - 1 was consumed); from then on the parity wait is exact.
+                const bool got_raw = wait_counter_above(raw_issued, r, abort_flag) && mbar_wait(&raw_full[rslot], rpar, abort_flag);
+                if (!got_raw) {
                     if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
                     ok = false;
                     break;
                 }
-                tc_fence_after();   // the MMAs that read this A stage are complete (tcgen05.commit -> empty[s])
-                const uint8_t* src = raw + rslot * raw_stage_bytes + (qd * 32 + lane) * p.raw_row_bytes + kt2 * (kHalfWords * 4);
-                uint32_t w[kHalfWords];
-                if (FMT == FMT_HQ4_G32_M5) {
-                    // 40 bytes at offset 0 (16-byte aligned) or 40 (8-byte aligned)
-                    if (kt2 == 0) {
-                        const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + 16);
-                        const uint2 d = *reinterpret_cast<const uint2*>(src + 32);
-                        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w; w[8] = d.x; w[9] = d.y;
-                    } else {
-                        const uint2 d = *reinterpret_cast<const uint2*>(src);
-                        const uint4 a = *reinterpret_cast<const uint4*>(src + 8), b = *reinterpret_cast<const uint4*>(src + 24);
-                        w[0] = d.x; w[1] = d.y; w[2] = a.x; w[3] = a.y; w[4] = a.z; w[5] = a.w; w[6] = b.x; w[7] = b.y; w[8] = b.z; w[9] = b.w;
-                    }
-                } else {
-                    // 72 bytes at offset 0 (16-byte aligned) or 72 (8-byte aligned)
-                    if (kt2 == 0) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const uint4 a = *reinterpret_cast<const uint4*>(src + 16 * i);
-                            w[4 * i] = a.x; w[4 * i + 1] = a.y; w[4 * i + 2] = a.z; w[4 * i + 3] = a.w;
-                        }
-                        const uint2 d = *reinterpret_cast<const uint2*>(src + 64);
-                        w[16] = d.x; w[17] = d.y;
-                    } else {
-                        const uint2 d = *reinterpret_cast<const uint2*>(src);
-                        w[0] = d.x; w[1] = d.y;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const uint4 a = *reinterpret_cast<const uint4*>(src + 8 + 16 * i);
-                            w[2 + 4 * i] = a.x; w[3 + 4 * i] = a.y; w[4 + 4 * i] = a.z; w[5 + 4 * i] = a.w;
-                        }
-                    }
-                }
+                uint32_t w[kTileWords];
                 uint32_t a32[32];
-                decode_regs_natural<FMT, 2>(w, a32);
-                tmem_st32(tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + static_cast<uint32_t>(kTsAccCols + s * 32), a32);
-                tmem_st_wait();
+                {
+                    load_tile_words<FMT>(raw + rslot * raw_stage_bytes + row_ofs, sub, w);
+                    decode_tile_natural<FMT>(w, a32);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_empty[rslot]);   // the packed words are in registers
+                // only now wait for the operand stage: the decode above overlapped the MMAs that were reading it
+                const bool got_empty = use == 0 || mbar_wait(&empty[s], (use - 1) & 1u, abort_flag);
+                if (!got_empty) {
+                    if (lane == 0) fail(QWC_DEV_WAIT_EMPTY_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();   // the MMAs that read this A stage are complete (tcgen05.commit -> empty[s])
+                {
+                    tmem_st32(lane_taddr + s * 32, a32);
+                    tmem_st_wait();
+                }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&full[s]);
-                    mbar_arrive(&raw_empty[rslot]);
-                }
+                if (lane == 0) mbar_arrive(&full[s]);
             }
         }
     } else if (warp >= kTsFirstConvWarp + kConvWarps) {
@@ -875,12 +651,18 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tiles_done) {
             const TileInfo ti = tc_get_tile(p, tile);
             const int as = tiles_done & 1;
-            if (!mbar_wait_relaxed(&acc_full[as], (tiles_done >> 1) & 1)) {
+            const bool got = mbar_wait_relaxed(&acc_full[as], (tiles_done >> 1) & 1, abort_flag);
+            // The four warps decide together whether to go on: the SwiGLU epilogue meets at a named barrier per 16
+            // tokens, so a warp that gave up alone would leave the others waiting there for ever.
+            volatile int* verdict = epi_ok + (tiles_done & 1u) * 4;
+            if (lane == 0) verdict[quarter] = got ? 1 : 0;
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (!(verdict[0] && verdict[1] && verdict[2] && verdict[3])) {
                 if (lane == 0) fail(QWC_DEV_WAIT_MMA_TIMEOUT);
                 break;
             }
             tc_fence_after();
-            tc_epilogue_tile(p, ti, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * kTsBN), xch,
+            tc_epilogue_tile(p, ti, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(as * p.acc_stride), xch,
                              quarter, lane);
             tc_fence_before();
             __syncwarp();
@@ -897,6 +679,8 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
 // Out-of-place activation rotation for the prefill path: rows of ldx -> dense rows of k.
 __global__ void __launch_bounds__(256) qwc_rotate_rows_kernel(const __half* __restrict__ x, int64_t ldx, __half* __restrict__ out,
                                                               int64_t m, int64_t k) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int64_t units = k / 32, total = m * units;
     const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
@@ -914,47 +698,41 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 template <int FMT>
-int launch_tc(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap64,
-              const CUtensorMap* xmaps, int smem, int grid) {
-    static bool configured[64] = {};
-    if (!configured[hal->device & 63]) {
-        QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured[hal->device & 63] = true;
-    }
-    qwc_gemm_tc_kernel<FMT><<<grid, kTcThreads, smem, st>>>(p, wmap, xmaps[0], xmaps[1], xmaps[2], wmap64);
-    QWC_CUDA_TRY(cudaGetLastError());
-    return QWC_OK;
-}
-
-template <int FMT>
 int launch_ts(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap64,
               const CUtensorMap* xmaps, int smem, int grid) {
-    static bool configured[64] = {};
-    if (!configured[hal->device & 63]) {
+    // once per device and instantiation; racing first calls both set the same value, which is harmless
+    static std::atomic<bool> configured[64];
+    if (!configured[hal->device & 63].load(std::memory_order_acquire)) {
         QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemm_ts_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured[hal->device & 63] = true;
+        configured[hal->device & 63].store(true, std::memory_order_release);
     }
-    qwc_gemm_ts_kernel<FMT><<<grid, kTsThreads, smem, st>>>(p, wmap, xmaps[0], xmaps[1], xmaps[2], wmap64);
-    QWC_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kTsThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QWC_CUDA_TRY(cudaLaunchKernelEx(&cfg, qwc_gemm_ts_kernel<FMT>, p, wmap, xmaps[0], xmaps[1], xmaps[2], wmap64));
     return QWC_OK;
 }
 
 }  // namespace
 
-// Can the tensor-core path take this call?  (HQ4_G32_M5 and HQ8_G32 banks, K % 128 == 0, 16-byte aligned rows.)
+// Can the tensor-core path take this call?  (K a multiple of one raw step, 16-byte aligned rows.)
 bool qwc_gemm_tc_supported(const qwc_hal* hal, const qwc_weight_view* w, int64_t m, int epilogue) {
     const int fmt = qwc_fmt_of(*w);
     if (hal->encode_tiled == nullptr) return false;
-    if (fmt != FMT_HQ4_G32_M5 && fmt != FMT_HQ8_G32) return false;
+    if (fmt == FMT_UNSUPPORTED) return false;
     // SwiGLU epilogues pair 64 gate rows with 64 up rows per tile
     if (epilogue != QWC_EPI_NONE && (w->n % 2 != 0 || (w->n / 2) % (kBM / 2) != 0)) return false;
-    // 16 tokens and more: measured at N = 17408, K = 5120 the tensor path takes 23.5 us at M = 16 against 28.3 us for the
-    // K-sliced stream kernel; at 9..12 tokens the stream kernel still wins (23.6 against 33.5 us)
-    static const int min_m = getenv("QWC_TC_MIN_M") ? atoi(getenv("QWC_TC_MIN_M")) : 16;
-    if (w->k % kRawK != 0 || m < min_m) return false;
+    // 16 tokens and more: below that the streaming kernel (register fragments, no decoded operand in memory) wins
+    if (w->k % (fmt == FMT_HQ4_G64 ? 256 : 128) != 0 || m < tune_env("QWC_TC_MIN_M", 16)) return false;
     if (reinterpret_cast<uintptr_t>(w->blocks) % 16 != 0) return false;
-    static const bool off = getenv("QWC_NO_TCGEN05") != nullptr;
-    return !off;
+    return tune_env("QWC_NO_TCGEN05", 0) == 0;
 }
 
 // Scratch for the rotated activations when the caller passes standard-basis x.
@@ -978,10 +756,14 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     p.k = static_cast<int>(w->k);
     p.y_f16 = y_dtype == QWC_F16;
     p.raw_row_bytes = fmt == FMT_HQ4_G32_M5 ? 80 : 144;
-    if (tiles == nullptr && fmt != FMT_HQ4_G32_M5) x_tile_rows = 192;   // 36-byte blocks: the raw stages are 1.8x larger
-    static const bool use_ts = getenv("QWC_TC_SS") == nullptr;   // default: decoded weights staged in tensor memory (tiles of <= 192 tokens)
-    if (use_ts && x_tile_rows > kTsBN) x_tile_rows = kTsBN;
+    if (tiles == nullptr) x_tile_rows = m <= 64 ? 64 : (m <= 128 ? 128 : kTsBN);   // dense: the narrowest tile that holds all tokens
+    if (x_tile_rows > kTsBN) x_tile_rows = kTsBN;
     p.x_tile_rows = x_tile_rows;
+    // few tokens per tile: short MMAs, so more operand stages in flight (and narrower accumulators to make room)
+    p.stages = x_tile_rows <= 128 ? kMaxStages : 4;
+    if (const int st_env = tune_env("QWC_TC_STAGES", 0); st_env == 4 || (st_env == 8 && x_tile_rows <= 128)) p.stages = st_env;
+    p.acc_stride = p.stages == kMaxStages ? 128 : kTsBN;
+    p.stage_shift = p.stages == kMaxStages ? 3 : 2;
     p.m_tiles = static_cast<int>((m + x_tile_rows - 1) / x_tile_rows);
     p.epilogue = epilogue;
     p.up_delta = static_cast<int>(w->n / 2);
@@ -989,22 +771,20 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     p.n_tiles = epilogue == QWC_EPI_NONE ? static_cast<int>((w->n + kBM - 1) / kBM) : static_cast<int>(w->n / kBM);
     const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
     p.x_slot_bytes = x_tile_rows * kBK * 2;
-    p.raw_stages = use_ts ? kTsMaxRaw : kMaxRaw;
-    auto smem_need = [&](int rs) {
-        return 1024 + kStages * (p.x_slot_bytes + (use_ts ? 0 : kWTileBytes)) + rs * raw_stage_bytes + 512 + p.xch_bytes;
-    };
+    p.raw_stages = kTsMaxRaw;
+    auto smem_need = [&](int rs) { return 1024 + p.stages * p.x_slot_bytes + rs * raw_stage_bytes + 512 + p.xch_bytes; };
     while (smem_need(p.raw_stages) > 227 * 1024 && p.raw_stages > 2) --p.raw_stages;
     if (smem_need(p.raw_stages) > 227 * 1024) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "shared-memory budget exceeded");
     const int smem = smem_need(p.raw_stages);
 
     const EncodeFn enc = reinterpret_cast<EncodeFn>(hal->encode_tiled);
     alignas(64) CUtensorMap wmaps[2];   // packed-weight boxes of 128 rows and (SwiGLU epilogues) 64 rows
-    alignas(64) CUtensorMap xmaps[3];   // activation boxes of 256, 128 and 64 rows
-    const int64_t row_bytes = (w->k / 32) * (fmt == FMT_HQ4_G32_M5 ? 20 : 36);
+    alignas(64) CUtensorMap xmaps[3];   // activation boxes of x_tile_rows, 128 and 64 rows
+    const int64_t row_bytes = (w->k / w->group) * qwc_block_bytes(w->kind, w->bits, w->group);
     for (int i = 0; i < 2; ++i) {
         const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(row_bytes / 8), static_cast<cuuint64_t>(w->n)};
         const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(row_bytes)};
-        const cuuint32_t box[2] = {static_cast<cuuint32_t>(p.raw_row_bytes / 8), static_cast<cuuint32_t>(i == 0 ? kBM : kBM / 2)};
+        cuuint32_t box[2] = {static_cast<cuuint32_t>(p.raw_row_bytes / 8), static_cast<cuuint32_t>(i == 0 ? kBM : kBM / 2)};
         const cuuint32_t estr[2] = {1, 1};
         const CUresult cr = enc(&wmaps[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w->blocks), gdim, gstride, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1023,33 +803,39 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     }
     const int64_t ntiles = tiles != nullptr ? max_tiles : static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     const int grid = static_cast<int>(ntiles < hal->sm_count ? (ntiles < 1 ? 1 : ntiles) : hal->sm_count);
-    if (use_ts) {
-        if (fmt == FMT_HQ4_G32_M5) return launch_ts<FMT_HQ4_G32_M5>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
-        return launch_ts<FMT_HQ8_G32>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
-    }
-    if (fmt == FMT_HQ4_G32_M5) return launch_tc<FMT_HQ4_G32_M5>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
-    return launch_tc<FMT_HQ8_G32>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
+    if (fmt == FMT_HQ4_G32_M5) return launch_ts<FMT_HQ4_G32_M5>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
+    if (fmt == FMT_HQ8_G32) return launch_ts<FMT_HQ8_G32>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
+    return launch_ts<FMT_HQ4_G64>(hal, st, p, wmaps[0], wmaps[1], xmaps, smem, grid);
 }
 
-int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
-                       void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace, size_t workspace_bytes) {
-    const __half* xr = static_cast<const __half*>(x);
-    int64_t ldxr = ldx;
+// Validation shared with the callers that must refuse before their first launch.
+int qwc_gemm_tc_check(const qwc_weight_view* w, const void* x, int64_t ldx, int64_t m, int x_is_rotated, const void* workspace,
+                      size_t workspace_bytes) {
     if (!x_is_rotated) {
         const size_t need = qwc_gemm_tc_workspace_bytes(w, m, 0);
         if (workspace == nullptr || workspace_bytes < need)
             return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace of %zu bytes needed (qwc_gemm_workspace_bytes), got %zu", need, workspace_bytes);
         if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace must be 16-byte aligned");
+    } else if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || ldx % 8 != 0) {
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "rotated activations must be 16-byte aligned with ldx %% 8 == 0 for the tensor-core path");
+    }
+    return QWC_OK;
+}
+
+int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
+                       void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace, size_t workspace_bytes) {
+    if (int rc = qwc_gemm_tc_check(w, x, ldx, m, x_is_rotated, workspace, workspace_bytes)) return rc;
+    const __half* xr = static_cast<const __half*>(x);
+    int64_t ldxr = ldx;
+    if (!x_is_rotated) {
         int64_t blocks = (m * (w->k / 32) + 7) / 8;
         if (blocks > hal->sm_count * 16) blocks = hal->sm_count * 16;
         qwc_rotate_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(xr, ldx, static_cast<__half*>(workspace), m, w->k);
         QWC_CUDA_TRY(cudaGetLastError());
         xr = static_cast<const __half*>(workspace);
         ldxr = w->k;
-    } else if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || ldx % 8 != 0) {
-        return qwc_fail(QWC_ERR_BAD_SHAPE, "rotated activations must be 16-byte aligned with ldx %% 8 == 0 for the tensor-core path");
     }
-    return tc_run(hal, st, w, xr, ldxr, m, y, y_dtype, ldy, nullptr, nullptr, 0, kBN, epilogue);
+    return tc_run(hal, st, w, xr, ldxr, m, y, y_dtype, ldy, nullptr, nullptr, 0, kTsBN, epilogue);
 }
 
 // Grouped expert GEMM: the same kernel over a device-side tile list (see qwc_moe_group_pairs).

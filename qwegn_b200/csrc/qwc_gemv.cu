@@ -26,6 +26,7 @@
 // shards of a tensor-parallel group: peer stores into every rank's inbox, flags, rank-ordered sum).
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -34,12 +35,19 @@
 
 namespace {
 
-constexpr int kConsumerWarps = 16;
+#ifndef QWC_GEMV_CONSUMER_WARPS
+#define QWC_GEMV_CONSUMER_WARPS 16
+#endif
+#ifndef QWC_GEMV_SMEM_KB
+#define QWC_GEMV_SMEM_KB 227
+#endif
+constexpr int kConsumerWarps = QWC_GEMV_CONSUMER_WARPS;
+constexpr int kCtasPerSm = QWC_GEMV_SMEM_KB <= 113 ? 2 : 1;   // half the shared memory: a second CTA (the next call's) fits beside this one
 constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
 constexpr int kTileRows = 16;
 constexpr int kMaxStages = 24;
 constexpr int kRowPad = 16;  // smem row stride = chunk bytes + 16: (stride / 4) % 32 == 4 -> conflict-free word reads
-constexpr int kSmemBudget = 227 * 1024;
+constexpr int kSmemBudget = QWC_GEMV_SMEM_KB * 1024;
 constexpr int kBarrierBytes = 512;  // 2 x kMaxStages mbarriers + the abort flag, padded to keep the stages 128-byte aligned
 
 template <int FMT> struct StreamCfg;
@@ -83,6 +91,8 @@ struct GemvParams {
     int red_bytes;    // smem bytes of the team reduction region
     int pdl;          // launched with programmatic stream serialization: weights prefetch before the dependency wait
     int use_tmap;     // full 16-row tiles arrive by one 2-D tensor copy instead of 16 row copies
+    int l2_evict_first;  // the weight stream is read once: mark its lines evict-first so that what a prefetch kernel
+                         // brought in for the next call outlives them in L2
     // segment mode (see the kernel): null in the ordinary one-bank form
     const qwc_gemv_seg* segs;
     const int32_t* seg_count;
@@ -90,6 +100,7 @@ struct GemvParams {
     // fused one-shot all-reduce over peer memory (row-parallel shards of a tensor-parallel group; ar_world > 1):
     int ar_world, ar_rank;
     uint32_t ar_epoch;        // call number: the flag value that marks this call's data as complete
+    uint64_t ar_wait_ns;      // limit of the peer wait (0: the library's default)
     float* ar_inbox[8];       // rank r's inbox for this call: [world][m][n] f32; slot [s] is written by rank s
     uint32_t* ar_flags[8];    // rank r's flags for this call: [world][grid]; word [s][cta] is written by CTA cta of rank s
 };
@@ -192,14 +203,17 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
-// Release store / acquire load of a shared-memory word (CTA scope).
+__device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+
+// Release store of a shared-memory word (CTA scope).
 __device__ __forceinline__ void st_release_cta(uint32_t* p, uint32_t v) {
     asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_cta(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
-    return v;
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
@@ -214,7 +228,7 @@ template <int FMT> __device__ __forceinline__ int x_offset(int tok, int unit, in
 }
 
 template <int FMT, int NT, int SUB>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) {
     using C = StreamCfg<FMT>;
     if (p.segs != nullptr) {
@@ -294,6 +308,8 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         int pslot = 0;
         uint32_t pparity = 0;  // phase parity of fill q in its slot
         bool ok = true;
+        uint64_t policy = 0;
+        if (p.l2_evict_first) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
         for (int r = 0; r < rounds && ok; ++r) {
             const int tl = min(T, njobs - r * T);
             for (int e = 0, sub = 0, c = 0; e < E && ok; ++e, ++c) {
@@ -311,7 +327,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                         pparity ^= 1u;
                     }
                     if (q >= static_cast<uint32_t>(p.stages)) {
-                        if (*abort_flag || !mbar_wait(&empty[slot], wait_parity)) {
+                        if (*abort_flag || !mbar_wait(&empty[slot], wait_parity, abort_flag)) {
                             if (!*abort_flag && lane == 0) atomicCAS(p.status, 0, QWC_DEV_WAIT_EMPTY_TIMEOUT);
                             *abort_flag = 1;
                             ok = false;
@@ -333,9 +349,11 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                         if (lane == 0) {
                             mbar_arrive_expect_tx(&full[slot], static_cast<uint32_t>(stage_bytes));
                             st_release_cta(issued, q + 1);
-                            tma_load_2d(stage0 + slot * stage_bytes, &tmap,
-                                        static_cast<int>((static_cast<int64_t>(p.unit0 + u0) * C::kUnitBytes) >> 3),
-                                        static_cast<int>(wrow), &full[slot]);
+                            const int tx = static_cast<int>((static_cast<int64_t>(p.unit0 + u0) * C::kUnitBytes) >> 3);
+                            if (p.l2_evict_first)
+                                tma_load_2d_hint(stage0 + slot * stage_bytes, &tmap, tx, static_cast<int>(wrow), &full[slot], policy);
+                            else
+                                tma_load_2d(stage0 + slot * stage_bytes, &tmap, tx, static_cast<int>(wrow), &full[slot]);
                         }
                         continue;
                     }
@@ -523,14 +541,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                     // wait cannot tell phase k from phase k - 2.  So first wait until the producer has started fill qn
                     // (it does that only after phase k - 1 of the slot was consumed); from then on the barrier is in
                     // phase k or past it and the parity wait is exact.
-                    for (uint32_t spin = 0; ld_acquire_cta(issued) <= qn; ++spin) {
-                        if (spin > (1u << 22)) {
-                            ok = false;
-                            break;
-                        }
-                        __nanosleep(spin < 64 ? 20 : 200);
-                    }
-                    ok = ok && mbar_wait(&full[slot], parity);
+                    ok = wait_counter_above(issued, qn, abort_flag) && mbar_wait(&full[slot], parity, abort_flag);
                     if (!ok) {
                         *abort_flag = 1;
                         if (lane == 0) atomicCAS(p.status, 0, QWC_DEV_WAIT_FULL_TIMEOUT);
@@ -686,14 +697,19 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             uint32_t* f = p.ar_flags[threadIdx.x] + p.ar_rank * grid + cta;
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ar_epoch) : "memory");
             const uint32_t* mine = p.ar_flags[p.ar_rank] + threadIdx.x * grid + cta;
+            // bounded by elapsed time: a peer that never raises its flag (it failed, or it never made the call) costs this
+            // rank the limit once, then the status word says so and the kernel finishes with whatever the inbox holds
             bool got = false;
-            for (uint32_t spin = 0; spin < (1u << 22); ++spin) {   // ~1 s at worst
+            const uint64_t t0 = qwc_globaltimer_ns();
+            const uint64_t limit = p.ar_wait_ns != 0 ? p.ar_wait_ns : static_cast<uint64_t>(QWC_WAIT_LIMIT_NS);
+            for (uint32_t spin = 0;; ++spin) {
                 uint32_t v;
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
                 if (v == p.ar_epoch) {
                     got = true;
                     break;
                 }
+                if ((spin & 15u) == 15u && qwc_globaltimer_ns() - t0 > limit) break;
                 __nanosleep(spin < 256 ? 40 : 250);
             }
             if (!got) atomicCAS(p.status, 0, QWC_DEV_WAIT_PEER_TIMEOUT);
@@ -710,6 +726,36 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             else static_cast<float*>(Y_)[o] = sum;
         }
     }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Companion of the stream kernel in static-weights mode: brings the head of every CTA's row range of the NEXT call's
+// bank into L2 while the previous kernel of the stream is still running.  The stream kernel keeps one CTA of ~220 KB
+// of shared memory per SM, so the next call's CTAs cannot become resident (and start their own copies) before the
+// previous call's CTAs have left; between the two, HBM would idle for the launch gap, the barrier set-up and one DRAM
+// latency.  This kernel needs no shared memory and one warp per SM, so it runs beside the previous call's CTAs: it
+// issues bulk L2 prefetches and then waits for the previous grid (so that the stream kernel launched after it, which
+// waits for THIS grid, still runs after everything before it).  Weights are load-time data under the static-weights
+// promise, so reading them early is safe.  CTA b covers the rows CTA b of the stream kernel will read.
+__global__ void __launch_bounds__(32) qwc_gemv_prefetch_kernel(const uint8_t* __restrict__ blocks, int64_t row_bytes,
+                                                               int row_quantum, int q_lo, int q_rem, int sub_stride_rows,
+                                                               int subs, int64_t cap_bytes) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int bq = static_cast<int>(blockIdx.x);
+    const int64_t rb = static_cast<int64_t>(q_lo * bq + min(bq, q_rem)) * row_quantum;
+    const int64_t re = rb + static_cast<int64_t>(q_lo + (bq < q_rem ? 1 : 0)) * row_quantum;
+    constexpr int kPiece = 4096;
+    for (int s = 0; s < subs; ++s) {   // a paired gate||up bank has two row ranges per CTA
+        const uint8_t* base = blocks + (rb + static_cast<int64_t>(s) * sub_stride_rows) * row_bytes;
+        int64_t bytes = (re - rb) * row_bytes;
+        if (bytes > cap_bytes / subs) bytes = cap_bytes / subs;
+        bytes &= ~static_cast<int64_t>(15);
+        for (int64_t o = static_cast<int64_t>(threadIdx.x) * kPiece; o < bytes; o += 32 * kPiece) {
+            const uint32_t sz = static_cast<uint32_t>(bytes - o < kPiece ? bytes - o : kPiece);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + o), "r"(sz) : "memory");
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -779,14 +825,14 @@ struct StreamGeom {
     int chunk_units, nchunks, team_warps, stages, stride, x_bytes, red_bytes, smem_bytes;
 };
 
-constexpr int kXCapBytes = 112 * 1024;  // at most this much shared memory for the staged activations of a K slice
+constexpr int kXCapBytes = (QWC_GEMV_SMEM_KB / 2 - 1) * 1024;  // at most this much shared memory for the staged activations of a K slice
 
 // units: 32-element units of this launch's K slice; jobs: 16-row (32 for FWHT) jobs per CTA.  The team count T
 // follows the jobs a CTA has (teams work on different jobs concurrently); K is cut into the fewest equal chunks that
 // leave the ring T + 2 stages deep (measured: wide chunks beat a deep ring, equal chunks beat a short last one).
 // Chunks are multiples of 8 units: with the 16-byte row pad the smem row stride in words is then 4 mod 8, which
 // makes the per-lane word reads of 8 rows x 4 units hit 32 distinct banks (a multiple of 4 only gives 8-way
-// conflicts).  QWC_GEMV_W / QWC_GEMV_CHUNK override both (tuning knobs).  Returns false when no geometry fits.
+// conflicts).  Returns false when no geometry fits.
 template <int FMT>
 bool plan_geometry(int units, int m, int nt, int sub, int jobs, int budget, StreamGeom* g) {
     using C = StreamCfg<FMT>;
@@ -801,12 +847,11 @@ bool plan_geometry(int units, int m, int nt, int sub, int jobs, int budget, Stre
     int teams = 1;
     // at most 8 teams: 16 single-warp teams need 18 stages, which forces 32-unit chunks, and narrow chunks cost far more
     // than wide teams (N = 248320: 198 us with 16 x 1 warps and 32-unit chunks, 139 us with 8 x 2 warps and 56-unit chunks)
-    while (teams < jobs && teams < 8) teams <<= 1;
+    while (teams < jobs && teams < 8 && teams < kConsumerWarps) teams <<= 1;
     // short rows (K <= 1024): a job is a handful of groups, so a warp takes a whole job alone and there is no team reduction
-    if (units <= 32 && jobs >= 16) teams = 16;
-    static const int env_w = getenv("QWC_GEMV_W") ? atoi(getenv("QWC_GEMV_W")) : 0;
-    static const int env_chunk = getenv("QWC_GEMV_CHUNK") ? atoi(getenv("QWC_GEMV_CHUNK")) : 0;
-    if (env_w == 1 || env_w == 2 || env_w == 4 || env_w == 8 || env_w == 16) teams = kConsumerWarps / env_w;
+    if (units <= 32 && jobs >= 16) teams = kConsumerWarps;
+    const int env_w = tune_env("QWC_GEMV_W", 0), env_chunk = tune_env("QWC_GEMV_CHUNK", 0);
+    if ((env_w == 1 || env_w == 2 || env_w == 4 || env_w == 8 || env_w == 16) && env_w <= kConsumerWarps) teams = kConsumerWarps / env_w;
     for (; teams >= 1; teams >>= 1) {
         const int w = kConsumerWarps / teams;
         const int want = teams + 2;
@@ -865,11 +910,12 @@ bool plan_geometry(int units, int m, int nt, int sub, int jobs, int budget, Stre
 template <int FMT, int NT, int SUB>
 int launch_stream_inst(const qwc_hal* hal, cudaStream_t st, const GemvParams& p, const CUtensorMap& tmap, int smem_bytes,
                        int grid) {
-    static bool configured[64] = {};
-    if (!configured[hal->device & 63]) {
+    // once per device and instantiation; racing first calls both set the same value, which is harmless
+    static std::atomic<bool> configured[64];
+    if (!configured[hal->device & 63].load(std::memory_order_acquire)) {
         QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemv_stream_kernel<FMT, NT, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           kSmemBudget));
-        configured[hal->device & 63] = true;
+        configured[hal->device & 63].store(true, std::memory_order_release);
     }
     if (p.pdl) {
         cudaLaunchConfig_t cfg{};
@@ -890,8 +936,11 @@ int launch_stream_inst(const qwc_hal* hal, cudaStream_t st, const GemvParams& p,
     return QWC_OK;
 }
 
+constexpr int kMaxSlices = 64;
+
+// dry != 0: plan only (every refusal this function can make), launch nothing.
 template <int FMT, int NT>
-int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_units, float* workspace) {
+int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_units, float* workspace, bool dry = false) {
     const int sub = p.epilogue == QWC_EPI_NONE ? 1 : (p.epilogue == QWC_EPI_SILU_PAIR ? 2 : 4);
     // K slices: as few as keep the staged activations within their share of shared memory.
     const int quantum = FMT == FMT_HQ4_G64 ? 8 : 4;
@@ -911,25 +960,57 @@ int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_u
         if (slices > 1) return qwc_fail(QWC_ERR_BLOCKED, "segment mode takes one K slice (tokens x K x 2 B <= 112 KB)");
         grid = p.seg_grid;
     }
+    // The geometry of every K slice is planned before the first launch, so that a refusal leaves the stream untouched.
+    if (slices > kMaxSlices) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "k needs %d slices, at most %d are planned", slices, kMaxSlices);
+    StreamGeom geoms[kMaxSlices];
+    {
+        const int rows_per_cta = p.segs != nullptr ? p.seg_cols : (p.n_out + grid - 1) / grid;
+        const int job_rows = sub == 4 ? 32 : 16;
+        const int jobs = (rows_per_cta + job_rows - 1) / job_rows;
+        for (int s = 0; s < slices; ++s) {
+            const int u0 = s * per_slice;
+            const int units = total_units - u0 < per_slice ? total_units - u0 : per_slice;
+            if (!plan_geometry<FMT>(units, p.m, NT, sub, jobs, kSmemBudget, &geoms[s]))
+                return qwc_fail(QWC_ERR_BAD_GEOMETRY, "no shared-memory geometry fits this k slice");
+        }
+    }
+    if (dry) return QWC_OK;
+    // Static-weights mode: a shared-memory-free companion kernel brings the head of every CTA's row range into L2 while
+    // the previous kernel of the stream still holds the SMs' shared memory (see qwc_gemv_prefetch_kernel).  A bank that
+    // fits in L2 beside the one being streamed (<= 48 MB of the 126 MB) is prefetched whole; of a larger one only the
+    // first 128 KB per CTA (19 MB: what the gap between two calls can absorb), and the stream kernel then marks its
+    // own reads evict-first so that they do not push the prefetched lines out (measured, N x K = 12288 x 4096 /
+    // 17408 x 5120 HQ4_G32 / 17408 x 5120 HQ8_G32: 9.8 -> 8.6, 14.2 -> 14.0, 19.6 -> 18.7 us per call; prefetching
+    // the larger banks whole, or without the evict-first mark, lost up to 18 %).
+    const bool small_bank = static_cast<int64_t>(p.n) * p.row_bytes <= (48ll << 20);
+    const int64_t pf_cap = static_cast<int64_t>(tune_env("QWC_GEMV_PF_KB", small_bank ? 512 : 128)) * 1024;
+    if (p.pdl && p.segs == nullptr && pf_cap > 0 && p.row_bytes % 16 == 0) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(32);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        QWC_CUDA_TRY(cudaLaunchKernelEx(&cfg, qwc_gemv_prefetch_kernel, p.blocks, p.row_bytes, p.row_quantum, quanta / grid,
+                                        quanta % grid, p.n_out, sub == 1 ? 1 : 2, pf_cap));
+    }
     for (int s = 0; s < slices; ++s) {
         GemvParams q = p;
         q.q_lo = quanta / grid;
         q.q_rem = quanta % grid;
+        q.l2_evict_first = p.pdl && tune_env("QWC_GEMV_EVICT_FIRST", small_bank ? 0 : 1) != 0;
         q.unit0 = s * per_slice;
         q.units = total_units - q.unit0 < per_slice ? total_units - q.unit0 : per_slice;
         q.partial = workspace;
         q.acc_in = s > 0;
         q.acc_out = s + 1 < slices;
-        StreamGeom g;
-        const int rows_per_cta = p.segs != nullptr ? p.seg_cols : (p.n_out + grid - 1) / grid;
-        const int job_rows = sub == 4 ? 32 : 16;
-        const int jobs = (rows_per_cta + job_rows - 1) / job_rows;
-        if (!plan_geometry<FMT>(q.units, q.m, NT, sub, jobs, kSmemBudget, &g))
-            return qwc_fail(QWC_ERR_BAD_GEOMETRY, "no shared-memory geometry fits this k slice");
-        static const bool trace = getenv("QWC_GEMV_TRACE") != nullptr;   // tuning aid: print the chosen geometry
-        if (trace)
-            fprintf(stderr, "qwc_gemv: fmt %d m %d units %d jobs/cta %d -> chunk %d x %d, teams %d x %d warps, %d stages, stride %d, smem %d\n",
-                    FMT, q.m, q.units, jobs, g.chunk_units, g.nchunks, kConsumerWarps / g.team_warps, g.team_warps, g.stages,
+        const StreamGeom& g = geoms[s];
+        if (tune_env("QWC_GEMV_TRACE", 0))   // tuning aid: print the chosen geometry
+            fprintf(stderr, "qwc_gemv: fmt %d m %d units %d -> chunk %d x %d, teams %d x %d warps, %d stages, stride %d, smem %d\n",
+                    FMT, q.m, q.units, g.chunk_units, g.nchunks, kConsumerWarps / g.team_warps, g.team_warps, g.stages,
                     g.stride, g.smem_bytes);
         q.chunk_units = g.chunk_units;
         q.nchunks = g.nchunks;
@@ -942,8 +1023,7 @@ int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_u
         alignas(64) CUtensorMap tmap;
         memset(&tmap, 0, sizeof(tmap));
         q.use_tmap = 0;
-        static const bool no_tmap = getenv("QWC_GEMV_NO_TMAP") != nullptr;
-        if (hal->encode_tiled != nullptr && g.stride / 8 <= 256 && !no_tmap) {
+        if (hal->encode_tiled != nullptr && g.stride / 8 <= 256) {
             using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                           const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                           CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -968,13 +1048,14 @@ int launch_stream(const qwc_hal* hal, cudaStream_t st, GemvParams p, int total_u
 
 template <int FMT>
 int launch_fmt(const qwc_hal* hal, cudaStream_t st, GemvParams p, int64_t m, bool stream_ok, int total_units,
-               float* workspace) {
+               float* workspace, bool dry) {
     const char* xb = reinterpret_cast<const char*>(p.x);
     char* yb = static_cast<char*>(p.y);
     const int64_t ysz = p.y_f16 ? 2 : 4;
     if (!stream_ok) {
         if (p.epilogue == QWC_EPI_SILU_PAIR_FWHT)
             return qwc_fail(QWC_ERR_BAD_GEOMETRY, "fused FWHT epilogue needs 16-byte aligned rows (K %% 128 == 0)");
+        if (dry) return QWC_OK;
         p.m = static_cast<int>(m);
         p.units = total_units;
         const int64_t items = static_cast<int64_t>(p.n_out) * m;
@@ -986,13 +1067,18 @@ int launch_fmt(const qwc_hal* hal, cudaStream_t st, GemvParams p, int64_t m, boo
         return QWC_OK;
     }
     // M > 16 is served in slabs of 16 tokens (each slab re-reads the weights); the tensor-core GEMM takes over there.
+    // With several slabs a planning pass comes first, so that no slab can refuse after an earlier one ran (a single slab
+    // plans all its K slices before its first launch anyway).
+    for (int pass = (dry || m <= 16) ? 1 : 0; pass < 2; ++pass)
     for (int64_t m0 = 0; m0 < m; m0 += 16) {
+        const bool plan_only = pass == 0 || dry;
+        if (pass == 0 && m0 != 0 && m0 + 16 < m) continue;   // full slabs plan alike: the first and the last are enough
         GemvParams q = p;
         q.m = static_cast<int>(m - m0 < 16 ? m - m0 : 16);
         q.x = reinterpret_cast<const __half*>(xb + m0 * p.ldx * 2);
         q.y = yb + m0 * p.ldy * ysz;
-        const int rc = q.m <= 8 ? launch_stream<FMT, 1>(hal, st, q, total_units, workspace)
-                                : launch_stream<FMT, 2>(hal, st, q, total_units, workspace);
+        const int rc = q.m <= 8 ? launch_stream<FMT, 1>(hal, st, q, total_units, workspace, plan_only)
+                                : launch_stream<FMT, 2>(hal, st, q, total_units, workspace, plan_only);
         if (rc) return rc;
     }
     return QWC_OK;
@@ -1014,7 +1100,13 @@ size_t qwc_gemv_workspace_bytes(const qwc_weight_view* w, int64_t m) {
 // Host entry used by qwc_gemm.  All arguments were validated by the caller.
 int qwc_launch_gemv_ar(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
                        void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace,
-                       size_t workspace_bytes, const qwc_allreduce_ctx* ar);
+                       size_t workspace_bytes, const qwc_allreduce_ctx* ar, bool dry = false);
+
+// Every refusal the streaming path can make for these arguments, without a launch.
+int qwc_gemv_check(const qwc_hal* hal, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx, void* y, int y_dtype,
+                   int64_t ldy, int epilogue, int x_is_rotated, void* workspace, size_t workspace_bytes) {
+    return qwc_launch_gemv_ar(hal, nullptr, w, x, m, ldx, y, y_dtype, ldy, epilogue, x_is_rotated, workspace, workspace_bytes, nullptr, true);
+}
 
 int qwc_launch_gemv(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
                     void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace,
@@ -1025,12 +1117,13 @@ int qwc_launch_gemv(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* 
 // ar != null: the fused all-reduce form (validated by the caller: one K slice, <= 8 tokens, no epilogue, 16-byte rows).
 int qwc_launch_gemv_ar(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w, const void* x, int64_t m, int64_t ldx,
                        void* y, int y_dtype, int64_t ldy, int epilogue, int x_is_rotated, void* workspace,
-                       size_t workspace_bytes, const qwc_allreduce_ctx* ar) {
+                       size_t workspace_bytes, const qwc_allreduce_ctx* ar, bool dry) {
     GemvParams p{};
     if (ar != nullptr) {
         p.ar_world = ar->world;
         p.ar_rank = ar->rank;
         p.ar_epoch = ar->epoch;
+        p.ar_wait_ns = ar->reserved > 0 ? static_cast<uint64_t>(ar->reserved) * 1000ull : 0ull;
         for (int r = 0; r < ar->world && r < 8; ++r) {
             p.ar_inbox[r] = static_cast<float*>(ar->inbox[r]);
             p.ar_flags[r] = static_cast<uint32_t*>(ar->flags[r]);
@@ -1052,6 +1145,7 @@ int qwc_launch_gemv_ar(const qwc_hal* hal, cudaStream_t st, const qwc_weight_vie
     p.epilogue = epilogue;
     p.x_is_rotated = x_is_rotated;
     p.row_quantum = epilogue == QWC_EPI_SILU_PAIR_FWHT ? 32 : 1;
+    if (const int rq = tune_env("QWC_GEMV_RQ", 0); rq > 0 && p.n_out % rq == 0 && rq % p.row_quantum == 0) p.row_quantum = rq;
     p.pdl = hal->static_weights;
     const int total_units = static_cast<int>(w->k / 32);
     const bool stream_ok = (p.row_bytes % 16 == 0) && (reinterpret_cast<uintptr_t>(w->blocks) % 16 == 0);
@@ -1062,9 +1156,9 @@ int qwc_launch_gemv_ar(const qwc_hal* hal, cudaStream_t st, const qwc_weight_vie
         return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace must be 4-byte aligned");
     float* ws = need > 0 ? static_cast<float*>(workspace) : nullptr;
     switch (fmt) {
-        case FMT_HQ4_G32_M5: return launch_fmt<FMT_HQ4_G32_M5>(hal, st, p, m, stream_ok, total_units, ws);
-        case FMT_HQ8_G32: return launch_fmt<FMT_HQ8_G32>(hal, st, p, m, stream_ok, total_units, ws);
-        case FMT_HQ4_G64: return launch_fmt<FMT_HQ4_G64>(hal, st, p, m, stream_ok, total_units, ws);
+        case FMT_HQ4_G32_M5: return launch_fmt<FMT_HQ4_G32_M5>(hal, st, p, m, stream_ok, total_units, ws, dry);
+        case FMT_HQ8_G32: return launch_fmt<FMT_HQ8_G32>(hal, st, p, m, stream_ok, total_units, ws, dry);
+        case FMT_HQ4_G64: return launch_fmt<FMT_HQ4_G64>(hal, st, p, m, stream_ok, total_units, ws, dry);
         default: return qwc_fail(QWC_ERR_BAD_WEIGHTS, "unsupported container");
     }
 }

@@ -19,14 +19,15 @@ int qwc_launch_gemv_segments(const qwc_hal*, cudaStream_t, const qwc_weight_view
 namespace {
 
 constexpr int kTileW = 128;  // weight rows per grouped-GEMM tile
-// Activation rows per grouped-GEMM tile.  The tensor-core kernel pays a fixed cost per K tile whatever the token
-// count, so fewer, taller tiles win (64-row tiles were measured 30 % slower at 64 rows per expert); 192 rows is the
-// tallest tile whose stages fit in shared memory for the 36-byte containers too.  The kernel still fetches only a
-// 64- or 128-row activation box when the tile is that small.
+// Activation rows per grouped-GEMM tile.  Every tile decodes its 128 weight rows once whatever its token count, so an
+// expert should fit in one tile; 192 rows is the tallest tile the tensor-memory budget allows.  The kernel fetches only
+// a 64- or 128-row activation box when the tile is that small.
 inline int moe_tile_rows(int64_t pairs, int64_t e) {
-    static const int env_rows = getenv("QWC_MOE_TILE_ROWS") ? atoi(getenv("QWC_MOE_TILE_ROWS")) : 0;   // tuning knob
+    const int env_rows = tune_env("QWC_MOE_TILE_ROWS", 0);
     if (env_rows == 64 || env_rows == 128 || env_rows == 192) return env_rows;
-    return (pairs >= 0 && e > 0) ? 192 : 192;
+    // Up to ~85 rows per expert on average, hardly any expert exceeds 128 rows: tiles of 128 rows then let the kernel run
+    // with eight operand stages (see qwc_gemm_tc.cu); above that, 192-row tiles keep an expert in one tile more often.
+    return (e > 0 && pairs * 3 <= e * 256) ? 128 : 192;
 }
 
 __device__ __forceinline__ bool finite_bits(float v) { return (__float_as_uint(v) & 0x7F800000u) != 0x7F800000u; }
@@ -35,6 +36,7 @@ __device__ __forceinline__ bool finite_bits(float v) { return (__float_as_uint(v
 __global__ void __launch_bounds__(128) qwc_moe_route_kernel(const float* __restrict__ logits, int t_rows, int e, int k,
                                                             int norm_topk, float routed_scale, int32_t* __restrict__ idx,
                                                             float* __restrict__ wts) {
+    pdl_enter();
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= t_rows) return;
@@ -131,6 +133,7 @@ __device__ __forceinline__ float router_cvt(unsigned short v) { return __uint_as
 template <typename XT, typename WT>
 __global__ void __launch_bounds__(256) qwc_moe_router_gemm_kernel(const XT* __restrict__ x, int64_t ldx, const WT* __restrict__ w,
                                                                   int t_rows, int e, int h, float* __restrict__ y) {
+    pdl_enter();
     __shared__ float xs[64][33];
     __shared__ float ws[64][33];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -198,6 +201,7 @@ constexpr int kSortChunk = 8192;
 
 __global__ void __launch_bounds__(512) qwc_moe_count_kernel(const int32_t* __restrict__ idx, int pairs, int e,
                                                             int32_t* __restrict__ counts, int32_t* __restrict__ inv_perm) {
+    pdl_enter();
     __shared__ int s_idx[kSortChunk];
     const int lane = threadIdx.x & 31;
     const int ex = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -227,6 +231,7 @@ __global__ void __launch_bounds__(512) qwc_moe_plan_kernel(const int32_t* counts
                                                            qwc_moe_tile* __restrict__ tiles_dn, int32_t* __restrict__ tile_counts) {
     __shared__ int s_off[513];
     __shared__ int s_tx[513];   // activation-tile prefix
+    pdl_enter();
     if (threadIdx.x == 0) {
         int run = 0, tx = 0;
         for (int i = 0; i < e; ++i) {
@@ -263,6 +268,7 @@ __global__ void __launch_bounds__(512) qwc_moe_plan_kernel(const int32_t* counts
 __global__ void __launch_bounds__(512) qwc_moe_place_kernel(const int32_t* __restrict__ idx, int pairs, int e, int k,
                                                             const int32_t* __restrict__ expert_off, int32_t* __restrict__ sorted_pair,
                                                             int32_t* __restrict__ sorted_tok, int32_t* __restrict__ inv_perm) {
+    pdl_enter();
     __shared__ int s_idx[kSortChunk];
     const int lane = threadIdx.x & 31;
     const int ex = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -308,6 +314,7 @@ __global__ void __launch_bounds__(kSortCta) qwc_moe_sort_kernel(const int32_t* _
     __shared__ int s_off[513];
     __shared__ int s_tx[513];
     __shared__ int s_wh[kSortCta / 32][512];
+    pdl_enter();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lo = blockIdx.x * kSortCta;
     for (int i = tid; i < e; i += kSortCta) s_cnt[i] = 0;
@@ -431,6 +438,7 @@ struct MoeSeg {
 __global__ void __launch_bounds__(512) qwc_moe_decode_plan_kernel(const int32_t* __restrict__ expert_off, int e, int inter, int h,
                                                                   int cols_gu, int cols_dn, MoeSeg* __restrict__ segs_gu,
                                                                   MoeSeg* __restrict__ segs_dn, int32_t* __restrict__ seg_counts) {
+    pdl_enter();
     __shared__ int s_warp[16];
     const int ex = threadIdx.x, lane = ex & 31, warp = ex >> 5;
     const int cnt = ex < e ? expert_off[ex + 1] - expert_off[ex] : 0;
@@ -466,6 +474,7 @@ __global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __res
                                                              const int32_t* __restrict__ sorted_tok,
                                                              const int32_t* __restrict__ expert_off, int e, int rotate, int vec,
                                                              __half* __restrict__ xs) {
+    pdl_enter();
     const int lane = threadIdx.x & 31, t4 = lane & 3, q8 = lane >> 2;
     const int units = h / 32;
     const int64_t total = static_cast<int64_t>(expert_off[e]) * units;
@@ -518,6 +527,7 @@ __global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __res
 // h[p, i] = fwht32(f16(silu(g) * u)) over expert-sorted rows; one warp per (row, 32-wide slice of inter).
 __global__ void __launch_bounds__(256) qwc_moe_silu_mul_kernel(const __half* __restrict__ gu, const int32_t* __restrict__ row_count,
                                                                int64_t rows_cap, int inter, int rotate, __half* __restrict__ hout) {
+    pdl_enter();
     const int lane = threadIdx.x & 31;
     const int units = inter / 32;
     const int64_t rows = row_count != nullptr ? static_cast<int64_t>(*row_count) : rows_cap;
@@ -538,23 +548,32 @@ __global__ void __launch_bounds__(256) qwc_moe_silu_mul_kernel(const __half* __r
     }
 }
 
-// out[t, :] = sum_k wts[t, k] * dn[inv_perm[t, k], :]; one thread per (token, 2 columns), f32 accumulate in k order.
-template <typename DnT, typename OutT>
+// out[t, :] = sum_k wts[t, k] * dn[inv_perm[t, k], :] (+ gate[t] * shared[t, :], the shared-expert term of the
+// reference's qwg_moe_down_reduce_combine_f32); one thread per (token, VEC columns) with 16-byte loads when VEC
+// elements of DnT are 16 bytes (VEC = 8 for f16 rows, 4 for f32 rows; VEC = 2 is the fallback for odd shapes),
+// f32 accumulate in route order.
+template <typename DnT, typename OutT, int VEC>
 __global__ void __launch_bounds__(256) qwc_moe_combine_kernel(const DnT* __restrict__ dn, const int32_t* __restrict__ inv_perm,
-                                                              const float* __restrict__ wts, int t_rows, int k, int h,
+                                                              const float* __restrict__ wts, const float* __restrict__ shared,
+                                                              const float* __restrict__ gate, int t_rows, int k, int h,
                                                               OutT* __restrict__ out) {
-    const int64_t total = static_cast<int64_t>(t_rows) * (h / 2);
+    pdl_enter();
+    const int per_row = h / VEC;
+    const int64_t total = static_cast<int64_t>(t_rows) * per_row;
     for (int64_t it = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; it < total;
          it += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int t = static_cast<int>(it / (h / 2));
-        const int c = static_cast<int>(it % (h / 2)) * 2;
-        float a0 = 0.0f, a1 = 0.0f;
+        const int t = static_cast<int>(it / per_row);
+        const int c = static_cast<int>(it % per_row) * VEC;
+        float acc[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
         // eight routes at a time: all positions and weights first, then all rows, then the sums in route order, so the
         // loads of a batch are in flight together instead of one dependent pair after the other
         constexpr int kBatch = 8;
         for (int j0 = 0; j0 < k; j0 += kBatch) {
             int pos[kBatch];
-            float w[kBatch], v0[kBatch], v1[kBatch];
+            float w[kBatch];
+            float v[kBatch][VEC];
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
                 const bool in = j0 + u < k;
@@ -563,29 +582,56 @@ __global__ void __launch_bounds__(256) qwc_moe_combine_kernel(const DnT* __restr
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                v0[u] = v1[u] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) v[u][i] = 0.0f;
                 if (pos[u] < 0) continue;
+                const DnT* src = dn + static_cast<int64_t>(pos[u]) * h + c;
                 if (sizeof(DnT) == 2) {
-                    const __half2 v = *reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(dn) + static_cast<int64_t>(pos[u]) * h + c);
-                    v0[u] = __low2float(v);
-                    v1[u] = __high2float(v);
+                    if (VEC == 8) {
+                        const uint4 raw = *reinterpret_cast<const uint4*>(src);
+                        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            v[u][2 * i] = __low2float(h2[i]);
+                            v[u][2 * i + 1] = __high2float(h2[i]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < VEC / 2; ++i) {
+                            const __half2 hv = reinterpret_cast<const __half2*>(src)[i];
+                            v[u][2 * i] = __low2float(hv);
+                            v[u][2 * i + 1] = __high2float(hv);
+                        }
+                    }
                 } else {
-                    const float2 v = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(dn) + static_cast<int64_t>(pos[u]) * h + c);
-                    v0[u] = v.x;
-                    v1[u] = v.y;
+                    if (VEC == 4) {
+                        const float4 raw = *reinterpret_cast<const float4*>(src);
+                        v[u][0] = raw.x; v[u][1] = raw.y; v[u][2] = raw.z; v[u][3] = raw.w;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) v[u][i] = reinterpret_cast<const float*>(src)[i];
+                    }
                 }
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u)
                 if (pos[u] >= 0) {
-                    a0 = fmaf(w[u], v0[u], a0);
-                    a1 = fmaf(w[u], v1[u], a1);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(w[u], v[u][i], acc[i]);
                 }
         }
+        if (shared != nullptr) {
+            const float g = gate[t];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = fmaf(g, shared[static_cast<int64_t>(t) * h + c + i], acc[i]);
+        }
+        OutT* dst = out + static_cast<int64_t>(t) * h + c;
         if (sizeof(OutT) == 2) {
-            *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(out) + static_cast<int64_t>(t) * h + c) = __floats2half2_rn(a0, a1);
+#pragma unroll
+            for (int i = 0; i < VEC / 2; ++i) reinterpret_cast<__half2*>(dst)[i] = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
         } else {
-            *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + static_cast<int64_t>(t) * h + c) = make_float2(a0, a1);
+#pragma unroll
+            for (int i = 0; i < VEC / 2; ++i) reinterpret_cast<float2*>(dst)[i] = make_float2(acc[2 * i], acc[2 * i + 1]);
         }
     }
 }
@@ -661,7 +707,7 @@ int qwc_moe_router_gemm(qwc_hal* hal, qwc_stream stream, const void* x, int32_t 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int ti = static_cast<int>(t), ei = static_cast<int>(e), hi = static_cast<int>(h);
 #define QWC_ROUTER_LAUNCH(XT, WT) \
-    qwc_moe_router_gemm_kernel<XT, WT><<<grid, 256, 0, st>>>(static_cast<const XT*>(x), ldx, static_cast<const WT*>(w), ti, ei, hi, logits)
+    QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_router_gemm_kernel<XT, WT>, grid, dim3(256), 0, st, static_cast<const XT*>(x), ldx, static_cast<const WT*>(w), ti, ei, hi, logits))
     if (x_dtype == QWC_F32) {
         if (w_dtype == QWC_F32) QWC_ROUTER_LAUNCH(float, float);
         else if (w_dtype == QWC_F16) QWC_ROUTER_LAUNCH(float, __half);
@@ -687,9 +733,8 @@ int qwc_moe_route(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t 
     if (t == 0) return QWC_OK;
     if (!logits || !idx || !wts) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
     const int blocks = static_cast<int>((t + 3) / 4);
-    qwc_moe_route_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, static_cast<int>(t), static_cast<int>(e),
-                                                                               static_cast<int>(k), norm_topk, routed_scale, idx, wts);
-    QWC_CUDA_TRY(cudaGetLastError());
+    QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_route_kernel, dim3(blocks), dim3(128), 0, static_cast<cudaStream_t>(stream), logits,
+                                static_cast<int>(t), static_cast<int>(e), static_cast<int>(k), norm_topk, routed_scale, idx, wts));
     return QWC_OK;
 }
 
@@ -712,10 +757,10 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
         int grid = static_cast<int>(pairs > 0 ? (pairs + kSortCta - 1) / kSortCta : 1);
         // the tile lists are written expert by expert, experts dealt over the CTAs: a short pair list still gets 32 CTAs for that
         if ((tiles_gu != nullptr || tiles_dn != nullptr) && grid < 32) grid = static_cast<int>(e < 32 ? e : 32);
-        qwc_moe_sort_kernel<<<grid, kSortCta, 0, st>>>(idx, static_cast<int>(pairs), static_cast<int>(e), static_cast<int>(k),
-                                                       moe_tile_rows(pairs, e), static_cast<int>(gu_rows), static_cast<int>(dn_rows),
-                                                       paired, expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn, tile_counts);
-        QWC_CUDA_TRY(cudaGetLastError());
+        QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_sort_kernel, dim3(grid), dim3(kSortCta), 0, st, idx, static_cast<int>(pairs),
+                                    static_cast<int>(e), static_cast<int>(k), moe_tile_rows(pairs, e), static_cast<int>(gu_rows),
+                                    static_cast<int>(dn_rows), paired, expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn,
+                                    tile_counts));
         return QWC_OK;
     }
     // larger lists: three passes, one warp per expert.
@@ -742,10 +787,9 @@ int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t l
     if (!x_f16 || !sorted_tok || !expert_off || !xs_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
     const int vec = reinterpret_cast<uintptr_t>(x_f16) % 16 == 0 && ldx % 8 == 0;
     if (reinterpret_cast<uintptr_t>(xs_f16) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "xs must be 16-byte aligned");
-    qwc_moe_gather_kernel<<<grid_for(hal, pairs * (h / 32), 64, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), sorted_tok, expert_off, static_cast<int>(e), !x_is_rotated, vec,
-        static_cast<__half*>(xs_f16));
-    QWC_CUDA_TRY(cudaGetLastError());
+    QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_gather_kernel, dim3(grid_for(hal, pairs * (h / 32), 64, 16)), dim3(256), 0,
+                                static_cast<cudaStream_t>(stream), static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), sorted_tok,
+                                expert_off, static_cast<int>(e), static_cast<int>(!x_is_rotated), vec, static_cast<__half*>(xs_f16)));
     return QWC_OK;
 }
 
@@ -762,8 +806,9 @@ int qwc_moe_grouped_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view*
     if (!xs_f16 || !tiles || !tile_count || !y) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
     if (y_dtype != QWC_F16 && y_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "y dtype must be f16 or f32");
     // The grouped door uses the tensor-core kernel only: K % 128 == 0, HQ4_G32_M5 or HQ8_G32, 16-byte aligned bank.
+    if (int rc0 = qwc_check_view(bank)) return rc0;
     if (!qwc_gemm_tc_supported(hal, bank, 17, QWC_EPI_NONE))
-        return qwc_fail(QWC_ERR_BLOCKED, "grouped expert GEMM needs an HQ4_G32_M5 / HQ8_G32 bank with k %% 128 == 0, 16-byte aligned");
+        return qwc_fail(QWC_ERR_BLOCKED, "grouped expert GEMM needs an HQ4_G32_M5 / HQ8_G32 bank with k %% 128 == 0 or an HQ4_G64 bank with k %% 256 == 0, 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(xs_f16) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "xs must be 16-byte aligned");
     return qwc_launch_gemm_tc_grouped(hal, static_cast<cudaStream_t>(stream), bank, xs_f16, pairs, tiles, tile_count, max_tiles, y,
                                       y_dtype, ldy, x_tile_rows, epilogue);
@@ -776,34 +821,44 @@ int qwc_moe_silu_mul(qwc_hal* hal, qwc_stream stream, const void* gu_f16, int64_
     if (inter <= 0 || inter % 32 != 0) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "inter=%lld must be a positive multiple of 32", (long long)inter);
     if (rows <= 0) return QWC_OK;
     if (!gu_f16 || !h_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
-    qwc_moe_silu_mul_kernel<<<grid_for(hal, rows * (inter / 32), 8, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(gu_f16), nullptr, rows, static_cast<int>(inter), rotate, static_cast<__half*>(h_f16));
-    QWC_CUDA_TRY(cudaGetLastError());
+    QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_silu_mul_kernel, dim3(grid_for(hal, rows * (inter / 32), 8, 16)), dim3(256), 0,
+                                static_cast<cudaStream_t>(stream), static_cast<const __half*>(gu_f16), static_cast<const int32_t*>(nullptr),
+                                rows, static_cast<int>(inter), static_cast<int>(rotate), static_cast<__half*>(h_f16)));
+    return QWC_OK;
+}
+
+int qwc_moe_combine_shared(qwc_hal* hal, qwc_stream stream, const void* dn, int32_t dn_dtype, const int32_t* inv_perm,
+                            const float* wts, const float* shared_f32, const float* gate_f32, int64_t t, int64_t k, int64_t h,
+                            void* out, int32_t out_dtype) {
+    qwc_clear_error();
+    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
+    if (h <= 0 || h % 2 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "hidden must be even");
+    if ((dn_dtype != QWC_F16 && dn_dtype != QWC_F32) || (out_dtype != QWC_F16 && out_dtype != QWC_F32))
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "dtypes must be f16 or f32");
+    if ((shared_f32 == nullptr) != (gate_f32 == nullptr)) return qwc_fail(QWC_ERR_BAD_SHAPE, "shared rows and their gate come together");
+    if (t <= 0) return QWC_OK;
+    if (!dn || !inv_perm || !wts || !out) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int ti = static_cast<int>(t), ki = static_cast<int>(k), hi = static_cast<int>(h);
+    const int wide = dn_dtype == QWC_F16 ? 8 : 4;   // elements of a 16-byte load
+    const bool vec = h % wide == 0 && reinterpret_cast<uintptr_t>(dn) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0;
+    const int grid = grid_for(hal, t * (h / (vec ? wide : 2)), 256, 16);
+    cudaError_t e;
+#define QWC_COMBINE(DT, OT, V)                                                                                                  \
+    e = qwc_launch_pdl(qwc_moe_combine_kernel<DT, OT, V>, dim3(grid), dim3(256), 0, st, static_cast<const DT*>(dn), inv_perm, wts, \
+                       shared_f32, gate_f32, ti, ki, hi, static_cast<OT*>(out))
+    if (dn_dtype == QWC_F16 && out_dtype == QWC_F32) { if (vec) QWC_COMBINE(__half, float, 8); else QWC_COMBINE(__half, float, 2); }
+    else if (dn_dtype == QWC_F16) { if (vec) QWC_COMBINE(__half, __half, 8); else QWC_COMBINE(__half, __half, 2); }
+    else if (out_dtype == QWC_F32) { if (vec) QWC_COMBINE(float, float, 4); else QWC_COMBINE(float, float, 2); }
+    else { if (vec) QWC_COMBINE(float, __half, 4); else QWC_COMBINE(float, __half, 2); }
+#undef QWC_COMBINE
+    QWC_CUDA_TRY(e);
     return QWC_OK;
 }
 
 int qwc_moe_combine(qwc_hal* hal, qwc_stream stream, const void* dn, int32_t dn_dtype, const int32_t* inv_perm,
                     const float* wts, int64_t t, int64_t k, int64_t h, void* out, int32_t out_dtype) {
-    qwc_clear_error();
-    if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
-    if (h <= 0 || h % 2 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "hidden must be even");
-    if (t <= 0) return QWC_OK;
-    if (!dn || !inv_perm || !wts || !out) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int grid = grid_for(hal, t * (h / 2), 256, 16);
-    const int ti = static_cast<int>(t), ki = static_cast<int>(k), hi = static_cast<int>(h);
-    if (dn_dtype == QWC_F16 && out_dtype == QWC_F32)
-        qwc_moe_combine_kernel<__half, float><<<grid, 256, 0, st>>>(static_cast<const __half*>(dn), inv_perm, wts, ti, ki, hi, static_cast<float*>(out));
-    else if (dn_dtype == QWC_F16 && out_dtype == QWC_F16)
-        qwc_moe_combine_kernel<__half, __half><<<grid, 256, 0, st>>>(static_cast<const __half*>(dn), inv_perm, wts, ti, ki, hi, static_cast<__half*>(out));
-    else if (dn_dtype == QWC_F32 && out_dtype == QWC_F32)
-        qwc_moe_combine_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(dn), inv_perm, wts, ti, ki, hi, static_cast<float*>(out));
-    else if (dn_dtype == QWC_F32 && out_dtype == QWC_F16)
-        qwc_moe_combine_kernel<float, __half><<<grid, 256, 0, st>>>(static_cast<const float*>(dn), inv_perm, wts, ti, ki, hi, static_cast<__half*>(out));
-    else
-        return qwc_fail(QWC_ERR_BAD_SHAPE, "dtypes must be f16 or f32");
-    QWC_CUDA_TRY(cudaGetLastError());
-    return QWC_OK;
+    return qwc_moe_combine_shared(hal, stream, dn, dn_dtype, inv_perm, wts, nullptr, nullptr, t, k, h, out, out_dtype);
 }
 
 size_t qwc_moe_scratch_bytes(int64_t t, int64_t e, int64_t k, int64_t h, int64_t inter) {
@@ -819,6 +874,9 @@ int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
     if (!bank_gu || !bank_dn) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "expert banks are null");
     const int64_t h = bank_gu->k;
+    if (e <= 0 || e > 512) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "experts=%lld must be in 1..512", (long long)e);
+    if (k <= 0 || k > 16 || k > e) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "top-k=%lld must be in 1..16 and <= experts", (long long)k);
+    if (inter <= 0 || h <= 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "empty expert banks");
     // Bank geometry (QWMoEOperator.Weights, QWMoEOperator.swift:10-130): gate||up is [e * 2 * inter, h], down is [e * h, inter].
     if (bank_gu->n != e * 2 * inter) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "gate/up bank has %lld rows, expected e * 2 * inter = %lld", (long long)bank_gu->n, (long long)(e * 2 * inter));
     if (bank_dn->n != e * h || bank_dn->k != inter) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "down bank must be [e * hidden, inter] = [%lld, %lld]", (long long)(e * h), (long long)inter);
@@ -828,6 +886,14 @@ int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank
     const MoeScratch L = moe_layout(t, e, k, h, inter);
     if (!scratch || scratch_bytes < L.total) return qwc_fail(QWC_ERR_BAD_SHAPE, "scratch of %zu bytes needed (qwc_moe_scratch_bytes), got %zu", L.total, scratch_bytes);
     if (reinterpret_cast<uintptr_t>(scratch) % 256 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "scratch must be 256-byte aligned");
+    // Every refusal comes before the first launch (QWGemm.swift:216-217; Tests/QWGEMMTests/QWGEMMTests.swift:221-248): the
+    // checks of the doors called below are made here, for the path this call will take.
+    if (int rc0 = qwc_check_view(bank_gu)) return rc0;
+    if (int rc0 = qwc_check_view(bank_dn)) return rc0;
+    if (h % 32 != 0 || inter % 32 != 0) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "hidden and inter must be multiples of 32");
+    if (ldx < h) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldx < hidden");
+    if (out_dtype != QWC_F16 && out_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "out dtype must be f16 or f32");
+    if (t * k >= (int64_t(1) << 30)) return qwc_fail(QWC_ERR_BAD_SHAPE, "too many pairs");
     uint8_t* sc = static_cast<uint8_t*>(scratch);
     const int64_t pairs = t * k;
     int32_t* idx = reinterpret_cast<int32_t*>(sc + L.idx);
@@ -840,14 +906,16 @@ int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank
     qwc_moe_tile* tiles_dn = reinterpret_cast<qwc_moe_tile*>(sc + L.tiles_dn);
     int32_t* tile_counts = reinterpret_cast<int32_t*>(sc + L.tile_counts);
     int rc;
-    if ((rc = qwc_moe_route(hal, stream, logits, t, e, k, norm_topk, routed_scale, idx, wts))) return rc;
     // ---- decode / verify sizes: per-expert streaming GEMVs over a device-side segment list
     const int64_t rb_gu = (h / bank_gu->group) * qwc_block_bytes(bank_gu->kind, bank_gu->bits, bank_gu->group);
     const int64_t rb_dn = (inter / bank_dn->group) * qwc_block_bytes(bank_dn->kind, bank_dn->bits, bank_dn->group);
-    static const bool no_decode_path = getenv("QWC_MOE_NO_DECODE_PATH") != nullptr;
-    if (t <= 8 && !no_decode_path && inter % 32 == 0 && rb_gu % 16 == 0 && rb_dn % 16 == 0 && 8 * h * 2 <= 112 * 1024 &&
-        8 * inter * 2 <= 112 * 1024 && reinterpret_cast<uintptr_t>(bank_gu->blocks) % 16 == 0 &&
-        reinterpret_cast<uintptr_t>(bank_dn->blocks) % 16 == 0) {
+    const bool no_decode_path = tune_env("QWC_MOE_NO_DECODE_PATH", 0) != 0;
+    bool decode_path = t <= 8 && !no_decode_path && rb_gu % 16 == 0 && rb_dn % 16 == 0 && 8 * h * 2 <= 112 * 1024 &&
+                       8 * inter * 2 <= 112 * 1024 && reinterpret_cast<uintptr_t>(bank_gu->blocks) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(bank_dn->blocks) % 16 == 0;
+    int cols_gu = 0, cols_dn = 0;
+    int64_t max_gu = 0, max_dn = 0;
+    if (decode_path) {
         // as many column blocks per expert as keep one wave of CTAs busy when every pair names a different expert
         // (whole 32-column blocks; the floors keep the lists inside the tile-list regions of the scratch)
         const int64_t act = pairs < e ? pairs : e;
@@ -857,26 +925,31 @@ int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank
             if (c < floor_cols) c = floor_cols;
             return static_cast<int>(c);
         };
-        const int cols_gu = pick_cols(inter, 64), cols_dn = pick_cols(h, 128);
-        const int64_t active_max = pairs < e ? pairs : e;
-        const int64_t max_gu = active_max * ((inter + cols_gu - 1) / cols_gu), max_dn = active_max * ((h + cols_dn - 1) / cols_dn);
-        if (static_cast<size_t>(max_gu) * sizeof(MoeSeg) <= static_cast<size_t>(qwc_moe_max_tiles(pairs, e, 2 * inter)) * sizeof(qwc_moe_tile) &&
-            static_cast<size_t>(max_dn) * sizeof(MoeSeg) <= static_cast<size_t>(qwc_moe_max_tiles(pairs, e, h)) * sizeof(qwc_moe_tile)) {
-            cudaStream_t st = static_cast<cudaStream_t>(stream);
-            if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h,
-                                          QWC_EPI_NONE, nullptr, nullptr, tile_counts))) return rc;
-            MoeSeg* segs_gu = reinterpret_cast<MoeSeg*>(tiles_gu);
-            MoeSeg* segs_dn = reinterpret_cast<MoeSeg*>(tiles_dn);
-            qwc_moe_decode_plan_kernel<<<1, 512, 0, st>>>(expert_off, static_cast<int>(e), static_cast<int>(inter), static_cast<int>(h),
-                                                          cols_gu, cols_dn, segs_gu, segs_dn, tile_counts + 2);
-            QWC_CUDA_TRY(cudaGetLastError());
-            if ((rc = qwc_moe_gather(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs))) return rc;
-            if ((rc = qwc_launch_gemv_segments(hal, st, bank_gu, sc + L.xs, h, sc + L.hs, QWC_F16, inter, QWC_EPI_SILU_PAIR_FWHT, inter,
-                                               cols_gu, segs_gu, tile_counts + 2, max_gu))) return rc;
-            if ((rc = qwc_launch_gemv_segments(hal, st, bank_dn, sc + L.hs, inter, sc + L.dn, QWC_F16, h, QWC_EPI_NONE, h, cols_dn,
-                                               segs_dn, tile_counts + 3, max_dn))) return rc;
-            return qwc_moe_combine(hal, stream, sc + L.dn, QWC_F16, inv_perm, wts, t, k, h, out, out_dtype);
-        }
+        cols_gu = pick_cols(inter, 64);
+        cols_dn = pick_cols(h, 128);
+        max_gu = act * ((inter + cols_gu - 1) / cols_gu);
+        max_dn = act * ((h + cols_dn - 1) / cols_dn);
+        decode_path = static_cast<size_t>(max_gu) * sizeof(MoeSeg) <= static_cast<size_t>(qwc_moe_max_tiles(pairs, e, 2 * inter)) * sizeof(qwc_moe_tile) &&
+                      static_cast<size_t>(max_dn) * sizeof(MoeSeg) <= static_cast<size_t>(qwc_moe_max_tiles(pairs, e, h)) * sizeof(qwc_moe_tile);
+    }
+    if (!decode_path && (!qwc_gemm_tc_supported(hal, bank_gu, 17, QWC_EPI_NONE) || !qwc_gemm_tc_supported(hal, bank_dn, 17, QWC_EPI_NONE)))
+        return qwc_fail(QWC_ERR_BLOCKED, "the grouped expert GEMMs need HQ4_G32_M5 / HQ8_G32 banks with k %% 128 == 0 or HQ4_G64 banks with k %% 256 == 0, "
+                                         "16-byte aligned");
+    if ((rc = qwc_moe_route(hal, stream, logits, t, e, k, norm_topk, routed_scale, idx, wts))) return rc;
+    if (decode_path) {
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h,
+                                      QWC_EPI_NONE, nullptr, nullptr, tile_counts))) return rc;
+        MoeSeg* segs_gu = reinterpret_cast<MoeSeg*>(tiles_gu);
+        MoeSeg* segs_dn = reinterpret_cast<MoeSeg*>(tiles_dn);
+        QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_decode_plan_kernel, dim3(1), dim3(512), 0, st, expert_off, static_cast<int>(e),
+                                    static_cast<int>(inter), static_cast<int>(h), cols_gu, cols_dn, segs_gu, segs_dn, tile_counts + 2));
+        if ((rc = qwc_moe_gather(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs))) return rc;
+        if ((rc = qwc_launch_gemv_segments(hal, st, bank_gu, sc + L.xs, h, sc + L.hs, QWC_F16, inter, QWC_EPI_SILU_PAIR_FWHT, inter,
+                                           cols_gu, segs_gu, tile_counts + 2, max_gu))) return rc;
+        if ((rc = qwc_launch_gemv_segments(hal, st, bank_dn, sc + L.hs, inter, sc + L.dn, QWC_F16, h, QWC_EPI_NONE, h, cols_dn,
+                                           segs_dn, tile_counts + 3, max_dn))) return rc;
+        return qwc_moe_combine(hal, stream, sc + L.dn, QWC_F16, inv_perm, wts, t, k, h, out, out_dtype);
     }
     // SwiGLU + FWHT run in the gate/up GEMM's epilogue when the tiles can pair 64 gate rows with their up rows
     const int32_t gu_epi = inter % 64 == 0 ? QWC_EPI_SILU_PAIR_FWHT : QWC_EPI_NONE;

@@ -69,24 +69,8 @@ int qwc_gemm_static_scratch(qwc_hal* hal, qwc_stream stream, const qwc_weight_vi
                             int64_t ldx, void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated) {
     qwc_clear_error();
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
-    if (!w || !w->blocks || w->n <= 0 || w->k <= 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "weight view is null or empty");
-    if (qwc_fmt_of(*w) == FMT_UNSUPPORTED || w->k % w->group != 0)
-        return qwc_fail(QWC_ERR_BAD_WEIGHTS, "unsupported container or k not a multiple of the group");
-    if (reinterpret_cast<uintptr_t>(w->blocks) % 4 != 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "blocks must be 4-byte aligned");
     if (m < 0 || m > 16) return qwc_fail(QWC_ERR_BAD_SHAPE, "this door serves 0..16 tokens, got m=%lld", (long long)m);
-    if (m == 0) return QWC_OK;
-    if (!x_f16 || !y) return qwc_fail(QWC_ERR_BAD_SHAPE, "x or y is null");
-    if (y_dtype != QWC_F16 && y_dtype != QWC_F32) return qwc_fail(QWC_ERR_BAD_SHAPE, "y dtype must be f16 or f32");
-    if (epilogue < QWC_EPI_NONE || epilogue > QWC_EPI_SILU_PAIR_FWHT) return qwc_fail(QWC_ERR_BAD_SHAPE, "unknown epilogue %d", epilogue);
-    int64_t n_out = w->n;
-    if (epilogue != QWC_EPI_NONE) {
-        if (w->n % 2 != 0) return qwc_fail(QWC_ERR_BAD_WEIGHTS, "silu-pair needs an even row count, got n=%lld", (long long)w->n);
-        n_out = w->n / 2;
-        if (epilogue == QWC_EPI_SILU_PAIR_FWHT && n_out % 32 != 0)
-            return qwc_fail(QWC_ERR_BAD_GEOMETRY, "fused FWHT needs n/2 %% 32 == 0, got %lld", (long long)n_out);
-    }
-    if (ldx < w->k) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldx=%lld < k=%lld", (long long)ldx, (long long)w->k);
-    if (ldy < n_out) return qwc_fail(QWC_ERR_BAD_SHAPE, "ldy=%lld < output width %lld", (long long)ldy, (long long)n_out);
+    if (int rc = qwc_check_view(w)) return rc;
     const size_t need = qwc_gemv_workspace_bytes(w, m);
     if (need > kScratchBytes)
         return qwc_fail(QWC_ERR_BAD_SHAPE,
@@ -95,6 +79,9 @@ int qwc_gemm_static_scratch(qwc_hal* hal, qwc_stream stream, const qwc_weight_vi
                         need, kScratchBytes);
     void* scratch = nullptr;
     if (int rc = scratch_address(hal, &scratch)) return rc;
+    // the same argument checks as qwc_gemm's streaming path, with the built-in array as the workspace
+    if (int rc = qwc_gemm_args_check_stream(hal, w, x_f16, m, ldx, y, y_dtype, ldy, epilogue, x_is_rotated, scratch, kScratchBytes)) return rc;
+    if (m == 0) return QWC_OK;
     return qwc_launch_gemv(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, epilogue, x_is_rotated,
                            scratch, kScratchBytes);
 }

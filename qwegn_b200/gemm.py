@@ -111,6 +111,48 @@ def _stream_ptr(stream: Optional[torch.cuda.Stream]) -> ctypes.c_void_p:
     return ctypes.c_void_p(s.cuda_stream)
 
 
+def check_matmul_tensors(hal: "QWHal", w: "QWWeightView", x: torch.Tensor, y: torch.Tensor, epi: int, x_dtype=torch.float16):
+    """The tensor checks every matmul door makes before it hands raw pointers to the C ABI (the C side sees only
+    pointers and strides, so a CPU tensor, a tensor on another device or a short y must be refused here): returns
+    (x2, y2, m, n_out, ldx, ldy)."""
+    if x.dtype != x_dtype or not x.is_cuda:
+        raise QWGemmError(3, f"x must be a CUDA {x_dtype} tensor")
+    if y.dtype not in (torch.float16, torch.float32) or not y.is_cuda:
+        raise QWGemmError(3, "y must be a CUDA float16/float32 tensor")
+    if x.device != hal.device or y.device != hal.device or w.bank.device != hal.device:
+        raise QWGemmError(3, f"x, y and the weight bank must live on {hal.device}")
+    if x.dim() not in (1, 2) or y.dim() not in (1, 2):
+        raise QWGemmError(3, "x and y must be vectors or matrices")
+    x2 = x if x.dim() == 2 else x.view(1, -1)
+    y2 = y if y.dim() == 2 else y.view(1, -1)
+    if x2.stride(1) != 1 or y2.stride(1) != 1:
+        raise QWGemmError(3, "x and y rows must be contiguous")
+    m = x2.shape[0]
+    if x2.shape[1] != w.k:
+        raise QWGemmError(3, f"x has {x2.shape[1]} columns, the bank has k={w.k}")
+    n_out = w.n if epi == EPI_NONE else w.n // 2
+    if y2.shape[0] != m or y2.shape[1] != n_out:
+        raise QWGemmError(3, f"y is {tuple(y2.shape)}, expected ({m}, {n_out})")
+    ldx = x2.stride(0) if m > 1 else max(x2.stride(0), w.k)
+    ldy = y2.stride(0) if m > 1 else max(y2.stride(0), n_out)
+    if m > 1 and (ldx < w.k or ldy < n_out):
+        raise QWGemmError(3, "row strides smaller than the row length (overlapping rows)")
+    return x2, y2, m, n_out, ldx, ldy
+
+
+def check_device_tensor(hal: "QWHal", t: torch.Tensor, name: str, dtype, numel: Optional[int] = None, contiguous: bool = True):
+    """One buffer of an MoE door: right device, dtype, layout and (when given) at least `numel` elements."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.device != hal.device:
+        raise QWGemmError(3, f"{name} must be a CUDA tensor on {hal.device}")
+    dts = dtype if isinstance(dtype, (tuple, list)) else (dtype,)
+    if t.dtype not in dts:
+        raise QWGemmError(3, f"{name} must be {' or '.join(str(d) for d in dts)}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise QWGemmError(3, f"{name} must be contiguous")
+    if numel is not None and t.numel() < numel:
+        raise QWGemmError(3, f"{name} holds {t.numel()} elements, {numel} needed")
+
+
 class QWWeightView:
     """QWWeightView (QWWeightView.swift:9-152): one bank of packed blocks resident in device memory."""
 
@@ -171,26 +213,13 @@ class QWGemm:
                x_is_rotated: bool = False, stream: Optional[torch.cuda.Stream] = None,
                workspace: Optional[torch.Tensor] = None) -> None:
         """y[m, n_out] = epilogue(rot(x) . W_rot^T).  x f16 [m, k] (or [k]); y f16/f32 [m, n_out] (or [n_out])."""
-        if x.dtype != torch.float16 or not x.is_cuda:
-            raise QWGemmError(3, "x must be a CUDA float16 tensor")
-        if y.dtype not in (torch.float16, torch.float32) or not y.is_cuda:
-            raise QWGemmError(3, "y must be a CUDA float16/float32 tensor")
-        x2 = x if x.dim() == 2 else x.view(1, -1)
-        y2 = y if y.dim() == 2 else y.view(1, -1)
-        if x2.stride(1) != 1 or y2.stride(1) != 1:
-            raise QWGemmError(3, "x and y rows must be contiguous")
-        m = x2.shape[0]
-        if x2.shape[1] != w.k:
-            raise QWGemmError(3, f"x has {x2.shape[1]} columns, the bank has k={w.k}")
-        n_out = w.n if epi == EPI_NONE else w.n // 2
-        if y2.shape[0] != m or y2.shape[1] != n_out:
-            raise QWGemmError(3, f"y is {tuple(y2.shape)}, expected ({m}, {n_out})")
-        ws_ptr, ws_bytes = (None, 0) if workspace is None else (workspace.data_ptr(), workspace.numel() * workspace.element_size())
-        _check(_lib.load().qwc_gemm(hal.handle, _stream_ptr(stream), ctypes.byref(w.c), x2.data_ptr(), m,
-                                    x2.stride(0) if m > 1 else max(x2.stride(0), w.k), y2.data_ptr(),
-                                    F16 if y.dtype == torch.float16 else F32,
-                                    y2.stride(0) if m > 1 else max(y2.stride(0), n_out), epi, int(x_is_rotated),
-                                    ws_ptr, ws_bytes))
+        x2, y2, m, n_out, ldx, ldy = check_matmul_tensors(hal, w, x, y, epi)
+        ws_ptr, ws_bytes = None, 0
+        if workspace is not None:
+            check_device_tensor(hal, workspace, "workspace", workspace.dtype)
+            ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+        _check(_lib.load().qwc_gemm(hal.handle, _stream_ptr(stream), ctypes.byref(w.c), x2.data_ptr(), m, ldx, y2.data_ptr(),
+                                    F16 if y.dtype == torch.float16 else F32, ldy, epi, int(x_is_rotated), ws_ptr, ws_bytes))
 
     # The reference's f16-store door (QWGemm.swift:137) is the same call with an f16 output tensor.
     encodeH16 = encode

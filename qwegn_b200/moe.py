@@ -10,7 +10,7 @@ import torch
 
 from . import _lib
 from ._lib import F16, F32, WeightViewC
-from .gemm import QWGemmError, QWHal, QWWeightView, _check, _stream_ptr
+from .gemm import QWGemmError, QWHal, QWWeightView, _check, _stream_ptr, check_device_tensor
 
 _i32, _i64, _vp, _sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
 _WV = ctypes.POINTER(WeightViewC)
@@ -29,6 +29,7 @@ _lib.register("qwc_moe_grouped_gemm", ctypes.c_int, [_vp, _vp, _WV, _vp, _i64, _
 _lib.register("qwc_moe_tile_rows", _i32, [_i64, _i64])
 _lib.register("qwc_moe_silu_mul", ctypes.c_int, [_vp, _vp, _vp, _i64, _i64, _i32, _vp])
 _lib.register("qwc_moe_combine", ctypes.c_int, [_vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _vp, _i32])
+_lib.register("qwc_moe_combine_shared", ctypes.c_int, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32])
 _lib.register("qwc_moe_forward", ctypes.c_int, [_vp, _vp, _WV, _WV, _i64, _i64, _vp, _i64, _i64, _i32, _vp, _i64, _i32,
                                                 ctypes.c_float, _vp, _i32, _vp, _sz])
 _lib.register("qwc_moe_scratch_bytes", _sz, [_i64, _i64, _i64, _i64, _i64])
@@ -58,7 +59,11 @@ class QWMoEOperator:
     def encodeResident(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor,
                        x_is_rotated: bool = False, stream: Optional[torch.cuda.Stream] = None) -> None:
         """x f16 [T, H]; logits f32 [T, E]; out f16/f32 [T, H]; scratch uint8 of scratchBytes(T) bytes."""
-        if x.dtype != torch.float16 or x.dim() != 2 or x.stride(1) != 1:
+        check_device_tensor(self.hal, x, "x", torch.float16, contiguous=False)
+        check_device_tensor(self.hal, logits, "logits", torch.float32)
+        check_device_tensor(self.hal, out, "out", (torch.float16, torch.float32))
+        check_device_tensor(self.hal, scratch, "scratch", torch.uint8, numel=self.scratchBytes(x.shape[0]) if x.dim() == 2 else None)
+        if x.dim() != 2 or x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) < x.shape[1]):
             raise QWGemmError(3, "x must be a float16 [T, H] tensor with contiguous rows")
         if logits.dtype != torch.float32 or not logits.is_contiguous() or logits.shape != (x.shape[0], self.experts):
             raise QWGemmError(3, "logits must be a contiguous float32 [T, E] tensor")
@@ -94,7 +99,12 @@ class QWGemmMoE:
     @staticmethod
     def encodeFnMoeRoute(hal: QWHal, logits: torch.Tensor, top_k: int, idx: torch.Tensor, wts: torch.Tensor,
                          norm_topk: bool = True, routed_scale: float = 0.0, stream=None) -> None:
+        check_device_tensor(hal, logits, "logits", torch.float32)
+        if logits.dim() != 2:
+            raise QWGemmError(3, "logits must be [T, E]")
         t, e = logits.shape
+        check_device_tensor(hal, idx, "idx", torch.int32, numel=t * top_k)
+        check_device_tensor(hal, wts, "wts", torch.float32, numel=t * top_k)
         _check(_lib.load().qwc_moe_route(hal.handle, _stream_ptr(stream), logits.data_ptr(), t, e, top_k, int(norm_topk),
                                          float(routed_scale), idx.data_ptr(), wts.data_ptr()))
 
@@ -107,6 +117,9 @@ class QWGemmMoE:
                             gu_epilogue: int = 0):
         """Returns (expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn, tile_counts), all on the device.
         gu_epilogue != 0 lists paired gate/up tiles (64 gate rows + their 64 up rows) for a SwiGLU epilogue."""
+        check_device_tensor(hal, idx, "idx", torch.int32)
+        if idx.dim() != 2:
+            raise QWGemmError(3, "idx must be [T, K]")
         t, k = idx.shape
         pairs = t * k
         dev = idx.device
@@ -123,7 +136,25 @@ class QWGemmMoE:
         return off, sp, st, inv, tg, td, tc
 
     @staticmethod
-    def encodeMoECombine(hal: QWHal, dn: torch.Tensor, inv_perm: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, stream=None):
+    def encodeMoECombine(hal: QWHal, dn: torch.Tensor, inv_perm: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, stream=None,
+                         shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None):
+        """out[t] = sum_k wts[t, k] * dn[inv_perm[t, k]] (+ gate[t] * shared[t], the shared-expert term: shared f32 [T, H],
+        gate f32 [T]) -- QWGemm.encodeMoEDownReduceCombineF32 (QWGemmMoE.swift:298-332)."""
+        check_device_tensor(hal, wts, "wts", torch.float32)
+        if wts.dim() != 2 or out.dim() != 2 or dn.dim() != 2:
+            raise QWGemmError(3, "wts must be [T, K], dn [P, H], out [T, H]")
         t, k = wts.shape
-        _check(_lib.load().qwc_moe_combine(hal.handle, _stream_ptr(stream), dn.data_ptr(), _dt(dn), inv_perm.data_ptr(),
-                                           wts.data_ptr(), t, k, out.shape[1], out.data_ptr(), _dt(out)))
+        h = out.shape[1]
+        check_device_tensor(hal, out, "out", (torch.float16, torch.float32), numel=t * h)
+        check_device_tensor(hal, dn, "dn", (torch.float16, torch.float32))
+        check_device_tensor(hal, inv_perm, "inv_perm", torch.int32, numel=t * k)
+        if dn.shape[1] != h or out.shape[0] != t:
+            raise QWGemmError(3, f"dn is {tuple(dn.shape)}, out {tuple(out.shape)}: both must have the hidden width, out one row per token")
+        if (shared is None) != (gate is None):
+            raise QWGemmError(3, "shared rows and their gate come together")
+        if shared is not None:
+            check_device_tensor(hal, shared, "shared", torch.float32, numel=t * h)
+            check_device_tensor(hal, gate, "gate", torch.float32, numel=t)
+        _check(_lib.load().qwc_moe_combine_shared(hal.handle, _stream_ptr(stream), dn.data_ptr(), _dt(dn), inv_perm.data_ptr(),
+                                                  wts.data_ptr(), None if shared is None else shared.data_ptr(),
+                                                  None if gate is None else gate.data_ptr(), t, k, h, out.data_ptr(), _dt(out)))

@@ -13,7 +13,7 @@ import torch
 
 from . import _lib
 from ._lib import EPI_NONE, F16, F32, WeightViewC
-from .gemm import QWGemmError, QWHal, QWWeightView, _check, _stream_ptr
+from .gemm import QWGemmError, QWHal, QWWeightView, _check, _stream_ptr, check_matmul_tensors
 
 _i32, _i64, _vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
 _lib.register("qwc_gemm_static_scratch", ctypes.c_int,
@@ -28,12 +28,7 @@ def static_scratch_capacity() -> int:
 def encode_static_scratch(hal: QWHal, w: QWWeightView, x: torch.Tensor, y: torch.Tensor, epi: int = EPI_NONE,
                           x_is_rotated: bool = False, stream: Optional[torch.cuda.Stream] = None) -> None:
     """Same contract as QWGemm.encode for up to 16 tokens, without a workspace argument."""
-    if x.dtype != torch.float16 or y.dtype not in (torch.float16, torch.float32):
-        raise QWGemmError(3, "x must be float16 and y float16/float32")
-    x2 = x if x.dim() == 2 else x.view(1, -1)
-    y2 = y if y.dim() == 2 else y.view(1, -1)
-    m = x2.shape[0]
+    x2, y2, m, _, ldx, ldy = check_matmul_tensors(hal, w, x, y, epi)
     _check(_lib.load().qwc_gemm_static_scratch(
-        hal.handle, _stream_ptr(stream), ctypes.byref(w.c), x2.data_ptr(), m, x2.stride(0) if m > 1 else max(x2.stride(0), w.k),
-        y2.data_ptr(), F16 if y.dtype == torch.float16 else F32, y2.stride(0) if m > 1 else max(y2.stride(0), y2.shape[1]),
-        epi, int(x_is_rotated)))
+        hal.handle, _stream_ptr(stream), ctypes.byref(w.c), x2.data_ptr(), m, ldx, y2.data_ptr(),
+        F16 if y.dtype == torch.float16 else F32, ldy, epi, int(x_is_rotated)))

@@ -38,10 +38,8 @@ def test_every_declared_symbol_is_exported(lib):
 
 def test_binding_covers_the_header(lib):
     from qwegn_b200 import _lib
-    try:
-        import qwegn_b200.moe  # noqa: F401  (registers the MoE entry points)
-    except ImportError:
-        pass
+    import qwegn_b200.moe  # noqa: F401  (registers the MoE entry points)
+    import qwegn_b200.parallel  # noqa: F401  (registers the fused all-reduce and the expert-parallel entry points)
     assert set(_declared_symbols()) <= set(_lib.SIGNATURES), sorted(set(_declared_symbols()) - set(_lib.SIGNATURES))
 
 
@@ -99,3 +97,43 @@ def test_product_does_not_import_the_oracle():
                 text = open(os.path.join(dirpath, f)).read()
                 for needle in ("import oracle", "from oracle", "qw_oracle", "libqworacle", "oracle/"):
                     assert needle not in text, f"{f} reaches into the oracle ({needle})"
+
+
+class _FakeHal:
+    """Stands in for QWHal where no GPU exists: the tensor checks only need the device the context lives on."""
+    def __init__(self):
+        import torch
+        self.device = torch.device("cuda", 0)
+
+
+class _FakeView:
+    def __init__(self, n, k):
+        import torch
+        self.n, self.k = n, k
+        self.bank = type("B", (), {"device": torch.device("cuda", 0)})()
+
+
+def test_matmul_doors_refuse_bad_tensors_before_any_call():
+    # The C side sees raw pointers and strides only, so a CPU tensor, a short y or overlapping rows must be refused
+    # by the Python doors before the C ABI is reached (QWGemm.encode, the scratch-free door and the MoE doors share
+    # these checks).  No GPU is needed to see the refusals: they come before any launch.
+    import torch
+    import qwegn_b200 as q
+    from qwegn_b200.gemm import check_device_tensor, check_matmul_tensors
+    from qwegn_b200 import noalloc
+    hal, w = _FakeHal(), _FakeView(64, 128)
+    x = torch.zeros((2, 128), dtype=torch.float16)
+    y = torch.zeros((2, 64), dtype=torch.float32)
+    for fn in (lambda: check_matmul_tensors(hal, w, x, y, 0),                      # CPU tensors
+               lambda: q.QWGemm.encode(hal, w, x, y),
+               lambda: noalloc.encode_static_scratch(hal, w, x, y)):
+        with pytest.raises(q.QWGemmError) as e:
+            fn()
+        assert e.value.case == "badShape"
+    with pytest.raises(q.QWGemmError):
+        check_device_tensor(hal, x, "x", torch.float16)
+    # shape logic (independent of the device check): reproduce it on meta tensors that claim to be on the GPU
+    xm = torch.empty((2, 128), dtype=torch.float16, device="meta")
+    assert not xm.is_cuda   # meta tensors are refused like CPU tensors
+    with pytest.raises(q.QWGemmError):
+        check_matmul_tensors(hal, w, xm, torch.empty((2, 64), dtype=torch.float32, device="meta"), 0)

@@ -80,7 +80,9 @@ def test_group_pairs_matches_the_oracle(hal, oracle, t, e, k):
     # tile plan: every expert's rows are covered exactly once per 128-row weight tile
     counts = tc.cpu().numpy()
     tiles = tg.cpu().numpy()[: counts[0]]
-    xt = 192
+    from qwegn_b200 import _lib
+    xt = int(_lib.load().qwc_moe_tile_rows(t * k, e))
+    assert xt in (128, 192)
     assert counts[0] == sum(-(-int(c) // xt) for c in np.diff(roff)) * 8
     cover = np.zeros(valid, dtype=np.int32)
     for w0, wr, x0, xr, y0, ex, _, _ in tiles:
@@ -95,11 +97,14 @@ def test_group_pairs_matches_the_oracle(hal, oracle, t, e, k):
 # (T <= 8, QWGemmMoE.swift:117-199: the grouped path serves them here), all with SwiGLU + FWHT fused into the gate/up epilogue (inter % 128 == 0
 # for the tensor path implies inter % 64 == 0; the unfused chain is covered door by door below)
 @pytest.mark.parametrize("cfg", [(64, 8, 2, 256, 128), (300, 32, 4, 512, 256), (40, 16, 8, 128, 128), (1, 32, 8, 256, 128),
-                                 (8, 64, 4, 256, 128), (5, 16, 2, 128, 128)])
-@pytest.mark.parametrize("name", ["HQ4_G32", "HQ8_G32"])
+                                 (8, 64, 4, 256, 128), (5, 16, 2, 128, 128), (17, 8, 2, 512, 256), (64, 4, 2, 256, 256),
+                                 (700, 4, 2, 256, 256), (8, 16, 4, 256, 256)])
+@pytest.mark.parametrize("name", ["HQ4_G32", "HQ8_G32", "HQ4_G64"])
 def test_moe_forward_vs_oracle(hal, oracle, cfg, name):
     import qwegn_b200 as q
     t, e, k, hidden, inter = cfg
+    if name == "HQ4_G64" and (hidden % 256 or inter % 256):
+        pytest.skip("HQ4_G64 expert banks need K % 256 == 0 (refusal covered by test_moe_forward_refuses_before_any_launch)")
     fmt = oracle.FORMATS[name]
     rng = np.random.default_rng(sum(cfg))
     gu, dn = _expert_banks(oracle, fmt, e, hidden, inter, rng)
@@ -188,3 +193,56 @@ def test_moe_forward_refusals(hal, oracle):
         bad.encodeResident(x, torch.zeros((3, 5), dtype=torch.float32, device="cuda"), out,
                            torch.empty(bad.scratchBytes(3), dtype=torch.uint8, device="cuda"))
     assert e.value.case == "badWeights"
+
+
+def test_moe_forward_refuses_before_any_launch(hal, oracle):
+    # The reference's rule (Tests/QWGEMMTests/QWGEMMTests.swift:221-248): a refused call leaves every buffer as it was.
+    # An HQ4_G64 down bank with K = 128 has no grouped kernel (K % 256 != 0): the call must be refused before the route,
+    # sort and gather kernels run, so out and scratch keep their fill.
+    import qwegn_b200 as q
+    t, e, k, hidden, inter = 64, 4, 2, 256, 128
+    rng = np.random.default_rng(3)
+    fmt = oracle.FORMATS["HQ4_G64"]
+    gu, dn = _expert_banks(oracle, fmt, e, hidden, inter, rng)
+    cont = q.CONTAINERS["HQ4_G64"]
+    op = q.QWMoEOperator(hal, q.QWWeightView(torch.from_numpy(gu.reshape(-1)).cuda(), e * 2 * inter, hidden, cont),
+                         q.QWWeightView(torch.from_numpy(dn.reshape(-1)).cuda(), e * hidden, inter, cont), e, inter, k)
+    scratch = torch.full((op.scratchBytes(t),), 0xAB, dtype=torch.uint8, device="cuda")
+    out = torch.full((t, hidden), 7.0, dtype=torch.float32, device="cuda")
+    x = torch.from_numpy(rng.standard_normal((t, hidden)).astype(np.float16)).cuda()
+    lg = torch.from_numpy(rng.standard_normal((t, e)).astype(np.float32)).cuda()
+    with pytest.raises(q.QWGemmError) as err:
+        op.encodeResident(x, lg, out, scratch)
+    assert err.value.case == "f3Blocked"
+    torch.cuda.synchronize()
+    assert bool((scratch == 0xAB).all()) and bool((out == 7.0).all())
+
+
+def test_combine_with_shared_expert_term(hal, oracle):
+    # out[t] = sum_k w[t, k] * dn[inv_perm[t, k]] + gate[t] * shared[t]  (qwg_moe_down_reduce_combine_f32,
+    # Sources/QWMetal/gemm/qwgemm_moe_nax_f16.metal:7-126), odd and vector-friendly widths, f16 and f32 rows.
+    import qwegn_b200 as q
+    rng = np.random.default_rng(9)
+    for t, k, h in ((5, 2, 16), (33, 8, 256), (7, 3, 50)):
+        pairs = t * k
+        inv = rng.permutation(pairs).astype(np.int32)
+        inv[rng.integers(0, pairs, 3)] = -1
+        wts = rng.random((t, k)).astype(np.float32)
+        dn = rng.standard_normal((pairs, h)).astype(np.float32)
+        shared = rng.standard_normal((t, h)).astype(np.float32)
+        gate = rng.random(t).astype(np.float32)
+        for dt in (torch.float16, torch.float32):
+            dnd = torch.from_numpy(dn).to(dt).cuda()
+            dnh = dnd.float().cpu().numpy()
+            ref = np.zeros((t, h), dtype=np.float64)
+            for ti in range(t):
+                for j in range(k):
+                    p = inv[ti * k + j]
+                    if p >= 0:
+                        ref[ti] += np.float64(wts[ti, j]) * dnh[p]
+            out = torch.full((t, h), float("nan"), dtype=torch.float32, device="cuda")
+            q.QWGemmMoE.encodeMoECombine(hal, dnd, torch.from_numpy(inv).cuda(), torch.from_numpy(wts).cuda(), out)
+            np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=1e-5, atol=1e-5)
+            q.QWGemmMoE.encodeMoECombine(hal, dnd, torch.from_numpy(inv).cuda(), torch.from_numpy(wts).cuda(), out,
+                                         shared=torch.from_numpy(shared).cuda(), gate=torch.from_numpy(gate).cuda())
+            np.testing.assert_allclose(out.cpu().numpy(), ref + gate[:, None].astype(np.float64) * shared, rtol=1e-5, atol=1e-5)
