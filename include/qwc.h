@@ -181,16 +181,31 @@ int qwc_gemm_static_scratch(qwc_hal* hal, qwc_stream stream, const qwc_weight_vi
                             int64_t ldx, void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated);
 size_t qwc_static_scratch_capacity(void);
 
+/* ---- peer-visible device memory (load time) ----------------------------------------------------------------------
+ * (No counterpart in the reference.)  The fused collectives below store into the other ranks' buffers directly; one
+ * process drives one GPU.  qwc_peer_alloc: a zeroed device buffer of this rank and its 64-byte handle, which the host
+ * hands to the peers by its own channel; qwc_peer_open: maps a peer's buffer from its handle (peer access is enabled on
+ * first use).  These calls allocate and synchronise: make them once, before the first encode call. */
+int qwc_peer_alloc(qwc_hal* hal, size_t bytes, void** ptr_out, void* handle_out_64);
+int qwc_peer_open(qwc_hal* hal, const void* handle_64, void** ptr_out);
+int qwc_peer_close(qwc_hal* hal, void* ptr);
+int qwc_peer_free(qwc_hal* hal, void* ptr);
+
 /* ---- tensor parallel: row-parallel matmul fused with its all-reduce ---------------------------------------------
  * (No counterpart in the reference, which runs on one device; the format decides the design: a K shard of the bank per
  * rank, f32 partial sums, one sum over the ranks.)  One kernel does both: every CTA stores its partial sums straight
  * into the inbox of every rank (ordinary peer stores over NVLink), raises a flag on every rank, waits (bounded) for the
  * flags of the matching CTAs of the other ranks and sums the world slots of its rows in rank order, so every rank ends
- * with the same bits.  The caller provides peer-mapped memory (for example torch.distributed._symmetric_memory):
- *   inbox[r]: rank r's inbox for this call, f32 [world][m][n];  flags[r]: rank r's flags for this call, u32
- *   [world][qwc_sm_count()], zero before the first call.  epoch: a value that differs from the previous two calls' (a
- *   call counter); alternate between two inbox/flag buffers from call to call so that a fast rank's next call does not
- *   overwrite data a slow rank is still summing.  Every rank of the group must make the same call (same shapes). */
+ * with the same bits.  The caller provides peer-mapped memory (qwc_peer_alloc / qwc_peer_open):
+ *   inbox[r]: rank r's inbox, f32 [world][m][n];  flags[r]: rank r's flags, u32 [world][qwc_sm_count()], zero before the
+ *   first call.  Two inbox / flag buffers are used in turn, so that a fast rank's next call does not overwrite data a
+ *   slow rank is still summing, and every call carries a number (the flag value that marks its data as complete).  Either
+ *   the host counts: epoch = a value that differs from the previous two calls' and inbox[r] / flags[r] point at the buffer
+ *   of THIS call (epoch_state = NULL); or the device counts: epoch_state points at two zero-initialised u32 words in this
+ *   rank's memory, inbox[r] / flags[r] point at the FIRST of two buffers inbox_floats / flag_words apart, and the kernel
+ *   takes call number *epoch_state + 1, picks the buffer by its parity and stores the new number when it is done -- the
+ *   form to use when calls are captured in a CUDA graph and replayed, where host values would repeat.
+ *   Every rank of the group must make the same calls (same shapes, same order). */
 typedef struct {
     int32_t rank, world;      /* 2 <= world <= 8 */
     uint32_t epoch;
@@ -199,6 +214,7 @@ typedef struct {
     void* flags[8];
     int64_t inbox_floats;     /* capacity of one inbox buffer in floats (>= world * m * n) */
     int64_t flag_words;       /* capacity of one flag buffer in words (>= world * qwc_sm_count()) */
+    void* epoch_state;        /* NULL, or this rank's device-side call counter (two u32 words, zero before the first call) */
 } qwc_allreduce_ctx;
 
 /* y[m, n] = sum over ranks of rot(x_local[m, k_local]) . W_local^T (no epilogue), m <= 8 (decode / verify), banks with
@@ -206,6 +222,58 @@ typedef struct {
 int qwc_gemm_allreduce(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w_local, const void* x_f16, int64_t m,
                        int64_t ldx, void* y, int32_t y_dtype, int64_t ldy, int32_t x_is_rotated,
                        const qwc_allreduce_ctx* ctx);
+
+/* ---- expert parallel: the MoE block with its token exchange over peer memory ------------------------------------
+ * (No counterpart in the reference, which runs on one device.  The exchange sits where the reference's own stages sit:
+ * the pair sort, Sources/QWMetal/gemm/qwgemm_moe_group_f32.metal:10-148, and the weighted combine,
+ * Sources/QWMetal/gemm/qwgemm_moe_nax_f16.metal:7-126; chain: QWMoEOperator.encodeResident,
+ * Sources/Operators/QWGEMM/QWMoEOperator.swift:246-362.)  Experts [r * E / R, (r + 1) * E / R) live on rank r; every
+ * rank routes its own t tokens.  dispatch: route, pair sort, and one kernel that rotates every sorted row and stores it
+ * into the receive buffer of the rank that owns its expert (plain peer stores), then raises this rank's flag on every
+ * peer.  experts: waits (bounded) for every peer's flag, regroups the received rows by local expert, runs the two grouped
+ * expert GEMMs (SwiGLU + FWHT fused; inter % 64 == 0) and stores every result row into the return buffer of the rank it
+ * came from; raises the return flags.  combine: waits (bounded) for the return flags, then the weighted combine.  No host
+ * synchronisation, no NCCL.  The caller provides peer-mapped memory, zero before the first call:
+ *   recv[r]   rank r's receive buffer, f16 [world][capacity_rows][hidden]      (qwc_ep_recv_bytes)
+ *   counts[r] rank r's count tables, i32 [world][experts / world + 2]          (qwc_ep_counts_bytes)
+ *   ret[r]    rank r's return buffer, f16 [capacity_rows][hidden]              (qwc_ep_ret_bytes)
+ *   flags[r]  rank r's flags, u32 [2 * world + 2]                              (qwc_ep_flags_bytes)
+ * capacity_rows >= the largest t * k of any rank.  Every rank must make the same calls in the same order (t may differ
+ * per rank, also 0).  The call number is epoch (host counted, must differ from the previous call's) or, with epoch_state
+ * != NULL (one zero-initialised u32 in this rank's memory), *epoch_state + 1, stored back by the combine phase: the form
+ * for calls captured in a CUDA graph.  A wait that runs out (wait_us, default 1 s) sets status 105; the rank then
+ * finishes the call without touching memory outside its buffers.  With fewer GPUs than ranks the three phases can be
+ * called rank after rank on one device, each rank with its own buffers: every wait then finds its flags raised. */
+typedef struct {
+    int32_t rank, world;      /* 1 <= world <= 8 */
+    uint32_t epoch;
+    int32_t wait_us;
+    int64_t capacity_rows;
+    void* recv[8];
+    void* counts[8];
+    void* ret[8];
+    void* flags[8];
+    void* epoch_state;
+} qwc_ep_ctx;
+
+size_t qwc_ep_recv_bytes(int32_t world, int64_t capacity_rows, int64_t h);
+size_t qwc_ep_ret_bytes(int64_t capacity_rows, int64_t h);
+size_t qwc_ep_counts_bytes(int32_t world, int64_t e_total);
+size_t qwc_ep_flags_bytes(int32_t world);
+size_t qwc_ep_scratch_bytes(const qwc_ep_ctx* ctx, int64_t t, int64_t e_total, int64_t k, int64_t h, int64_t inter);
+int qwc_ep_dispatch(qwc_hal* hal, qwc_stream stream, const qwc_ep_ctx* ctx, int64_t e_total, const void* x_f16, int64_t t,
+                    int64_t ldx, int64_t h, int32_t x_is_rotated, const float* logits, int64_t k, int32_t norm_topk,
+                    float routed_scale, void* scratch, size_t scratch_bytes, int64_t inter);
+int qwc_ep_experts(qwc_hal* hal, qwc_stream stream, const qwc_ep_ctx* ctx, const qwc_weight_view* bank_gu_local,
+                   const qwc_weight_view* bank_dn_local, int64_t e_total, int64_t inter, int64_t t, int64_t k, void* scratch,
+                   size_t scratch_bytes);
+int qwc_ep_combine(qwc_hal* hal, qwc_stream stream, const qwc_ep_ctx* ctx, int64_t e_total, int64_t inter, int64_t t, int64_t k,
+                   int64_t h, void* out, int32_t out_dtype, void* scratch, size_t scratch_bytes);
+/* The three phases in one call (what a rank of a real group makes). */
+int qwc_ep_moe(qwc_hal* hal, qwc_stream stream, const qwc_ep_ctx* ctx, const qwc_weight_view* bank_gu_local,
+               const qwc_weight_view* bank_dn_local, int64_t e_total, int64_t inter, const void* x_f16, int64_t t, int64_t ldx,
+               int32_t x_is_rotated, const float* logits, int64_t k, int32_t norm_topk, float routed_scale, void* out,
+               int32_t out_dtype, void* scratch, size_t scratch_bytes);
 
 /* ---- mixture of experts ---------------------------------------------------------------------------------------
  * The operator chain of QWMoEOperator.encodeResident (Sources/Operators/QWGEMM/QWMoEOperator.swift:206-442), grouped

@@ -82,6 +82,8 @@ def lib() -> ctypes.CDLL:
         L.qwo_moe_forward.argtypes = [vp, vp, i32, i32, i32, i64, i64, i64, vp, i64, i64, vp, vp, vp]
         L.qwo_moe_forward_f32.argtypes = [vp, i64, i64, i64, i64, i64, i32, vp, vp, vp, i64, vp, vp, vp, vp, vp]
         L.qwo_num_threads.restype = ctypes.c_int
+        L.qwo_set_num_threads.restype = ctypes.c_int
+        L.qwo_set_num_threads.argtypes = [ctypes.c_int]
         _lib = L
     return _lib
 
@@ -96,6 +98,11 @@ def _c(a, dtype) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().qwo_num_threads())
+
+
+def set_num_threads(n: int) -> int:
+    """Use n OpenMP threads from now on (launchers may export OMP_NUM_THREADS=1); returns the number in effect."""
+    return int(lib().qwo_set_num_threads(int(n)))
 
 
 def fwht32(x: np.ndarray) -> np.ndarray:

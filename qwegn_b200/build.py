@@ -13,7 +13,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libqwcuda.so")
 SOURCES = ["qwc_api.cu", "qwc_dequant.cu", "qwc_gemv.cu"]
-OPTIONAL_SOURCES = ["qwc_gemm_tc.cu", "qwc_moe.cu", "qwc_noalloc.cu", "qwc_norm.cu", "qwc_f32.cu"]
+OPTIONAL_SOURCES = ["qwc_gemm_tc.cu", "qwc_moe.cu", "qwc_noalloc.cu", "qwc_norm.cu", "qwc_f32.cu", "qwc_ep.cu"]
 HEADERS = ["qwc_common.cuh", os.path.join("..", "..", "include", "qwc.h")]
 
 NVCC_FLAGS = [

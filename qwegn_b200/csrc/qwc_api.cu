@@ -315,4 +315,54 @@ int qwc_gemm_allreduce(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w
                               nullptr, 0, ctx);
 }
 
+// ---- peer-visible device memory (load-time helpers of the tensor- and expert-parallel doors) -------------------------
+// One process drives one GPU; the fused collectives store into the other ranks' buffers directly.  A rank allocates its
+// buffer here, hands the 64-byte handle to its peers by whatever channel the host has (the Python mirror uses
+// torch.distributed), and every peer maps it.  Allocation and mapping happen once, before the first encode call.
+int qwc_peer_alloc(qwc_hal* hal, size_t bytes, void** ptr_out, void* handle_out_64) {
+    qwc_clear_error();
+    if (!hal || !ptr_out || !handle_out_64 || bytes == 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "qwc_peer_alloc: bad argument");
+    *ptr_out = nullptr;
+    QWC_CUDA_TRY(cudaSetDevice(hal->device));
+    void* p = nullptr;
+    QWC_CUDA_TRY(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return qwc_fail(QWC_ERR_CUDA, "qwc_peer_alloc: %s", cudaGetErrorString(e));
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+    memcpy(handle_out_64, &h, 64);
+    *ptr_out = p;
+    return QWC_OK;
+}
+
+int qwc_peer_open(qwc_hal* hal, const void* handle_64, void** ptr_out) {
+    qwc_clear_error();
+    if (!hal || !handle_64 || !ptr_out) return qwc_fail(QWC_ERR_BAD_SHAPE, "qwc_peer_open: bad argument");
+    QWC_CUDA_TRY(cudaSetDevice(hal->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle_64, 64);
+    QWC_CUDA_TRY(cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+    return QWC_OK;
+}
+
+int qwc_peer_close(qwc_hal* hal, void* ptr) {
+    qwc_clear_error();
+    if (!hal || !ptr) return QWC_OK;
+    QWC_CUDA_TRY(cudaSetDevice(hal->device));
+    QWC_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+    return QWC_OK;
+}
+
+int qwc_peer_free(qwc_hal* hal, void* ptr) {
+    qwc_clear_error();
+    if (!hal || !ptr) return QWC_OK;
+    QWC_CUDA_TRY(cudaSetDevice(hal->device));
+    QWC_CUDA_TRY(cudaFree(ptr));
+    return QWC_OK;
+}
+
 }  // extern "C"

@@ -101,6 +101,8 @@ struct GemvParams {
     int ar_world, ar_rank;
     uint32_t ar_epoch;        // call number: the flag value that marks this call's data as complete
     uint64_t ar_wait_ns;      // limit of the peer wait (0: the library's default)
+    uint32_t* ar_state;       // device-side call counter (see qwc_allreduce_ctx::epoch_state); null: ar_epoch comes from the host
+    int64_t ar_inbox_stride, ar_flag_stride;   // distance between the two buffers (floats / words) when the kernel picks the buffer
     float* ar_inbox[8];       // rank r's inbox for this call: [world][m][n] f32; slot [s] is written by rank s
     uint32_t* ar_flags[8];    // rank r's flags for this call: [world][grid]; word [s][cta] is written by CTA cta of rank s
 };
@@ -497,6 +499,15 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     // everything the previous grid may have produced (activations, outputs, the K-slice scratch) is touched only after
     // this point.  The producer warp above does not wait: packed weights are load-time data.
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Fused all-reduce with a device-side call counter: the call number is read here (the previous call of the stream
+    // has completed), and its parity picks one of the two inbox / flag buffers.
+    uint32_t ar_epoch = p.ar_epoch;
+    int64_t ar_inbox_ofs = 0, ar_flag_ofs = 0;
+    if (SUB == 1 && p.ar_world > 1 && p.ar_state != nullptr) {
+        ar_epoch = *reinterpret_cast<volatile uint32_t*>(p.ar_state) + 1u;
+        ar_inbox_ofs = (ar_epoch & 1u) ? p.ar_inbox_stride : 0;
+        ar_flag_ofs = (ar_epoch & 1u) ? p.ar_flag_stride : 0;
+    }
     for (int base = warp * 8; base < items; base += 2 * kItemStride) {
         const uint4 ra = load_item(ia), rb4 = load_item(ib);
         const StageItem na = make_item(base + 2 * kItemStride + sub8), nb = make_item(base + 3 * kItemStride + sub8);
@@ -648,7 +659,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                             hval[ot][nt][i] = __half2float(__float2half_rn(v));
                         } else if (SUB == 1 && p.ar_world > 1) {
                             // the partial sum goes straight into every rank's inbox (peer stores over NVLink), its own too
-                            const int64_t o = (static_cast<int64_t>(p.ar_rank) * M_ + tok) * p.n + row;
+                            const int64_t o = ar_inbox_ofs + (static_cast<int64_t>(p.ar_rank) * M_ + tok) * p.n + row;
                             for (int r = 0; r < p.ar_world; ++r) p.ar_inbox[r][o] = v;
                         } else {
                             const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
@@ -694,9 +705,9 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         named_bar_sync(11, kConsumerWarps * 32);
         const int cta = static_cast<int>(blockIdx.x), grid = static_cast<int>(gridDim.x);
         if (threadIdx.x < static_cast<unsigned>(p.ar_world)) {
-            uint32_t* f = p.ar_flags[threadIdx.x] + p.ar_rank * grid + cta;
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ar_epoch) : "memory");
-            const uint32_t* mine = p.ar_flags[p.ar_rank] + threadIdx.x * grid + cta;
+            uint32_t* f = p.ar_flags[threadIdx.x] + ar_flag_ofs + p.ar_rank * grid + cta;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(ar_epoch) : "memory");
+            const uint32_t* mine = p.ar_flags[p.ar_rank] + ar_flag_ofs + threadIdx.x * grid + cta;
             // bounded by elapsed time: a peer that never raises its flag (it failed, or it never made the call) costs this
             // rank the limit once, then the status word says so and the kernel finishes with whatever the inbox holds
             bool got = false;
@@ -705,7 +716,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             for (uint32_t spin = 0;; ++spin) {
                 uint32_t v;
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-                if (v == p.ar_epoch) {
+                if (v == ar_epoch) {
                     got = true;
                     break;
                 }
@@ -716,7 +727,7 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         }
         named_bar_sync(11, kConsumerWarps * 32);
         const int rows_cta = re - rb;
-        const float* inbox = p.ar_inbox[p.ar_rank];
+        const float* inbox = p.ar_inbox[p.ar_rank] + ar_inbox_ofs;
         for (int i = threadIdx.x; i < rows_cta * M_; i += kConsumerWarps * 32) {
             const int tok = i / rows_cta, row = rb + (i - tok * rows_cta);
             float sum = 0.0f;
@@ -724,6 +735,18 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
             if (p.y_f16) static_cast<__half*>(Y_)[o] = __float2half_rn(sum);
             else static_cast<float*>(Y_)[o] = sum;
+        }
+        if (p.ar_state != nullptr) {
+            // the last CTA to finish publishes the call number: every CTA read the old one before it got here
+            named_bar_sync(11, kConsumerWarps * 32);
+            if (threadIdx.x == 0) {
+                __threadfence();
+                if (atomicAdd(p.ar_state + 1, 1u) == static_cast<uint32_t>(grid) - 1u) {
+                    p.ar_state[1] = 0u;
+                    __threadfence();
+                    *reinterpret_cast<volatile uint32_t*>(p.ar_state) = ar_epoch;
+                }
+            }
         }
     }
 }
@@ -1124,6 +1147,9 @@ int qwc_launch_gemv_ar(const qwc_hal* hal, cudaStream_t st, const qwc_weight_vie
         p.ar_rank = ar->rank;
         p.ar_epoch = ar->epoch;
         p.ar_wait_ns = ar->reserved > 0 ? static_cast<uint64_t>(ar->reserved) * 1000ull : 0ull;
+        p.ar_state = static_cast<uint32_t*>(ar->epoch_state);
+        p.ar_inbox_stride = ar->inbox_floats;
+        p.ar_flag_stride = ar->flag_words;
         for (int r = 0; r < ar->world && r < 8; ++r) {
             p.ar_inbox[r] = static_cast<float*>(ar->inbox[r]);
             p.ar_flags[r] = static_cast<uint32_t*>(ar->flags[r]);

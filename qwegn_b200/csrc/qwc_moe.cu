@@ -756,7 +756,7 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
         // one launch: every CTA reads the whole pair list (<= 1 MB, L2-resident)
         int grid = static_cast<int>(pairs > 0 ? (pairs + kSortCta - 1) / kSortCta : 1);
         // the tile lists are written expert by expert, experts dealt over the CTAs: a short pair list still gets 32 CTAs for that
-        if ((tiles_gu != nullptr || tiles_dn != nullptr) && grid < 32) grid = static_cast<int>(e < 32 ? e : 32);
+        if ((tiles_gu != nullptr || tiles_dn != nullptr) && grid < 32 && grid < e) grid = static_cast<int>(e < 32 ? e : 32);
         QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_sort_kernel, dim3(grid), dim3(kSortCta), 0, st, idx, static_cast<int>(pairs),
                                     static_cast<int>(e), static_cast<int>(k), moe_tile_rows(pairs, e), static_cast<int>(gu_rows),
                                     static_cast<int>(dn_rows), paired, expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn,

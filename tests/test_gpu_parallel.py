@@ -80,6 +80,56 @@ def _worker(rank, world, port, results):
         err = np.abs(out.cpu().numpy() - ref).max() / np.abs(ref).max()
         assert err < 8e-3, ("ep moe", err)
         assert hal.device_status() == 0
+
+        # ---- the same block with the exchange inside the library (peer stores + flags; no NCCL, no host read), twice
+        # eagerly and once more as a replayed CUDA graph (the call number is counted on the device)
+        epf = par.EPMoEFused(hal, torch.from_numpy(bgu.reshape(-1)), torch.from_numpy(bdn.reshape(-1)), e, hid, it, k, cont, rank, world,
+                             max_tokens=t1 - t0)
+        xd, ld = torch.from_numpy(xs[t0:t1]).cuda(), torch.from_numpy(lg[t0:t1]).cuda()
+        outf = torch.full((t1 - t0, hid), float("nan"), dtype=torch.float32, device="cuda")
+        for _ in range(2):
+            epf.forward(xd, ld, outf)
+            err = np.abs(outf.cpu().numpy() - ref).max() / np.abs(ref).max()
+            assert err < 8e-3, ("ep moe fused", err)
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        torch.cuda.synchronize()
+        dist.barrier()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                epf.forward(xd, ld, outf)
+        for _ in range(3):
+            outf.fill_(float("nan"))
+            g.replay()
+            torch.cuda.synchronize()
+            err = np.abs(outf.cpu().numpy() - ref).max() / np.abs(ref).max()
+            assert err < 8e-3, ("ep moe fused, graph replay", err)
+        assert hal.device_status() == 0
+
+        # ---- tensor-parallel layer stack (HQ8_G32 attention projections, HQ4_G32 MLP) against the same stack on one device
+        hidden, inter, qh, kvh, hd = 512, 1024, 8, 2, 64
+        c8 = q.CONTAINERS["HQ8_G32"]
+        planes = []
+        for _ in range(2):
+            planes.append({
+                "qkv": torch.from_numpy(qo.quantize(rng.normal(0, 0.05, ((qh + 2 * kvh) * hd, hidden)).astype(np.float32), qo.HQ8_G32).reshape(-1)),
+                "o": torch.from_numpy(qo.quantize(rng.normal(0, 0.05, (hidden, qh * hd)).astype(np.float32), qo.HQ8_G32).reshape(-1)),
+                "gate_up": torch.from_numpy(qo.quantize(rng.normal(0, 0.05, (2 * inter, hidden)).astype(np.float32), fmt).reshape(-1)),
+                "down": torch.from_numpy(qo.quantize(rng.normal(0, 0.05, (hidden, inter)).astype(np.float32), fmt).reshape(-1))})
+        one = par.TPLayerStack([par.TPLayer(hal, pl, hidden, inter, qh, kvh, hd, c8, cont, 0, 1, fused_allreduce=False) for pl in planes], hal)
+        tp = par.TPLayerStack([par.TPLayer(hal, pl, hidden, inter, qh, kvh, hd, c8, cont, rank, world, fused_allreduce=True) for pl in planes], hal)
+        for mtok, chunk in ((1, 0), (5, 0), (300, 128)):
+            x0 = torch.from_numpy(rng.standard_normal((mtok, hidden)).astype(np.float16)).cuda()
+            xn_a, res_a = torch.empty_like(x0), x0.clone()
+            q.QWGemm.encodeRMSNorm(hal, x0, one.layers[0].gamma1, xn_a)
+            xn_b, res_b = xn_a.clone(), res_a.clone()
+            one.forward(xn_a, res_a, one.buffers(mtok))
+            tp.forward(xn_b, res_b, tp.buffers(mtok), chunk=chunk)
+            torch.cuda.synchronize()
+            a, b = res_a.float().cpu().numpy(), res_b.float().cpu().numpy()
+            err = np.abs(a - b).max() / np.abs(a).max()
+            assert np.isfinite(b).all() and err < 1e-2, ("tp layer stack", mtok, err)
+        assert hal.device_status() == 0
         results[rank] = True
     finally:
         dist.barrier()

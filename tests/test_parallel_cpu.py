@@ -145,3 +145,23 @@ def test_tensor_parallel_mlp_world2():
     results = mgr.dict()
     mp.spawn(_tp_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     assert all(results.get(r) for r in range(world))
+
+
+def test_section_column_shard_keeps_every_ranks_heads(oracle):
+    # A fused QKV plane: query, key and value rows are each cut over the ranks on head boundaries.
+    fmt, cont = oracle.HQ8_G32, q.CONTAINERS["HQ8_G32"]
+    heads, kv, hd, k, world = 8, 4, 32, 256, 4
+    sections = [heads * hd, kv * hd, kv * hd]
+    rng = np.random.default_rng(4)
+    blocks = oracle.quantize(rng.normal(0, 0.02, (sum(sections), k)).astype(np.float32), fmt)
+    plane = torch.from_numpy(blocks.reshape(-1))
+    full = oracle.dequant(blocks, fmt)
+    for r in range(world):
+        sh, local = par.section_column_shard(plane, sections, k, cont, r, world, quantum=hd)
+        assert local == [heads * hd // world, kv * hd // world, kv * hd // world]
+        got = oracle.dequant(sh.numpy().reshape(sum(local), k // fmt.group, fmt.block_bytes), fmt)
+        base, at = 0, 0
+        for n_sec, n_loc in zip(sections, local):
+            assert np.array_equal(got[at:at + n_loc], full[base + r * n_loc:base + (r + 1) * n_loc])
+            base += n_sec
+            at += n_loc
