@@ -182,8 +182,11 @@ __global__ void __launch_bounds__(1024) qwc_head_argmax_kernel(const float* __re
             const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
             best = other > best ? other : best;
         }
-        if (lane == 0) *cluster.map_shared_rank(&s_cluster[crank], 0) = best;
     }
+    // Distributed shared memory may only be touched once the target CTA is known to be running: every CTA of the
+    // cluster meets here first (with a short vocabulary the other ranks would otherwise reach the store at once).
+    cluster.sync();
+    if (warp == 0 && lane == 0) *cluster.map_shared_rank(&s_cluster[crank], 0) = best;
     cluster.sync();
     if (crank == 0 && tid == 0) {
         best = s_cluster[0];

@@ -20,6 +20,9 @@ Files written:
   selfpack.qwp       pack_file() of the --selfpack tensor (Scripts/quantize/pack.py:742-758);
                      asserted byte-identical to the reference's committed fixture.
   formats.npz        quantize/dequantize outputs of the reference for HQ4_G32, HQ8_G32, HQ4_G64.
+  moepack.qwp        pack_file() of a small layer: 3-D expert stacks ("….experts.…" names, Scripts/quantize/pack.py:104-112,
+                     231-255) in HQ4_G32_M5, HQ8_G32 and HQ4_G64, plus 2-D HQ8_G32 / HQ4_G64 planes
+  moepack.npz        the tensors that went into moepack.qwp and the reference's per-expert dequantised sidecars
   matmul.npz         reduced-size restatements of the fixture recipes of
                      Scripts/oracle/gen_s1_q4_fixtures.py, gen_f5_fixtures.py, gen_mlp_fixtures.py
                      (same seeds, distributions and arithmetic; smaller N/K).
@@ -182,7 +185,37 @@ def main():
         mm[f"mlp_h_M{M}"] = h16
         mm[f"mlp_y_M{M}"] = (h16.astype(np.float32) @ dq.T).astype(np.float32)
     np.savez_compressed(HERE / "matmul.npz", **mm)
-    for f in ("ref_fixtures.npz", "selfpack.qwp", "formats.npz", "matmul.npz"):
+
+    # ---- 4. a pack with expert stacks and the rotated HQ containers --------
+    rng = np.random.default_rng(31)
+    stacks = {}
+    # layer: (quant spec, experts, hidden, intermediate); weights are drawn as f16 values so that the .npz stays small
+    layers = {"l0": (None, 4, 128, 128), "l1": ((8, 32, False), 4, 128, 128), "l2": ((4, 64, False), 2, 256, 256)}
+    tensors = []
+
+    def draw(shape, sigma):
+        return rng.normal(0.0, sigma, shape).astype(np.float16)
+
+    for layer, (kind, E, H, I) in layers.items():
+        gu, dn = draw((E, 2 * I, H), 0.05), draw((E, H, I), 0.05)
+        stacks[f"{layer}_gate_up"], stacks[f"{layer}_down"] = gu, dn
+        for nm, arr in ((f"{layer}.mlp.experts.gate_up_proj", gu), (f"{layer}.mlp.experts.down_proj", dn)):
+            arr = arr.astype(np.float32)
+            tensors.append((nm, arr, kind) if kind else (nm, arr))
+        stacks[f"{layer}_x"] = rng.standard_normal((24, H)).astype(np.float16)
+        stacks[f"{layer}_logits"] = rng.standard_normal((24, E)).astype(np.float32)
+    stacks["q_proj"], stacks["o_proj"] = draw((96, 128), 0.02), draw((64, 256), 0.02)
+    tensors.append(("l0.attn.q_proj.weight", stacks["q_proj"].astype(np.float32), (8, 32, False)))
+    tensors.append(("l0.attn.o_proj.weight", stacks["o_proj"].astype(np.float32), (4, 64, False)))
+    with tempfile.TemporaryDirectory() as td:
+        out = Path(td) / "moepack.qwp"
+        pack.pack_file(tensors, out, {"source": "moepack", "sha256_source": "n/a"}, sidecar_dir=Path(td) / "side")
+        (HERE / "moepack.qwp").write_bytes(out.read_bytes())
+        for layer in layers:   # the reference's own dequantisation of expert 1 of each stack (first 16 rows)
+            for proj in ("gate_up_proj", "down_proj"):
+                stacks[f"{layer}_{proj}_e1_dq"] = np.load(Path(td) / "side" / f"{layer}.mlp.experts.{proj}.e1.dq4.npy")[:16]
+    np.savez_compressed(HERE / "moepack.npz", **stacks)
+    for f in ("ref_fixtures.npz", "selfpack.qwp", "formats.npz", "matmul.npz", "moepack.qwp", "moepack.npz"):
         print(f, (HERE / f).stat().st_size, "bytes")
 
 

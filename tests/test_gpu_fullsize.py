@@ -89,6 +89,34 @@ def test_prefill_shapes_m4096(hal):
     assert hal.device_status() == 0
 
 
+# C5: one 70B-class layer (hidden 8192, intermediate 28672, 64 query + 8 key/value heads of 128): QKV and O in HQ8_G32, the MLP
+# in HQ4_G32, whole and as the 1/8 shards of tensor parallelism (column shards cut N, row shards cut K)
+_LAYER_BANKS = [
+    ("HQ8_G32", 10240, 8192), ("HQ8_G32", 8192, 8192), ("HQ4_G32", 57344, 8192), ("HQ4_G32", 8192, 28672),
+    ("HQ8_G32", 1280, 8192), ("HQ8_G32", 8192, 1024), ("HQ4_G32", 7168, 8192), ("HQ4_G32", 8192, 3584),
+]
+
+
+@pytest.mark.parametrize("name,n,k", _LAYER_BANKS)
+def test_layer_bank_shapes_h8192_i28672(hal, name, n, k):
+    import qwegn_b200 as q
+    view, wq = _bank(q, hal, n, k, name, seed=n + k)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(n ^ k)
+    for m in (1, 8192):
+        x = torch.randn((m, k), generator=gen, device="cuda").to(torch.float16)
+        dt = torch.float32 if m == 1 else torch.float16
+        y = _encode(q, hal, view, x, dtype=dt)
+        assert torch.equal(y, _encode(q, hal, view, x, dtype=dt)), "not deterministic"
+        if m == 1:
+            assert float((_encode(q, hal, view, x * 2, dtype=dt) - y * 2).abs().max()) <= 1e-5 * float(y.abs().max())
+        xr = x.clone()
+        q.QWGemm.encodeFwht32(hal, xr)
+        _close(y.float(), xr.float() @ wq.t(), 3e-3)
+        del x, xr, y
+    assert hal.device_status() == 0
+
+
 @pytest.mark.parametrize("tokens", [2048, 8])
 def test_moe_block_t2048_e256_top8(hal, tokens):
     # C4: 256 experts, top-8, hidden 2048, expert intermediate 512; 2048 tokens (grouped tensor path) and 8 (decode path)
