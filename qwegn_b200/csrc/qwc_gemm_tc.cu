@@ -14,16 +14,17 @@
 //   * A converter thread owns one weight row = one TMEM lane: it reads its row's 64 k of the raw step, decodes them in
 //     registers (magic-bias form and one f16 FMA with scale and bias: the reference's in-register decode,
 //     qw_gemm_nax.metalh:114-127) and only then waits for the operand stage to be free and writes 32 TMEM columns
-//     with tcgen05.st, so the decode of K tile j + S overlaps the MMAs of K tile j.  Converter warp c serves lane
-//     quarter c % 4 and the K tiles j with j % 4 == c / 4.
+//     with tcgen05.st, so the decode of stage j + S overlaps the MMAs of stage j.  Converter warp c serves lane
+//     quarter c % 4 and the operand stages j with j % 4 == c / 4.
 //   * The MMAs take A from tensor memory and B (the activations) from shared memory: tcgen05.mma, M = 128 weight rows,
 //     N = tokens, K = 16, into a TMEM accumulator; tcgen05.commit releases the stage and, after the last K tile, hands
 //     the accumulator to the epilogue warps (tcgen05.ld, lane = weight row; plain store or the fused SwiGLU (+ FWHT)
 //     epilogue); two accumulators alternate so the epilogue of one tile overlaps the main loop of the next.
-//   * TMEM budget (512 columns): tiles of up to 192 tokens use two 192-column accumulators and 4 operand stages of 32
-//     columns; tiles of up to 128 tokens (expert tiles, verify-sized calls) use two 128-column accumulators and 8
-//     operand stages, because with few tokens an MMA is short and the hand-off latencies, not the tensor pipe, set the
-//     pace: more stages in flight hide them.
+//   * TMEM budget (512 columns), four operand stages: tiles of up to 192 tokens use two 192-column accumulators and stages
+//     of one 64-wide K tile (32 columns of A each); tiles of up to 128 tokens (expert tiles, verify-sized calls) use two
+//     128-column accumulators and stages of two K tiles (64 columns of A, two activation sub-tiles), because the MMA
+//     warp's issue loop costs a fixed ~400 cycles per stage (barrier wait, fence, election, commit: measured with every
+//     other role idle) and with few tokens the MMAs of one K tile are shorter than that.
 // Weights are the M operand so that all tokens of a tile share every decoded weight.  The grouped (mixture-of-experts)
 // door runs the same kernel over a device-side tile list.  The kernel is launched with programmatic stream
 // serialization and waits for the grid before it (griddepcontrol.wait) after its own set-up, before any global access.
@@ -63,11 +64,12 @@ struct TcParams {
     int m, n, k;
     int y_f16;
     int raw_stages;
-    int stages;          // operand stages: 4 (tiles of up to 192 tokens) or 8 (tiles of up to 128 tokens); a power of two
-    int stage_shift;     // log2(stages): stage of K tile j = j & (stages - 1), its use count = j >> stage_shift
+    int stages;          // operand stages; a power of two
+    int stage_shift;     // log2(stages): slot of stage j = j & (stages - 1), its use count = j >> stage_shift
+    int kt_per_stage;    // 64-wide K tiles per operand stage: 1 or 2 (a divisor of the K tiles of a raw step)
     int acc_stride;      // TMEM columns per accumulator: 192 or 128; the operand stages start at column 2 * acc_stride
     int x_tile_rows;     // activation rows per tile: 192, 128 or 64
-    int x_slot_bytes;    // bytes of one activation stage: x_tile_rows x 128 B
+    int x_slot_bytes;    // bytes of one activation stage: kt_per_stage x x_tile_rows x 128 B
     int raw_row_bytes;   // packed bytes of one raw step of one row: 80 (HQ4_G32_M5) or 144 (HQ8_G32, HQ4_G64)
     int m_tiles, n_tiles;
     int epilogue;        // QWC_EPI_NONE, or a SwiGLU epilogue: a tile is then 64 gate rows + the 64 matching up rows
@@ -432,7 +434,9 @@ __device__ __forceinline__ void load_tile_words(const uint8_t* src, int sub, uin
     }
 }
 
-template <int FMT>
+// KS = 64-wide K tiles per operand stage: compile-time, because the loops that use it pace the kernel and every instruction
+// in them counts.
+template <int FMT, int KS>
 __global__ void __launch_bounds__(kTsThreads, 1)
 qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    const __grid_constant__ CUtensorMap xmap128, const __grid_constant__ CUtensorMap xmap64,
@@ -457,7 +461,6 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     uint64_t* acc_empty = acc_full + 2;            // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint32_t* raw_issued = tmem_slot + 2;          // raw steps the weight producer has started
     volatile int* epi_ok = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [2][4] the epilogue warps' verdicts on a tile
     uint8_t* xch = reinterpret_cast<uint8_t*>(bars) + 512;
 
@@ -469,14 +472,13 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         }
         for (int s = 0; s < p.raw_stages; ++s) {
             mbar_init(&raw_full[s], 1);
-            mbar_init(&raw_empty[s], 4 * KPR);   // every K tile of the step: four quarter warps
+            mbar_init(&raw_empty[s], 4 * KPR / KS);   // every operand stage of the step: four quarter warps
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
             mbar_init(&acc_empty[s], kEpiWarps);
         }
         *abort_flag = 0;
-        *raw_issued = 0;
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -495,6 +497,8 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     const int total_tiles = p.tiles != nullptr ? *p.tile_count : p.m_tiles * p.n_tiles;
     const int ktiles = p.k / kBK;
     const int raw_steps = ktiles / KPR;
+    const int kstages = ktiles / KS;                       // operand stages per tile
+    const uint32_t x_sub_bytes = static_cast<uint32_t>(p.x_slot_bytes / KS);   // one 64-wide K tile of the activations inside a stage
     const uint32_t a_col0 = static_cast<uint32_t>(2 * p.acc_stride);
     const uint32_t smask = static_cast<uint32_t>(p.stages - 1);
     auto fail = [&](int code) {
@@ -502,8 +506,8 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         *abort_flag = 1;
     };
 
-    // K tile number j of the kernel (all tiles) uses operand stage j % stages in phase (j / stages) & 1 and belongs to
-    // raw step j / KPR, which uses raw slot r % raw_stages in phase (r / raw_stages) & 1.
+    // Operand stage number j of the kernel (all tiles) holds KS consecutive K tiles, uses slot j % stages in phase
+    // (j / stages) & 1 and reads raw step j * KS / KPR, which uses raw slot r % raw_stages in phase (r / raw_stages) & 1.
     if (warp == 0) {
         // ---------------- TMA producer: rotated activations (one tile per K tile) ----------------
         if (lane == 0) {
@@ -513,7 +517,7 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                 const TileInfo ti = tc_get_tile(p, tile);
                 const CUtensorMap* xm = ti.x_rows <= 64 ? &xmap64 : (ti.x_rows <= 128 ? &xmap128 : &xmap);
                 const uint32_t xbytes = (ti.x_rows <= 64 ? 64u : (ti.x_rows <= 128 ? 128u : static_cast<uint32_t>(p.x_tile_rows))) * kBK * 2u;
-                for (int kt = 0; kt < ktiles; ++kt, ++j) {
+                for (int ks = 0; ks < kstages; ++ks, ++j) {
                     const uint32_t s = j & smask;
                     const bool got_x = j < static_cast<uint32_t>(p.stages) || mbar_wait_relaxed(&empty[s], ((j >> p.stage_shift) - 1) & 1u, abort_flag);
                     if (!got_x) {
@@ -521,8 +525,10 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                         ok = false;
                         break;
                     }
-                    mbar_arrive_expect_tx(&full[s], xbytes);
-                    tma_load_2d(xt + s * p.x_slot_bytes, xm, kt * kBK, ti.x_row0, &full[s]);
+                    mbar_arrive_expect_tx(&full[s], xbytes * static_cast<uint32_t>(KS));
+#pragma unroll
+                    for (int q = 0; q < KS; ++q)
+                        tma_load_2d(xt + s * p.x_slot_bytes + q * x_sub_bytes, xm, (ks * KS + q) * kBK, ti.x_row0, &full[s]);
                 }
             }
         }
@@ -550,7 +556,6 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                         tma_load_2d(raw + s * raw_stage_bytes + (kBM / 2) * p.raw_row_bytes, &wmap64, rs * (p.raw_row_bytes / 8),
                                     ti.w_row1, &raw_full[s]);
                     }
-                    asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(raw_issued)), "r"(r + 1) : "memory");
                 }
             }
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
@@ -571,7 +576,7 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * p.acc_stride);
             const uint32_t idesc = make_idesc(min(p.acc_stride, (tc_get_tile(p, tile).x_rows + 15) & ~15));
-            for (int kt = 0; kt < ktiles; ++kt, ++j) {
+            for (int ks = 0; ks < kstages; ++ks, ++j) {
                 const uint32_t s = j & smask;
                 const bool got_full = mbar_wait_spin(&full[s], (j >> p.stage_shift) & 1u, abort_flag);   // all lanes poll: measured faster than one polling lane
                 if (!got_full) {
@@ -581,11 +586,15 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                 }
                 tc_fence_after();   // the converters' tcgen05.st happen-before these MMAs
                 const uint32_t b_lo = b_lo0 + s * b_step;
-                const uint32_t a_tmem = tmem_base + a_col0 + s * 32;
+                const uint32_t a_tmem = tmem_base + a_col0 + s * 32 * KS;
                 if (elect_one()) {
 #pragma unroll
-                    for (int q = 0; q < kBK / 16; ++q)
-                        umma_f16_ts(d_tmem, a_tmem + q * 8, pack_desc(b_lo + 2 * q, b_hi), idesc, (kt > 0 || q > 0) ? 1u : 0u);
+                    for (int h = 0; h < KS; ++h) {
+                        const uint32_t bh = b_lo + h * (x_sub_bytes >> 4);
+#pragma unroll
+                        for (int q = 0; q < kBK / 16; ++q)
+                            umma_f16_ts(d_tmem, a_tmem + (h * 4 + q) * 8, pack_desc(bh + 2 * q, b_hi), idesc, (ks > 0 || h > 0 || q > 0) ? 1u : 0u);
+                    }
                     umma_commit(&empty[s]);
                 }
                 __syncwarp();
@@ -596,37 +605,38 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         __syncwarp();
     } else if (warp >= kTsFirstConvWarp && warp < kTsFirstConvWarp + kConvWarps) {
         // ------------------------------- converters -------------------------------
-        // Converter warp c: TMEM lane quarter c & 3, K tiles j with j % 4 == c >> 2.  A thread owns one weight row.
+        // Converter warp c: TMEM lane quarter c & 3, operand stages j with j % 4 == c >> 2.  A thread owns one weight row.
         const int c = warp - kTsFirstConvWarp;
         const int qd = c & 3, cl = c >> 2;
-        const int sub = cl % KPR;   // which K tile of its raw step this warp decodes (constant: 4 % KPR == 0)
         const uint32_t row_ofs = static_cast<uint32_t>(qd * 32 + lane) * p.raw_row_bytes;
         const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + a_col0;
         bool ok = true;
-        uint32_t jbase = 0;   // K tiles of the tiles already done
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, jbase += ktiles) {
-            // first K tile of this tile that belongs to this warp's class
-            for (uint32_t j = jbase + ((cl + 4u - (jbase & 3u)) & 3u); j < jbase + ktiles; j += 4) {
-                const uint32_t r = j / KPR;
+        uint32_t jbase = 0;   // operand stages of the tiles already done
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, jbase += kstages) {
+            // first stage of this tile that belongs to this warp's class
+            for (uint32_t j = jbase + ((cl + 4u - (jbase & 3u)) & 3u); j < jbase + kstages; j += 4) {
+                const uint32_t kt0 = j * KS;          // first K tile of the stage (KS divides KPR: one raw step per stage)
+                const uint32_t r = kt0 / KPR;
+                const int sub0 = static_cast<int>(kt0 % KPR);
                 const uint32_t rslot = r % p.raw_stages, rpar = (r / p.raw_stages) & 1u;
                 const uint32_t s = j & smask, use = j >> p.stage_shift;
-                // A raw slot's successive phases are consumed by different warps, and a parity wait cannot tell phase k
-                // from phase k - 2: wait first until the producer has started step r (which it does only after phase
-                // k - 1 was consumed); from then on the parity wait is exact.
-                const bool got_raw = wait_counter_above(raw_issued, r, abort_flag) && mbar_wait(&raw_full[rslot], rpar, abort_flag);
+                // The parity wait is exact: raw_stages is a power of two, so this warp (every fourth stage) meets every phase
+                // of the raw slots it uses, and it has seen phase k - 1 of a slot complete before it waits for phase k.
+                const bool got_raw = mbar_wait(&raw_full[rslot], rpar, abort_flag);
                 if (!got_raw) {
                     if (lane == 0) fail(QWC_DEV_WAIT_FULL_TIMEOUT);
                     ok = false;
                     break;
                 }
+                const uint8_t* src = raw + rslot * raw_stage_bytes + row_ofs;
                 uint32_t w[kTileWords];
                 uint32_t a32[32];
-                {
-                    load_tile_words<FMT>(raw + rslot * raw_stage_bytes + row_ofs, sub, w);
-                    decode_tile_natural<FMT>(w, a32);
-                }
+                uint32_t w1[KS == 2 ? kTileWords : 1];
+                load_tile_words<FMT>(src, sub0, w);
+                if (KS == 2) load_tile_words<FMT>(src, sub0 + 1, w1);
+                decode_tile_natural<FMT>(w, a32);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&raw_empty[rslot]);   // the packed words are in registers
+                if (lane == 0) mbar_arrive(&raw_empty[rslot]);   // the packed words of the stage are in registers
                 // only now wait for the operand stage: the decode above overlapped the MMAs that were reading it
                 const bool got_empty = use == 0 || mbar_wait(&empty[s], (use - 1) & 1u, abort_flag);
                 if (!got_empty) {
@@ -635,10 +645,13 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
                     break;
                 }
                 tc_fence_after();   // the MMAs that read this A stage are complete (tcgen05.commit -> empty[s])
-                {
-                    tmem_st32(lane_taddr + s * 32, a32);
-                    tmem_st_wait();
+                tmem_st32(lane_taddr + s * 32 * KS, a32);
+                if (KS == 2) {
+                    tmem_st_wait();   // the first store has read its registers
+                    decode_tile_natural<FMT>(w1, a32);
+                    tmem_st32(lane_taddr + s * 64 + 32, a32);
                 }
+                tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&full[s]);
@@ -697,13 +710,13 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-template <int FMT>
-int launch_ts(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap64,
-              const CUtensorMap* xmaps, int smem, int grid) {
+template <int FMT, int KS>
+int launch_ts_inst(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap64,
+                   const CUtensorMap* xmaps, int smem, int grid) {
     // once per device and instantiation; racing first calls both set the same value, which is harmless
     static std::atomic<bool> configured[64];
     if (!configured[hal->device & 63].load(std::memory_order_acquire)) {
-        QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemm_ts_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        QWC_CUDA_TRY(cudaFuncSetAttribute(qwc_gemm_ts_kernel<FMT, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured[hal->device & 63].store(true, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg{};
@@ -716,8 +729,15 @@ int launch_ts(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUte
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    QWC_CUDA_TRY(cudaLaunchKernelEx(&cfg, qwc_gemm_ts_kernel<FMT>, p, wmap, xmaps[0], xmaps[1], xmaps[2], wmap64));
+    QWC_CUDA_TRY(cudaLaunchKernelEx(&cfg, qwc_gemm_ts_kernel<FMT, KS>, p, wmap, xmaps[0], xmaps[1], xmaps[2], wmap64));
     return QWC_OK;
+}
+
+template <int FMT>
+int launch_ts(const qwc_hal* hal, cudaStream_t st, const TcParams& p, const CUtensorMap& wmap, const CUtensorMap& wmap64,
+              const CUtensorMap* xmaps, int smem, int grid) {
+    if (p.kt_per_stage == 2) return launch_ts_inst<FMT, 2>(hal, st, p, wmap, wmap64, xmaps, smem, grid);
+    return launch_ts_inst<FMT, 1>(hal, st, p, wmap, wmap64, xmaps, smem, grid);
 }
 
 }  // namespace
@@ -759,10 +779,14 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     if (tiles == nullptr) x_tile_rows = m <= 64 ? 64 : (m <= 128 ? 128 : kTsBN);   // dense: the narrowest tile that holds all tokens
     if (x_tile_rows > kTsBN) x_tile_rows = kTsBN;
     p.x_tile_rows = x_tile_rows;
-    // few tokens per tile: short MMAs, so more operand stages in flight (and narrower accumulators to make room)
-    p.stages = x_tile_rows <= 128 ? kMaxStages : 4;
-    if (const int st_env = tune_env("QWC_TC_STAGES", 0); st_env == 4 || (st_env == 8 && x_tile_rows <= 128)) p.stages = st_env;
-    p.acc_stride = p.stages == kMaxStages ? 128 : kTsBN;
+    // Four operand stages.  The issue loop of the MMA warp costs a fixed ~0.2 us per stage (barrier wait, fence, commit), so a
+    // stage of one 64-wide K tile paces the kernel whenever its MMAs are shorter than that: tiles of up to 128 tokens (expert
+    // tiles, verify-sized calls) take 128 k per stage and narrower accumulators to make room in tensor memory.
+    p.kt_per_stage = x_tile_rows <= 128 ? 2 : 1;
+    if (const int ks_env = tune_env("QWC_TC_KS", 0); ks_env == 1 || (ks_env == 2 && x_tile_rows <= 128)) p.kt_per_stage = ks_env;
+    p.stages = 4;
+    if (p.kt_per_stage == 1 && x_tile_rows <= 128 && tune_env("QWC_TC_STAGES", 8) == 8) p.stages = kMaxStages;
+    p.acc_stride = x_tile_rows <= 128 ? 128 : kTsBN;
     p.stage_shift = p.stages == kMaxStages ? 3 : 2;
     p.m_tiles = static_cast<int>((m + x_tile_rows - 1) / x_tile_rows);
     p.epilogue = epilogue;
@@ -770,10 +794,10 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     p.xch_bytes = epilogue == QWC_EPI_NONE ? 0 : (kBM / 2) * 16 * 2;
     p.n_tiles = epilogue == QWC_EPI_NONE ? static_cast<int>((w->n + kBM - 1) / kBM) : static_cast<int>(w->n / kBM);
     const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
-    p.x_slot_bytes = x_tile_rows * kBK * 2;
+    p.x_slot_bytes = p.kt_per_stage * x_tile_rows * kBK * 2;
     p.raw_stages = kTsMaxRaw;
     auto smem_need = [&](int rs) { return 1024 + p.stages * p.x_slot_bytes + rs * raw_stage_bytes + 512 + p.xch_bytes; };
-    while (smem_need(p.raw_stages) > 227 * 1024 && p.raw_stages > 2) --p.raw_stages;
+    while (smem_need(p.raw_stages) > 227 * 1024 && p.raw_stages > 2) p.raw_stages >>= 1;   // a power of two (see the converters' raw wait)
     if (smem_need(p.raw_stages) > 227 * 1024) return qwc_fail(QWC_ERR_BAD_GEOMETRY, "shared-memory budget exceeded");
     const int smem = smem_need(p.raw_stages);
 
