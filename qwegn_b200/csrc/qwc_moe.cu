@@ -470,6 +470,8 @@ __global__ void __launch_bounds__(512) qwc_moe_decode_plan_kernel(const int32_t*
 // xs[p, :] = rot(x[sorted_tok[p], :]).  A quad handles one (sorted row, 32-element unit): lane t holds elements
 // 8t..8t+7 (one 16-byte load), rotates with three in-lane butterfly stages and two xor-shuffle stages (the
 // reference's h = 1, 2, 4, 8, 16 order) and writes one 16-byte chunk.  vec != 0 needs 16-byte aligned rows.
+// IdxT = uint32_t while pairs * units fits (the item index is divided per item: 32-bit division is several times cheaper).
+template <typename IdxT>
 __global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __restrict__ x, int64_t ldx, int h,
                                                              const int32_t* __restrict__ sorted_tok,
                                                              const int32_t* __restrict__ expert_off, int e, int rotate, int vec,
@@ -477,13 +479,14 @@ __global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __res
     pdl_enter();
     const int lane = threadIdx.x & 31, t4 = lane & 3, q8 = lane >> 2;
     const int units = h / 32;
-    const int64_t total = static_cast<int64_t>(expert_off[e]) * units;
-    const int64_t step = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5) * 8;
-    for (int64_t base = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 8; base < total; base += step) {
-        const int64_t it = base + q8;
+    const IdxT total = static_cast<IdxT>(expert_off[e]) * static_cast<IdxT>(units);
+    const IdxT step = static_cast<IdxT>(gridDim.x) * (blockDim.x >> 5) * 8;
+    for (IdxT base = (static_cast<IdxT>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 8; base < total; base += step) {
+        const IdxT it = base + q8;
         const bool live = it < total;
-        const int64_t pr = live ? it / units : 0;
-        const int u = live ? static_cast<int>(it % units) : 0;
+        const IdxT prq = live ? it / static_cast<IdxT>(units) : 0;
+        const int u = live ? static_cast<int>(it - prq * static_cast<IdxT>(units)) : 0;
+        const int64_t pr = static_cast<int64_t>(prq);
         const __half* src = x + static_cast<int64_t>(live ? sorted_tok[pr] : 0) * ldx + u * 32 + 8 * t4;
         uint4 raw = make_uint4(0, 0, 0, 0);
         if (live) {
@@ -787,9 +790,17 @@ int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t l
     if (!x_f16 || !sorted_tok || !expert_off || !xs_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
     const int vec = reinterpret_cast<uintptr_t>(x_f16) % 16 == 0 && ldx % 8 == 0;
     if (reinterpret_cast<uintptr_t>(xs_f16) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "xs must be 16-byte aligned");
-    QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_gather_kernel, dim3(grid_for(hal, pairs * (h / 32), 64, 16)), dim3(256), 0,
-                                static_cast<cudaStream_t>(stream), static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), sorted_tok,
-                                expert_off, static_cast<int>(e), static_cast<int>(!x_is_rotated), vec, static_cast<__half*>(xs_f16)));
+    const int grid = grid_for(hal, pairs * (h / 32), 64, 16);
+    // 32-bit item indices while the last item plus one grid step of the loop still fits
+    const bool idx32 = pairs * (h / 32) + static_cast<int64_t>(grid) * 64 < (1ll << 32);
+    if (idx32)
+        QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_gather_kernel<uint32_t>, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                    static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), sorted_tok, expert_off, static_cast<int>(e),
+                                    static_cast<int>(!x_is_rotated), vec, static_cast<__half*>(xs_f16)));
+    else
+        QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_gather_kernel<int64_t>, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                    static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), sorted_tok, expert_off, static_cast<int>(e),
+                                    static_cast<int>(!x_is_rotated), vec, static_cast<__half*>(xs_f16)));
     return QWC_OK;
 }
 
