@@ -569,8 +569,9 @@ def bench_moe(q, hal, peaks):
     return {"us": round(ms * 1e3, 1), "TFLOPs": round(tf, 1), "frac_of_burst_tensor_peak": round(tf / peaks["bf16_tflops"], 3),
             "weight_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1), "frac_of_hbm_peak": round(wbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
             "decode_T8_us": round(ms8 * 1e3, 1),
-            "bound": "the HBM roof (503 MB of expert weights: ~78 us) and the tensor roof (~65 us) are close; neither binds yet: the grouped "
-                     "kernel's pipeline advances one 64-wide K step per ~0.25 us whatever the token count of a tile"}
+            "bound": "the HBM roof (503 MB of expert weights: ~78 us) and the tensor roof (~65 us) are close; neither binds yet: with ~64 "
+                     "tokens per expert every decoded 128 x 64 weight tile feeds one short MMA, so the converters' decode and their "
+                     "hand-offs to the MMA warp set the pace (~0.2 us per 64-wide K step per SM)"}
 
 
 def _max_rel_and_cos(a, b):
