@@ -137,7 +137,8 @@ int qwc_weight_view_init(qwc_weight_view* view, const void* blocks, size_t bank_
 }
 
 // QWGemmShape.family + QWGemm.plan (QWGemm.swift:24-33, 92-133) with the live thresholds of the shipped engine
-// (GEMV at M = 1, batched verify for 2 <= M < 16, tensor GEMM from 16 tokens on; QWGemmF32.swift:413-440).
+// (the families follow the reference: GEMV at M = 1, batched verify for 2 <= M < 16, tensor GEMM from 16 tokens on,
+// QWGemmF32.swift:413-440; the backend is this library's: the tensor-core kernel from 9 tokens on, 4 for HQ8_G32).
 int qwc_gemm_plan(int64_t m, int64_t n, int64_t k, int32_t kind, int32_t bits, int32_t group, int32_t epilogue,
                   int64_t vocab, qwc_plan* out) {
     qwc_clear_error();
@@ -165,7 +166,7 @@ int qwc_gemm_plan(int64_t m, int64_t n, int64_t k, int32_t kind, int32_t bits, i
         out->backend = QWC_BACKEND_ROWWISE;
         out->threads_per_cta = 256;
         snprintf(out->kernel, sizeof(out->kernel), "qwc_gemv_rowwise_%s", fname);
-    } else if (m >= 16 && (epilogue == QWC_EPI_NONE || (n % 2 == 0 && (n / 2) % 64 == 0)) && k % (fmt == FMT_HQ4_G64 ? 256 : 128) == 0) {
+    } else if (m >= qwc_tc_min_tokens(fmt) && (epilogue == QWC_EPI_NONE || (n % 2 == 0 && (n / 2) % 64 == 0)) && k % (fmt == FMT_HQ4_G64 ? 256 : 128) == 0) {
         out->backend = QWC_BACKEND_TCGEN05;
         out->threads_per_cta = 24 * 32;
         snprintf(out->kernel, sizeof(out->kernel), "qwc_gemm_ts_%s_128x%dx64", fname, m <= 64 ? 64 : (m <= 128 ? 128 : 192));

@@ -689,9 +689,9 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
 }
 
-// Out-of-place activation rotation for the prefill path: rows of ldx -> dense rows of k.
+// Staging pre-pass of the tensor path: rows of ldx -> rows of ldo, rotated (FWHT-32 per unit) or copied.
 __global__ void __launch_bounds__(256) qwc_rotate_rows_kernel(const __half* __restrict__ x, int64_t ldx, __half* __restrict__ out,
-                                                              int64_t m, int64_t k) {
+                                                              int64_t ldo, int64_t m, int64_t k, int rotate) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
@@ -699,10 +699,15 @@ __global__ void __launch_bounds__(256) qwc_rotate_rows_kernel(const __half* __re
     const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
     for (int64_t it = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); it < total; it += warps) {
         const int64_t r = it / units, u = it % units;
-        float v = __half2float(x[r * ldx + u * 32 + lane]);
+        const __half xin = x[r * ldx + u * 32 + lane];
+        if (!rotate) {
+            out[r * ldo + u * 32 + lane] = xin;
+            continue;
+        }
+        float v = __half2float(xin);
 #pragma unroll
         for (int h = 1; h < 32; h <<= 1) v = fwht_xor_stage(v, h, (lane & h) != 0);
-        out[r * k + u * 32 + lane] = __float2half_rn(__fmul_rn(v, qwc_inv_sqrt32()));
+        out[r * ldo + u * 32 + lane] = __float2half_rn(__fmul_rn(v, qwc_inv_sqrt32()));
     }
 }
 
@@ -749,15 +754,28 @@ bool qwc_gemm_tc_supported(const qwc_hal* hal, const qwc_weight_view* w, int64_t
     if (fmt == FMT_UNSUPPORTED) return false;
     // SwiGLU epilogues pair 64 gate rows with 64 up rows per tile
     if (epilogue != QWC_EPI_NONE && (w->n % 2 != 0 || (w->n / 2) % (kBM / 2) != 0)) return false;
-    // 16 tokens and more: below that the streaming kernel (register fragments, no decoded operand in memory) wins
-    if (w->k % (fmt == FMT_HQ4_G64 ? 256 : 128) != 0 || m < tune_env("QWC_TC_MIN_M", 16)) return false;
+    // 9 tokens and more (4 for HQ8_G32): below that the streaming kernel (register fragments, no decoded operand in memory)
+    // wins (N = 17408, K = 5120, us per call, stream / tensor: HQ4_G32 8 tokens 19.0 / 19.1, 9 tokens 22.5 / 18.1; HQ8_G32
+    // 2 tokens 19.2 / 23.2, 4 tokens 25.3 / 23.2, 8 tokens 27.8 / 23.2; HQ4_G64 8 tokens 21.7 / 22.7, 9 tokens 23.7 / 22.7)
+    if (w->k % (fmt == FMT_HQ4_G64 ? 256 : 128) != 0 || m < tune_env("QWC_TC_MIN_M", qwc_tc_min_tokens(fmt))) return false;
     if (reinterpret_cast<uintptr_t>(w->blocks) % 16 != 0) return false;
     return tune_env("QWC_NO_TCGEN05", 0) == 0;
 }
 
-// Scratch for the rotated activations when the caller passes standard-basis x.
+// The activations are staged (rotated, or copied when they come rotated) into the caller's workspace when the caller passes
+// standard-basis x, and always below 16 tokens.  Row stride of the staged copy: all CTAs read the same few activation rows
+// at the same time, and measured on B200 those reads crawl when the rows span less than 128 KiB of addresses (N = 17408,
+// K = 5120, rotated x: 25-28 us per call for 1..12 tokens, 15.9 us for 13 tokens and more, and 15.9 us for 8 tokens once the
+// rows lie 20 KB apart), so short staged copies get a row stride that spreads them over 136 KiB.
+static int64_t tc_stage_ld(int64_t k, int64_t m) {
+    const int64_t span = 136 * 1024;
+    if (m * k * 2 >= span) return k;
+    const int64_t ld = (span / (2 * m) + 63) / 64 * 64;
+    return ld > k ? ld : k;
+}
+static bool tc_stages_x(int64_t m, int x_is_rotated) { return !x_is_rotated || m < 16; }
 size_t qwc_gemm_tc_workspace_bytes(const qwc_weight_view* w, int64_t m, int x_is_rotated) {
-    return x_is_rotated ? 0 : static_cast<size_t>(m) * static_cast<size_t>(w->k) * 2;
+    return tc_stages_x(m, x_is_rotated) ? static_cast<size_t>(m) * static_cast<size_t>(tc_stage_ld(w->k, m)) * 2 : 0;
 }
 
 // Shared by the dense door and the grouped (MoE) door: tensor maps, shared-memory budget, launch.
@@ -835,8 +853,8 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
 // Validation shared with the callers that must refuse before their first launch.
 int qwc_gemm_tc_check(const qwc_weight_view* w, const void* x, int64_t ldx, int64_t m, int x_is_rotated, const void* workspace,
                       size_t workspace_bytes) {
-    if (!x_is_rotated) {
-        const size_t need = qwc_gemm_tc_workspace_bytes(w, m, 0);
+    if (tc_stages_x(m, x_is_rotated)) {
+        const size_t need = qwc_gemm_tc_workspace_bytes(w, m, x_is_rotated);
         if (workspace == nullptr || workspace_bytes < need)
             return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace of %zu bytes needed (qwc_gemm_workspace_bytes), got %zu", need, workspace_bytes);
         if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "workspace must be 16-byte aligned");
@@ -851,13 +869,14 @@ int qwc_launch_gemm_tc(const qwc_hal* hal, cudaStream_t st, const qwc_weight_vie
     if (int rc = qwc_gemm_tc_check(w, x, ldx, m, x_is_rotated, workspace, workspace_bytes)) return rc;
     const __half* xr = static_cast<const __half*>(x);
     int64_t ldxr = ldx;
-    if (!x_is_rotated) {
+    if (tc_stages_x(m, x_is_rotated)) {
         int64_t blocks = (m * (w->k / 32) + 7) / 8;
         if (blocks > hal->sm_count * 16) blocks = hal->sm_count * 16;
-        qwc_rotate_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(xr, ldx, static_cast<__half*>(workspace), m, w->k);
+        ldxr = tc_stage_ld(w->k, m);
+        qwc_rotate_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(xr, ldx, static_cast<__half*>(workspace), ldxr, m, w->k,
+                                                                             x_is_rotated ? 0 : 1);
         QWC_CUDA_TRY(cudaGetLastError());
         xr = static_cast<const __half*>(workspace);
-        ldxr = w->k;
     }
     return tc_run(hal, st, w, xr, ldxr, m, y, y_dtype, ldy, nullptr, nullptr, 0, kTsBN, epilogue);
 }

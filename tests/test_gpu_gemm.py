@@ -196,28 +196,51 @@ def test_decode_gemv_bench_shape_properties(hal, oracle):
 
 
 def test_k_sliced_call_needs_and_uses_the_workspace(hal, oracle):
-    # 15 tokens x K = 5120 (the largest batch of the stream kernel; 16 and up take the tensor path): the staged
-    # activations exceed their shared-memory share, K is processed in slices and the raw sums travel through the
-    # caller's workspace.
+    # 15 tokens x K = 5120 on the stream kernel: the staged activations exceed their shared-memory share, K is processed
+    # in slices and the raw sums travel through the caller's workspace.  From 9 tokens on the plain call takes the tensor
+    # path, so the stream kernel is reached here through a SwiGLU epilogue whose halves are not whole 64-row tiles.
     import qwegn_b200 as q
-    n, k, m = 200, 5120, 15
+    k, m, inter = 5120, 15, 96
     fmt = oracle.HQ4_G32
     rng = np.random.default_rng(8)
-    blocks = oracle.quantize(rng.normal(0.0, 0.02, (n, k)).astype(np.float32), fmt)
     x = rng.standard_normal((m, k)).astype(np.float16)
-    view = _bank(q, blocks, "HQ4_G32")
-    assert q.QWGemm.workspaceBytes(hal, view, m) == m * n * 4
-    assert q.QWGemm.workspaceBytes(hal, view, 1) == 0
+    gu = oracle.quantize(rng.normal(0.0, 0.03, (2 * inter, k)).astype(np.float32), fmt)
+    view = _bank(q, gu, "HQ4_G32")
+    assert q.QWGemm.plan(m, 2 * inter, k, q.CONTAINERS["HQ4_G32"], epi=q.EPI_SILU_PAIR_FWHT).backend == 1
+    assert q.QWGemm.workspaceBytes(hal, view, m, q.EPI_SILU_PAIR_FWHT) == m * 2 * inter * 4
+    assert q.QWGemm.workspaceBytes(hal, view, 1, q.EPI_SILU_PAIR_FWHT) == 0
     xd = torch.from_numpy(x).cuda()
-    y = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    h = torch.zeros((m, inter), dtype=torch.float16, device="cuda")
     with pytest.raises(q.QWGemmError) as e:
-        q.QWGemm.encode(hal, view, xd, y)
+        q.QWGemm.encode(hal, view, xd, h, epi=q.EPI_SILU_PAIR_FWHT)
     assert e.value.case == "badShape"
-    assert_matmul_close(_run(q, hal, view, x), oracle.matmul(blocks, fmt, x))
-    gu = oracle.quantize(rng.normal(0.0, 0.03, (128, k)).astype(np.float32), fmt)
     href = oracle.swiglu_f16(oracle.matmul(gu, fmt, x), rotate=True).astype(np.float32)
-    assert_matmul_close(_run(q, hal, _bank(q, gu, "HQ4_G32"), x, epi=q.EPI_SILU_PAIR_FWHT, out_dtype=torch.float16),
-                        href, tight=4e-3)
+    assert_matmul_close(_run(q, hal, view, x, epi=q.EPI_SILU_PAIR_FWHT, out_dtype=torch.float16), href, tight=4e-3)
+
+
+def test_nine_to_fifteen_tokens_take_the_tensor_path_through_a_staged_copy(hal, oracle):
+    # Below 16 tokens the activations are always staged into the workspace (rotated, or copied when they come rotated),
+    # with a row stride that spreads the few rows over 136 KiB of addresses.
+    import qwegn_b200 as q
+    n, k = 200, 5120
+    fmt = oracle.HQ4_G32
+    rng = np.random.default_rng(18)
+    blocks = oracle.quantize(rng.normal(0.0, 0.02, (n, k)).astype(np.float32), fmt)
+    view = _bank(q, blocks, "HQ4_G32")
+    for m in (9, 12, 15):
+        assert q.QWGemm.plan(m, n, k, q.CONTAINERS["HQ4_G32"]).backend == 2
+        x = rng.standard_normal((m, k)).astype(np.float16)
+        for rotated in (False, True):
+            need = q.QWGemm.workspaceBytes(hal, view, m, 0, rotated)
+            assert need >= max(m * k * 2, 136 * 1024)
+            y = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+            with pytest.raises(q.QWGemmError) as e:
+                q.QWGemm.encode(hal, view, torch.from_numpy(x).cuda(), y, x_is_rotated=rotated)
+            assert e.value.case == "badShape"
+        yref = oracle.matmul(blocks, fmt, x)
+        assert_matmul_close(_run(q, hal, view, x), yref)
+        assert_matmul_close(_run(q, hal, view, oracle.fwht32_f16(x), rotated=True), yref)
+    assert hal.device_status() == 0
 
 
 def test_static_weights_mode_gives_identical_results(oracle):
