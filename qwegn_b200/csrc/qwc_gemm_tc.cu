@@ -221,67 +221,107 @@ __device__ __forceinline__ TileInfo tc_get_tile(const TcParams& p, int tile) {
     return t;
 }
 
+// One chunk of TOK (16 or 32) tokens of a SwiGLU epilogue for one epilogue warp.  rr = the warp's TOK accumulator columns
+// (lane = weight row).  The warp parks the TOK / 2 tokens its partner finishes in the exchange buffer (f16, as the reference's
+// threadgroup tile), meets the other three warps, takes its partner's values for the TOK / 2 tokens it finishes itself:
+// h = f16(silu(g) * u), FWHT-32 across the 32 rows the warp holds, store.  All TOK / 2 tokens go through each step side by
+// side: the five butterfly stages of one token are a chain of dependent shuffles (~30 cycles each), and token after token
+// those chains alone took ~1200 cycles per 16 tokens.
+template <int TOK>
+__device__ __forceinline__ void tc_swiglu_chunk(const TcParams& p, const TileInfo& ti, const uint32_t* rr, uint8_t* xch, bool is_up,
+                                                int hrow, int lane, int tok_base) {
+    constexpr int HALF = TOK / 2;
+    constexpr int ROWB = TOK;   // bytes per row of one side of the exchange buffer: HALF f16
+    uint8_t* park = xch + (is_up ? 0 : 64 * ROWB) + hrow * ROWB;          // what this warp gives
+    const uint8_t* take = xch + (is_up ? 64 * ROWB : 0) + hrow * ROWB;    // what it gets
+    {
+        // the gate warps give the upper half of the chunk's tokens, the up warps the lower (selects between constant
+        // register indices: a computed index would put the columns in local memory)
+#pragma unroll
+        for (int v = 0; v < HALF / 8; ++v) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int j = 8 * v + 2 * i;
+                const float a = __uint_as_float(is_up ? rr[j] : rr[HALF + j]), b = __uint_as_float(is_up ? rr[j + 1] : rr[HALF + j + 1]);
+                const __half2 h2 = __floats2half2_rn(a, b);
+                pk[i] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            reinterpret_cast<uint4*>(park)[v] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    uint32_t other[HALF / 2];
+#pragma unroll
+    for (int v = 0; v < HALF / 8; ++v) {
+        const uint4 got = reinterpret_cast<const uint4*>(take)[v];
+        other[4 * v] = got.x; other[4 * v + 1] = got.y; other[4 * v + 2] = got.z; other[4 * v + 3] = got.w;
+    }
+    const int m0 = is_up ? HALF : 0;       // the tokens this warp finishes
+    const int tok0 = tok_base + m0;
+    float h[HALF];
+#pragma unroll
+    for (int jj = 0; jj < HALF; ++jj) {
+        const __half2 o2 = *reinterpret_cast<const __half2*>(&other[jj >> 1]);
+        const float o = (jj & 1) ? __high2float(o2) : __low2float(o2);
+        const float mine = __half2float(__float2half_rn(__uint_as_float(is_up ? rr[HALF + jj] : rr[jj])));
+        const float g = is_up ? o : mine, u = is_up ? mine : o;
+        h[jj] = __half2float(__float2half_rn(__fdividef(g, 1.0f + __expf(-g)) * u));
+    }
+    if (p.epilogue == QWC_EPI_SILU_PAIR_FWHT) {
+#pragma unroll
+        for (int st = 0; st < 5; ++st) {
+            const float sg = (lane >> st) & 1 ? -1.0f : 1.0f;
+            float oh[HALF];
+#pragma unroll
+            for (int jj = 0; jj < HALF; ++jj) oh[jj] = __shfl_xor_sync(0xFFFFFFFFu, h[jj], 1 << st);
+#pragma unroll
+            for (int jj = 0; jj < HALF; ++jj) h[jj] = fmaf(h[jj], sg, oh[jj]);
+        }
+#pragma unroll
+        for (int jj = 0; jj < HALF; ++jj) h[jj] = __fmul_rn(h[jj], qwc_inv_sqrt32());
+    }
+    const int esz = p.y_f16 ? 2 : 4;
+    uint8_t* yrow = static_cast<uint8_t*>(p.y) + (static_cast<int64_t>(ti.x_row0 + tok0) * p.ldy + ti.y_col0 + hrow) * esz;
+    const int64_t ystep = p.ldy * esz;
+#pragma unroll
+    for (int jj = 0; jj < HALF; ++jj) {
+        if (tok0 + jj < ti.x_rows) {
+            if (p.y_f16) *reinterpret_cast<__half*>(yrow) = __float2half_rn(h[jj]);
+            else *reinterpret_cast<float*>(yrow) = __half2float(__float2half_rn(h[jj]));
+        }
+        yrow += ystep;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // the exchange buffer is reused by the next chunk
+}
+
 // Epilogue of one tile for one of the four epilogue warps: taddr = TMEM address of the accumulator's first column in
-// this warp's lane quarter; xch = 2 KB of shared memory (SwiGLU epilogues only).
+// this warp's lane quarter; xch = 4 KB of shared memory (SwiGLU epilogues only).
 __device__ __forceinline__ void tc_epilogue_tile(const TcParams& p, const TileInfo& ti, uint32_t taddr, uint8_t* xch, int quarter,
                                                  int lane) {
     const int wr = quarter * 32 + lane;          // weight row inside the tile
     if (p.epilogue != QWC_EPI_NONE) {
         // SwiGLU epilogues (the reference's qwg_gemm_q4g_h16_swiglu, include/qw_gemm_nax_swiglu.metalh:8-154): TMEM
         // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows, so the two halves of a pair sit in
-        // different warps.  Per 16 tokens each warp parks the 8 tokens its partner will finish (f16, as the
-        // reference's threadgroup tile) in shared memory: the gate warps finish tokens 0..7 with the partner's up
-        // values, the up warps tokens 8..15 with the partner's gate values, so all four warps share the SwiGLU,
-        // the FWHT-32 across the 32 rows a warp holds, and the stores.
+        // different warps.  Per chunk of tokens each warp parks the half its partner will finish in shared memory: the
+        // gate warps finish the lower half with the partner's up values, the up warps the upper half with the partner's
+        // gate values, so all four warps share the SwiGLU, the FWHT-32 across the 32 rows a warp holds, and the stores.
         const bool is_up = quarter >= 2;
         const int hrow = (quarter & 1) * 32 + lane;   // row of h inside the tile
-        uint4* park = reinterpret_cast<uint4*>(xch + (is_up ? 0 : 1024) + hrow * 16);        // what this warp gives
-        const uint4* take = reinterpret_cast<const uint4*>(xch + (is_up ? 1024 : 0) + hrow * 16);   // what it gets
-        const float sgn[5] = {(lane & 1) ? -1.0f : 1.0f, (lane & 2) ? -1.0f : 1.0f, (lane & 4) ? -1.0f : 1.0f,
-                              (lane & 8) ? -1.0f : 1.0f, (lane & 16) ? -1.0f : 1.0f};
-        const int chunks16 = (ti.x_rows + 15) / 16;
+        // chunks of 32 tokens while more than 16 are left (half as many meetings of the four warps), one of 16 at the end
+        int c0 = 0;
 #pragma unroll 1
-        for (int c = 0; c < chunks16; ++c) {
-            uint32_t rr[16];
-            tmem_ld16(taddr + c * 16, rr);
+        for (; ti.x_rows - c0 > 16; c0 += 32) {
+            uint32_t rr[32];
+            tmem_ld32(taddr + c0, rr);
             tmem_ld_wait();
-            {
-                const int g0 = is_up ? 0 : 8;   // the gate warps give tokens 8..15, the up warps tokens 0..7
-                uint32_t pk[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const __half2 h2 = __floats2half2_rn(__uint_as_float(rr[g0 + 2 * i]), __uint_as_float(rr[g0 + 2 * i + 1]));
-                    pk[i] = *reinterpret_cast<const uint32_t*>(&h2);
-                }
-                *park = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            const uint4 got = *take;
-            const uint32_t other[4] = {got.x, got.y, got.z, got.w};
-            const int m0 = is_up ? 8 : 0;       // the tokens this warp finishes
-            const int tok0 = c * 16 + m0;
-            uint8_t* yrow = static_cast<uint8_t*>(p.y) +
-                            (static_cast<int64_t>(ti.x_row0 + tok0) * p.ldy + ti.y_col0 + hrow) * (p.y_f16 ? 2 : 4);
-            const int64_t ystep = p.ldy * (p.y_f16 ? 2 : 4);
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-                const __half2 o2 = *reinterpret_cast<const __half2*>(&other[jj >> 1]);
-                const float o = (jj & 1) ? __high2float(o2) : __low2float(o2);
-                const float mine = __half2float(__float2half_rn(__uint_as_float(rr[m0 + jj])));
-                const float g = is_up ? o : mine, u = is_up ? mine : o;
-                float h = __half2float(__float2half_rn(__fdividef(g, 1.0f + __expf(-g)) * u));
-                if (p.epilogue == QWC_EPI_SILU_PAIR_FWHT) {
-#pragma unroll
-                    for (int st = 0; st < 5; ++st) h = fmaf(h, sgn[st], __shfl_xor_sync(0xFFFFFFFFu, h, 1 << st));
-                    h = __fmul_rn(h, qwc_inv_sqrt32());
-                }
-                if (tok0 + jj < ti.x_rows) {
-                    if (p.y_f16) *reinterpret_cast<__half*>(yrow) = __float2half_rn(h);
-                    else *reinterpret_cast<float*>(yrow) = __half2float(__float2half_rn(h));
-                }
-                yrow += ystep;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");   // the exchange buffer is reused by the next 16 tokens
+            tc_swiglu_chunk<32>(p, ti, rr, xch, is_up, hrow, lane, c0);
+        }
+        if (c0 < ti.x_rows) {
+            uint32_t rr[16];
+            tmem_ld16(taddr + c0, rr);
+            tmem_ld_wait();
+            tc_swiglu_chunk<16>(p, ti, rr, xch, is_up, hrow, lane, c0);
         }
     } else {
     // plain epilogue: lane = weight row, 32 token columns per TMEM load; a lane's stores walk down one output column
@@ -567,6 +607,7 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
         const uint64_t b_d0 = umma_desc_sw128(smem_u32(xt));
         const uint32_t b_lo0 = static_cast<uint32_t>(b_d0), b_hi = static_cast<uint32_t>(b_d0 >> 32);
         const uint32_t b_step = static_cast<uint32_t>(p.x_slot_bytes) >> 4;
+        int next_rows = total_tiles > 0 ? tc_get_tile(p, min(static_cast<int>(blockIdx.x), total_tiles - 1)).x_rows : 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tiles_done) {
             const int as = tiles_done & 1;
             if (tiles_done >= 2 && !mbar_wait_spin(&acc_empty[as], ((tiles_done >> 1) - 1) & 1, abort_flag)) {
@@ -575,7 +616,11 @@ qwc_gemm_ts_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, c
             }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * p.acc_stride);
-            const uint32_t idesc = make_idesc(min(p.acc_stride, (tc_get_tile(p, tile).x_rows + 15) & ~15));
+            const uint32_t idesc = make_idesc(min(p.acc_stride, (next_rows + 15) & ~15));
+            {   // the entry of the tile after this one is fetched now: a list entry is a global-memory round trip
+                const int tn = tile + static_cast<int>(gridDim.x);
+                next_rows = tc_get_tile(p, tn < total_tiles ? tn : tile).x_rows;
+            }
             for (int ks = 0; ks < kstages; ++ks, ++j) {
                 const uint32_t s = j & smask;
                 const bool got_full = mbar_wait_spin(&full[s], (j >> p.stage_shift) & 1u, abort_flag);   // all lanes poll: measured faster than one polling lane
@@ -809,7 +854,7 @@ static int tc_run(const qwc_hal* hal, cudaStream_t st, const qwc_weight_view* w,
     p.m_tiles = static_cast<int>((m + x_tile_rows - 1) / x_tile_rows);
     p.epilogue = epilogue;
     p.up_delta = static_cast<int>(w->n / 2);
-    p.xch_bytes = epilogue == QWC_EPI_NONE ? 0 : (kBM / 2) * 16 * 2;
+    p.xch_bytes = epilogue == QWC_EPI_NONE ? 0 : (kBM / 2) * 32 * 2;   // 64 rows x 16 parked tokens (f16) per side
     p.n_tiles = epilogue == QWC_EPI_NONE ? static_cast<int>((w->n + kBM - 1) / kBM) : static_cast<int>(w->n / kBM);
     const int raw_stage_bytes = ((kBM * p.raw_row_bytes + 127) / 128) * 128;
     p.x_slot_bytes = p.kt_per_stage * x_tile_rows * kBK * 2;
