@@ -152,7 +152,7 @@ int qwc_quantize(qwc_hal* hal, qwc_stream stream, const float* w_f32, int64_t n,
  * y = silu(gate) * up.  SILU_PAIR_FWHT: same, then FWHT-32 along n_out (n_out % 32 == 0).
  * y: f16 or f32 [m, n_out] rows ldy apart.  workspace may be NULL when qwc_gemm_workspace_bytes() is 0.  The workspace holds
  * what the chosen kernel needs: the rotated (or, below 16 tokens, copied) activations of the tensor-core kernel, which takes
- * calls of 9 tokens and more (4 for HQ8_G32), or the K-slice sums of the streaming kernel; 16-byte aligned.  Numeric class of
+ * calls of 9 tokens and more (8 for HQ8_G32), or the K-slice sums of the streaming kernel; 16-byte aligned.  Numeric class of
  * every door: f16 weights (decoded exactly as the reference decodes them) x f16 activations, f32 accumulate. */
 int qwc_gemm(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w, const void* x_f16, int64_t m, int64_t ldx,
              void* y, int32_t y_dtype, int64_t ldy, int32_t epilogue, int32_t x_is_rotated, void* workspace,

@@ -138,7 +138,7 @@ int qwc_weight_view_init(qwc_weight_view* view, const void* blocks, size_t bank_
 
 // QWGemmShape.family + QWGemm.plan (QWGemm.swift:24-33, 92-133) with the live thresholds of the shipped engine
 // (the families follow the reference: GEMV at M = 1, batched verify for 2 <= M < 16, tensor GEMM from 16 tokens on,
-// QWGemmF32.swift:413-440; the backend is this library's: the tensor-core kernel from 9 tokens on, 4 for HQ8_G32).
+// QWGemmF32.swift:413-440; the backend is this library's: the tensor-core kernel from 9 tokens on, 8 for HQ8_G32).
 int qwc_gemm_plan(int64_t m, int64_t n, int64_t k, int32_t kind, int32_t bits, int32_t group, int32_t epilogue,
                   int64_t vocab, qwc_plan* out) {
     qwc_clear_error();

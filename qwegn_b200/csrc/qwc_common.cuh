@@ -67,7 +67,7 @@ int qwc_gemm_args_check_stream(const qwc_hal* hal, const qwc_weight_view* w, con
 // The three containers this library decodes.
 enum QwcFmt : int { FMT_HQ4_G32_M5 = 0, FMT_HQ8_G32 = 1, FMT_HQ4_G64 = 2, FMT_UNSUPPORTED = -1 };
 // Fewest tokens the tensor-core path takes, per format (measured crossover against the streaming kernel).
-inline int qwc_tc_min_tokens(int fmt) { return fmt == FMT_HQ8_G32 ? 4 : 9; }
+inline int qwc_tc_min_tokens(int fmt) { return fmt == FMT_HQ8_G32 ? 8 : 9; }
 
 inline int qwc_fmt_of(const qwc_weight_view& w) {
     if (w.kind == QWC_KIND_HQ4_G32_M5) return FMT_HQ4_G32_M5;

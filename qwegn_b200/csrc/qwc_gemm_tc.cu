@@ -799,9 +799,10 @@ bool qwc_gemm_tc_supported(const qwc_hal* hal, const qwc_weight_view* w, int64_t
     if (fmt == FMT_UNSUPPORTED) return false;
     // SwiGLU epilogues pair 64 gate rows with 64 up rows per tile
     if (epilogue != QWC_EPI_NONE && (w->n % 2 != 0 || (w->n / 2) % (kBM / 2) != 0)) return false;
-    // 9 tokens and more (4 for HQ8_G32): below that the streaming kernel (register fragments, no decoded operand in memory)
+    // 9 tokens and more (8 for HQ8_G32): below that the streaming kernel (register fragments, no decoded operand in memory)
     // wins (N = 17408, K = 5120, us per call, stream / tensor: HQ4_G32 8 tokens 19.0 / 19.1, 9 tokens 22.5 / 18.1; HQ8_G32
-    // 2 tokens 19.2 / 23.2, 4 tokens 25.3 / 23.2, 8 tokens 27.8 / 23.2; HQ4_G64 8 tokens 21.7 / 22.7, 9 tokens 23.7 / 22.7)
+    // 4 tokens 25.3 / 33.5 (with so few activation rows the activation reads of all CTAs land on the same few lines, whatever
+    // the row stride), 8 tokens 27.8 / 23.2; HQ4_G64 8 tokens 21.7 / 22.7, 9 tokens 23.7 / 22.7)
     if (w->k % (fmt == FMT_HQ4_G64 ? 256 : 128) != 0 || m < tune_env("QWC_TC_MIN_M", qwc_tc_min_tokens(fmt))) return false;
     if (reinterpret_cast<uintptr_t>(w->blocks) % 16 != 0) return false;
     return tune_env("QWC_NO_TCGEN05", 0) == 0;
