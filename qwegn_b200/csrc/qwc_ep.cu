@@ -47,12 +47,13 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 
-// "Last CTA done": after every thread's stores are fenced at system scope, one thread per CTA takes a ticket; the CTA
-// that takes the last one resets the ticket and raises `word` (call number) on every peer.
+// "Last CTA done": the CTA's stores are ordered before its barrier; one thread per CTA then fences at system scope
+// (cumulative over what the barrier ordered before it: one fence per CTA, not one per thread) and takes a ticket; the CTA
+// that takes the last one resets the ticket, fences again and raises `word` (call number) on every peer.
 __device__ __forceinline__ void raise_flags_when_grid_done(uint32_t* ticket, const EpPeers& peers, int world, int flag_index, uint32_t epoch) {
-    __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         if (atomicAdd(ticket, 1u) == gridDim.x - 1u) {
             *ticket = 0u;
             __threadfence_system();
