@@ -197,26 +197,26 @@ int qwc_peer_free(qwc_hal* hal, void* ptr);
 /* ---- tensor parallel: row-parallel matmul fused with its all-reduce ---------------------------------------------
  * (No counterpart in the reference, which runs on one device; the format decides the design: a K shard of the bank per
  * rank, f32 partial sums, one sum over the ranks.)  One kernel does both: every CTA stores its partial sums straight
- * into the inbox of every rank (ordinary peer stores over NVLink), raises a flag on every rank, waits (bounded) for the
- * flags of the matching CTAs of the other ranks and sums the world slots of its rows in rank order, so every rank ends
- * with the same bits.  The caller provides peer-mapped memory (qwc_peer_alloc / qwc_peer_open):
- *   inbox[r]: rank r's inbox, f32 [world][m][n];  flags[r]: rank r's flags, u32 [world][qwc_sm_count()], zero before the
- *   first call.  Two inbox / flag buffers are used in turn, so that a fast rank's next call does not overwrite data a
- *   slow rank is still summing, and every call carries a number (the flag value that marks its data as complete).  Either
- *   the host counts: epoch = a value that differs from the previous two calls' and inbox[r] / flags[r] point at the buffer
- *   of THIS call (epoch_state = NULL); or the device counts: epoch_state points at two zero-initialised u32 words in this
- *   rank's memory, inbox[r] / flags[r] point at the FIRST of two buffers inbox_floats / flag_words apart, and the kernel
- *   takes call number *epoch_state + 1, picks the buffer by its parity and stores the new number when it is done -- the
- *   form to use when calls are captured in a CUDA graph and replayed, where host values would repeat.
+ * into the inbox of every rank (ordinary peer stores over NVLink), each as ONE 8-byte store of (value, call number), and
+ * then reads the world slots of its own rows from its own inbox, waiting (bounded) until each carries this call's number,
+ * and sums them in rank order, so every rank ends with the same bits.  No fences and no flags: a slot that carries the
+ * call's number holds the call's value.  The caller provides peer-mapped memory (qwc_peer_alloc / qwc_peer_open):
+ *   inbox[r]: rank r's inbox, [world][m][n] slots of 8 bytes (f32 value, u32 call number), zero before the first call.
+ *   Two inbox buffers are used in turn, so that a fast rank's next call does not overwrite a slot a slow rank has not
+ *   read yet.  Either the host counts: epoch = a non-zero value that differs from the previous two calls' and inbox[r]
+ *   points at the buffer of THIS call (epoch_state = NULL); or the device counts: epoch_state points at two zero-initialised
+ *   u32 words in this rank's memory, inbox[r] points at the FIRST of two buffers inbox_floats apart, and the kernel takes
+ *   call number *epoch_state + 1, picks the buffer by its parity and stores the new number when it is done -- the form to
+ *   use when calls are captured in a CUDA graph and replayed, where host values would repeat.
  *   Every rank of the group must make the same calls (same shapes, same order). */
 typedef struct {
     int32_t rank, world;      /* 2 <= world <= 8 */
     uint32_t epoch;
-    int32_t reserved;         /* > 0: limit of the wait for the peers' flags in microseconds (0: the library's default, 1 s) */
-    void* inbox[8];
-    void* flags[8];
-    int64_t inbox_floats;     /* capacity of one inbox buffer in floats (>= world * m * n) */
-    int64_t flag_words;       /* capacity of one flag buffer in words (>= world * qwc_sm_count()) */
+    int32_t reserved;         /* > 0: limit of the wait for the peers' values in microseconds (0: the library's default, 1 s) */
+    void* inbox[8];           /* 8-byte aligned */
+    void* flags[8];           /* not used (kept for the layout of earlier callers) */
+    int64_t inbox_floats;     /* capacity of one inbox buffer in floats: even, >= 2 * world * m * n */
+    int64_t flag_words;       /* not used */
     void* epoch_state;        /* NULL, or this rank's device-side call counter (two u32 words, zero before the first call) */
 } qwc_allreduce_ctx;
 

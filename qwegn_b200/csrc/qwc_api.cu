@@ -308,10 +308,12 @@ int qwc_gemm_allreduce(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* w
     if (m > 8 || row_bytes % 16 != 0 || reinterpret_cast<uintptr_t>(w->blocks) % 16 != 0 || qwc_gemv_workspace_bytes(w, m) != 0)
         return qwc_fail(QWC_ERR_BLOCKED, "the fused all-reduce takes m <= 8, 16-byte bank rows and one K slice");
     for (int r = 0; r < ctx->world; ++r)
-        if (!ctx->inbox[r] || !ctx->flags[r]) return qwc_fail(QWC_ERR_BAD_SHAPE, "peer buffer %d is null", r);
-    if (ctx->inbox_floats < static_cast<int64_t>(ctx->world) * m * w->n || ctx->flag_words < static_cast<int64_t>(ctx->world) * hal->sm_count)
-        return qwc_fail(QWC_ERR_BAD_SHAPE, "peer buffers too small: need %lld floats and %lld flag words",
-                        (long long)(static_cast<int64_t>(ctx->world) * m * w->n), (long long)(static_cast<int64_t>(ctx->world) * hal->sm_count));
+        if (!ctx->inbox[r] || reinterpret_cast<uintptr_t>(ctx->inbox[r]) % 8 != 0)
+            return qwc_fail(QWC_ERR_BAD_SHAPE, "inbox %d is null or not 8-byte aligned", r);
+    if (ctx->inbox_floats < 2 * static_cast<int64_t>(ctx->world) * m * w->n || ctx->inbox_floats % 2 != 0)
+        return qwc_fail(QWC_ERR_BAD_SHAPE, "inbox too small: an even number of at least %lld floats is needed (two per slot)",
+                        (long long)(2 * static_cast<int64_t>(ctx->world) * m * w->n));
+    if (ctx->epoch_state == nullptr && ctx->epoch == 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "call number 0 marks an empty slot: count from 1");
     return qwc_launch_gemv_ar(hal, static_cast<cudaStream_t>(stream), w, x_f16, m, ldx, y, y_dtype, ldy, QWC_EPI_NONE, x_is_rotated,
                               nullptr, 0, ctx);
 }

@@ -99,12 +99,11 @@ struct GemvParams {
     int seg_grid, seg_cols;   // host side: capacity of the list (= grid) and output columns per entry
     // fused one-shot all-reduce over peer memory (row-parallel shards of a tensor-parallel group; ar_world > 1):
     int ar_world, ar_rank;
-    uint32_t ar_epoch;        // call number: the flag value that marks this call's data as complete
+    uint32_t ar_epoch;        // call number: the tag that marks a slot as holding this call's value (never 0)
     uint64_t ar_wait_ns;      // limit of the peer wait (0: the library's default)
     uint32_t* ar_state;       // device-side call counter (see qwc_allreduce_ctx::epoch_state); null: ar_epoch comes from the host
-    int64_t ar_inbox_stride, ar_flag_stride;   // distance between the two buffers (floats / words) when the kernel picks the buffer
-    float* ar_inbox[8];       // rank r's inbox for this call: [world][m][n] f32; slot [s] is written by rank s
-    uint32_t* ar_flags[8];    // rank r's flags for this call: [world][grid]; word [s][cta] is written by CTA cta of rank s
+    int64_t ar_inbox_stride;  // distance between the two inbox buffers (floats) when the kernel picks the buffer
+    float* ar_inbox[8];       // rank r's inbox for this call: [world][m][n] slots of (f32 value, u32 call number); [s] is written by rank s
 };
 
 // Shared-memory loads by 32-bit shared-window address (no 64-bit pointer arithmetic in the inner loop).
@@ -502,11 +501,10 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     // Fused all-reduce with a device-side call counter: the call number is read here (the previous call of the stream
     // has completed), and its parity picks one of the two inbox / flag buffers.
     uint32_t ar_epoch = p.ar_epoch;
-    int64_t ar_inbox_ofs = 0, ar_flag_ofs = 0;
+    int64_t ar_inbox_ofs = 0;
     if (SUB == 1 && p.ar_world > 1 && p.ar_state != nullptr) {
         ar_epoch = *reinterpret_cast<volatile uint32_t*>(p.ar_state) + 1u;
         ar_inbox_ofs = (ar_epoch & 1u) ? p.ar_inbox_stride : 0;
-        ar_flag_ofs = (ar_epoch & 1u) ? p.ar_flag_stride : 0;
     }
     for (int base = warp * 8; base < items; base += 2 * kItemStride) {
         const uint4 ra = load_item(ia), rb4 = load_item(ib);
@@ -658,9 +656,13 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                         if (SUB == 4) {
                             hval[ot][nt][i] = __half2float(__float2half_rn(v));
                         } else if (SUB == 1 && p.ar_world > 1) {
-                            // the partial sum goes straight into every rank's inbox (peer stores over NVLink), its own too
-                            const int64_t o = ar_inbox_ofs + (static_cast<int64_t>(p.ar_rank) * M_ + tok) * p.n + row;
-                            for (int r = 0; r < p.ar_world; ++r) p.ar_inbox[r][o] = v;
+                            // the partial sum goes straight into every rank's inbox (peer stores over NVLink), its own too,
+                            // as ONE 8-byte store of (value, call number): the receiver polls the slot itself, so neither
+                            // side needs a fence or a flag
+                            const int64_t o = ar_inbox_ofs + 2 * ((static_cast<int64_t>(p.ar_rank) * M_ + tok) * p.n + row);
+                            for (int r = 0; r < p.ar_world; ++r)
+                                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.ar_inbox[r] + o), "r"(__float_as_uint(v)),
+                                             "r"(ar_epoch) : "memory");
                         } else {
                             const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
                             if (p.y_f16) static_cast<__half*>(Y_)[o] = __float2half_rn(v);
@@ -698,47 +700,44 @@ qwc_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     }
 
     if (SUB == 1 && p.ar_world > 1) {
-        // ---- fused one-shot all-reduce: CTA c of every rank owns the same output rows, so CTA c only has to meet the
-        // CTAs c of the other ranks.  Pushes (above) -> system fence -> flag to every rank -> wait for every rank's flag
-        // -> sum the world slots of this CTA's rows in rank order (same bits on every rank).  All waits are bounded.
-        // The pushes of all consumer threads are ordered before the barrier; the threads that raise the flags then fence at
-        // system scope (cumulative over what the barrier ordered before them) and store the flag with release semantics.
-        // One fence per flag-raising thread instead of one per consumer thread: 512 system fences per CTA cost microseconds.
-        named_bar_sync(11, kConsumerWarps * 32);
-        const int cta = static_cast<int>(blockIdx.x), grid = static_cast<int>(gridDim.x);
-        if (threadIdx.x < static_cast<unsigned>(p.ar_world)) {
-            __threadfence_system();
-            uint32_t* f = p.ar_flags[threadIdx.x] + ar_flag_ofs + p.ar_rank * grid + cta;
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(ar_epoch) : "memory");
-            const uint32_t* mine = p.ar_flags[p.ar_rank] + ar_flag_ofs + threadIdx.x * grid + cta;
-            // bounded by elapsed time: a peer that never raises its flag (it failed, or it never made the call) costs this
-            // rank the limit once, then the status word says so and the kernel finishes with whatever the inbox holds
-            bool got = false;
-            const uint64_t t0 = qwc_globaltimer_ns();
+        // ---- fused one-shot all-reduce: CTA c of every rank owns the same output rows, so a thread only has to wait for
+        // the slots of its own (token, row) from every rank: each slot is an 8-byte (value, call number) pair stored whole
+        // by its producer, so a slot that carries this call's number holds this call's value -- no fences, no flags (a
+        // system-scope fence or release / acquire access costs microseconds here; this form costs one NVLink latency).
+        // The world slots are summed in rank order (same bits on every rank).  The wait is bounded in time.
+        {
+            const int rows_cta = re - rb;
+            const float* inbox = p.ar_inbox[p.ar_rank] + ar_inbox_ofs;
             const uint64_t limit = p.ar_wait_ns != 0 ? p.ar_wait_ns : static_cast<uint64_t>(QWC_WAIT_LIMIT_NS);
-            for (uint32_t spin = 0;; ++spin) {
-                uint32_t v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-                if (v == ar_epoch) {
-                    got = true;
-                    break;
+            uint64_t t0 = 0;
+            bool gave_up = false;
+            for (int i = threadIdx.x; i < rows_cta * M_; i += kConsumerWarps * 32) {
+                const int tok = i / rows_cta, row = rb + (i - tok * rows_cta);
+                float sum = 0.0f;
+                for (int r = 0; r < p.ar_world; ++r) {
+                    const float* slot = inbox + 2 * ((static_cast<int64_t>(r) * M_ + tok) * p.n + row);
+                    uint32_t val = 0, tag = 0;
+                    for (uint32_t spin = 0; !gave_up; ++spin) {
+                        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(val), "=r"(tag) : "l"(slot) : "memory");
+                        if (tag == ar_epoch) break;
+                        // a peer that never stores (it failed, or it never made the call) costs this rank the limit once;
+                        // then the status word says so and the kernel finishes with whatever the inbox holds
+                        if ((spin & 31u) == 31u) {
+                            const uint64_t now = qwc_globaltimer_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > limit) gave_up = true;
+                        }
+                        if (spin > 16) __nanosleep(spin < 256 ? 40 : 250);
+                    }
+                    sum += __uint_as_float(val);
                 }
-                if ((spin & 15u) == 15u && qwc_globaltimer_ns() - t0 > limit) break;
-                __nanosleep(spin < 256 ? 40 : 250);
+                const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
+                if (p.y_f16) static_cast<__half*>(Y_)[o] = __float2half_rn(sum);
+                else static_cast<float*>(Y_)[o] = sum;
             }
-            if (!got) atomicCAS(p.status, 0, QWC_DEV_WAIT_PEER_TIMEOUT);
+            if (gave_up) atomicCAS(p.status, 0, QWC_DEV_WAIT_PEER_TIMEOUT);
         }
-        named_bar_sync(11, kConsumerWarps * 32);
-        const int rows_cta = re - rb;
-        const float* inbox = p.ar_inbox[p.ar_rank] + ar_inbox_ofs;
-        for (int i = threadIdx.x; i < rows_cta * M_; i += kConsumerWarps * 32) {
-            const int tok = i / rows_cta, row = rb + (i - tok * rows_cta);
-            float sum = 0.0f;
-            for (int r = 0; r < p.ar_world; ++r) sum += __ldcg(inbox + (static_cast<int64_t>(r) * M_ + tok) * p.n + row);
-            const int64_t o = static_cast<int64_t>(tok) * p.ldy + row;
-            if (p.y_f16) static_cast<__half*>(Y_)[o] = __float2half_rn(sum);
-            else static_cast<float*>(Y_)[o] = sum;
-        }
+        const int grid = static_cast<int>(gridDim.x);
         if (p.ar_state != nullptr) {
             // the last CTA to finish publishes the call number: every CTA read the old one before it got here
             named_bar_sync(11, kConsumerWarps * 32);
@@ -1152,10 +1151,8 @@ int qwc_launch_gemv_ar(const qwc_hal* hal, cudaStream_t st, const qwc_weight_vie
         p.ar_wait_ns = ar->reserved > 0 ? static_cast<uint64_t>(ar->reserved) * 1000ull : 0ull;
         p.ar_state = static_cast<uint32_t*>(ar->epoch_state);
         p.ar_inbox_stride = ar->inbox_floats;
-        p.ar_flag_stride = ar->flag_words;
         for (int r = 0; r < ar->world && r < 8; ++r) {
             p.ar_inbox[r] = static_cast<float*>(ar->inbox[r]);
-            p.ar_flags[r] = static_cast<uint32_t*>(ar->flags[r]);
         }
     }
     const int fmt = qwc_fmt_of(*w);

@@ -187,9 +187,9 @@ _lib.register("qwc_gemm_allreduce", ctypes.c_int, [ctypes.c_void_p, ctypes.c_voi
 
 class FusedRowParallelLinear(RowParallelLinear):
     """Row-parallel matmul whose kernel also does the all-reduce (decode / verify, m <= 8): every CTA pushes its partial
-    sums into all ranks' inboxes over NVLink, flags, waits for the matching CTAs of the other ranks and sums in rank
-    order.  The inboxes and flags are peer-mapped buffers (PeerBuffer; two of each, used in turn); the call number is counted
-    on the device, so the calls can be captured in a CUDA graph and replayed.  Shapes the fused form does not take fall
+    sums into all ranks' inboxes over NVLink as (value, call number) pairs, waits until the slots of its own rows carry the
+    call's number and sums them in rank order.  The inboxes are peer-mapped buffers (PeerBuffer; two, used in turn); the call
+    number is counted on the device, so the calls can be captured in a CUDA graph and replayed.  Shapes the fused form does not take fall
     back to the matmul + NCCL all-reduce of the base class."""
 
     def __init__(self, hal: QWHal, shard: torch.Tensor, n: int, k_local: int, cont: ContainerKind,
@@ -199,17 +199,15 @@ class FusedRowParallelLinear(RowParallelLinear):
         self.rank = dist.get_rank(grp)
         dev = torch.device("cuda", hal.device.index)
         self.max_m, self.sms = max_m, hal.sm_count
-        in_floats, fl_words = self.world * max_m * n, self.world * self.sms
+        in_floats = 2 * self.world * max_m * n                    # a slot is (f32 value, u32 call number)
         self.inbox = PeerBuffer(hal, 2 * in_floats * 4, grp)     # two buffers, used in turn
-        self.flags = PeerBuffer(hal, 2 * fl_words * 4, grp)
         self.state = torch.zeros(2, dtype=torch.int32, device=dev)   # device-side call counter + ticket
         torch.cuda.synchronize(dev)
         self.ctx = AllReduceCtxC()
         self.ctx.rank, self.ctx.world, self.ctx.epoch = self.rank, self.world, 0
         for r in range(self.world):
             self.ctx.inbox[r] = self.inbox.ptrs[r]
-            self.ctx.flags[r] = self.flags.ptrs[r]
-        self.ctx.inbox_floats, self.ctx.flag_words = in_floats, fl_words
+        self.ctx.inbox_floats, self.ctx.flag_words = in_floats, 0
         self.ctx.epoch_state = self.state.data_ptr()
 
     def forward(self, x_local: torch.Tensor, y: torch.Tensor, x_is_rotated: bool = False,

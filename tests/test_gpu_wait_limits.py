@@ -1,7 +1,7 @@
 """A bounded device wait that runs out: the kernel must return by itself, report through the status word and leave the
 context usable.  The failure is made on the host side of the protocol (a peer that never makes the call), never by a
 fault: the fused row-parallel matmul + all-reduce is called for a world of two with both ranks' inboxes and flags in
-local memory, and the second rank is simply never launched, so its flags are never raised."""
+local memory, and the second rank is simply never launched, so its slots never carry the call's number."""
 import ctypes
 import time
 
@@ -28,16 +28,13 @@ def test_peer_wait_runs_out_and_the_context_stays_usable(oracle):
     x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float16)).cuda()
     y = torch.zeros((m, n), dtype=torch.float32, device="cuda")
     world, sms = 2, hal.sm_count
-    inbox = torch.zeros((world, world, m, n), dtype=torch.float32, device="cuda")    # [owner rank][source rank][m][n]
-    flags = torch.zeros((world, world, sms), dtype=torch.int32, device="cuda")
+    inbox = torch.zeros((world, world, m, n, 2), dtype=torch.float32, device="cuda")    # [owner rank][source rank][m][n] slots of (value, call number)
     ctx = AllReduceCtxC()
     ctx.rank, ctx.world, ctx.epoch = 0, world, 1
     ctx.reserved = 20000     # wait limit in microseconds: 20 ms instead of the default second
     for r in range(world):
         ctx.inbox[r] = inbox[r].data_ptr()
-        ctx.flags[r] = flags[r].data_ptr()
-    ctx.inbox_floats = world * m * n
-    ctx.flag_words = world * sms
+    ctx.inbox_floats = 2 * world * m * n
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     rc = lib.qwc_gemm_allreduce(hal.handle, _stream_ptr(None), ctypes.byref(view.c), x.data_ptr(), m, k, y.data_ptr(), 1, n, 0,
@@ -49,7 +46,8 @@ def test_peer_wait_runs_out_and_the_context_stays_usable(oracle):
     assert elapsed < 5.0, elapsed         # it gave up after the limit, not after the default second per CTA wave
     # rank 0's own partial sums did arrive in its inbox slot: the matmul itself ran
     yref = oracle.matmul(blocks, oracle.HQ4_G32, x.cpu().numpy())
-    assert_matmul_close(inbox[0, 0].cpu().numpy(), yref)
+    assert_matmul_close(inbox[0, 0, :, :, 0].cpu().numpy(), yref)
+    assert (inbox[0, 0, :, :, 1].view(torch.int32) == 1).all()       # every slot of rank 0 carries the call's number
     hal.close()
     # the context is intact: a fresh hal computes the same product
     hal2 = q.QWHal(0)
