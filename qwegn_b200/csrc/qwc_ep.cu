@@ -38,12 +38,14 @@ struct EpPeers {
     uint32_t* flags[kMaxWorld];   // rank r's flags: u32 [2][world] (dispatch arrived / results arrived, per source) + 2 tickets
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Flag accesses are relaxed (volatile) and the ordering comes from ONE system-scope fence on each side: a system fence, a
+// release store or an acquire load each cost about 3.5 us on B200, and a poll loop of acquire loads pays that per poll.
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
     uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
 
@@ -57,7 +59,7 @@ __device__ __forceinline__ void raise_flags_when_grid_done(uint32_t* ticket, con
         if (atomicAdd(ticket, 1u) == gridDim.x - 1u) {
             *ticket = 0u;
             __threadfence_system();
-            for (int d = 0; d < world; ++d) st_release_sys(peers.flags[d] + flag_index, epoch);
+            for (int d = 0; d < world; ++d) st_relaxed_sys(peers.flags[d] + flag_index, epoch);   // after the fence above
         }
     }
 }
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(32) qwc_ep_wait_kernel(const uint32_t* flags, 
         bool got = false;
         const uint64_t t0 = qwc_globaltimer_ns();
         for (uint32_t spin = 0;; ++spin) {
-            if (ld_acquire_sys(flags + base + lane) == epoch) {
+            if (ld_relaxed_sys(flags + base + lane) == epoch) {
                 got = true;
                 break;
             }
@@ -88,6 +90,7 @@ __global__ void __launch_bounds__(32) qwc_ep_wait_kernel(const uint32_t* flags, 
             __nanosleep(spin < 256 ? 40 : 250);
         }
         if (!got) atomicCAS(status, 0, QWC_DEV_WAIT_PEER_TIMEOUT);
+        __threadfence_system();   // acquire side: what the peer wrote before it raised the flag is ordered before what follows
     }
     __syncwarp();
     if (bump && epoch_state != nullptr && lane == 0) *reinterpret_cast<volatile uint32_t*>(epoch_state) = epoch;
