@@ -630,7 +630,8 @@ def bench_parallel(q, hal, rank, world, dist, peaks):
                 bad = (d > 1e-2 * float(ref.double().abs().max())).any(dim=1).nonzero().flatten()
                 if bad.numel():
                     where = f"; {bad.numel()} of {got.shape[0]} rows off, first {int(bad[0])}, last {int(bad[-1])}"
-            msg = f"parity check failed on rank {rank}: {name}: max-rel {err:.3e}, cosine {cos:.6f}{where}"
+            msg = (f"parity check failed on rank {rank}: {name}: max-rel {err:.3e}, cosine {cos:.6f}{where}; "
+                   f"kernel status word {hal.device_status()}")
             if attempt == 1 or recompute is None:
                 raise RuntimeError(msg)
             first = {"parity_ok": False, "max_rel_err": round(err, 6), "cosine": round(cos, 7), "where": where.lstrip("; "),
