@@ -471,6 +471,8 @@ __global__ void __launch_bounds__(512) qwc_moe_decode_plan_kernel(const int32_t*
 // 8t..8t+7 (one 16-byte load), rotates with three in-lane butterfly stages and two xor-shuffle stages (the
 // reference's h = 1, 2, 4, 8, 16 order) and writes one 16-byte chunk.  vec != 0 needs 16-byte aligned rows.
 // IdxT = uint32_t while pairs * units fits (the item index is divided per item: 32-bit division is several times cheaper).
+// sorted_tok == nullptr: rows in place (row p of the output is row p of x), `e` rows in all: the rotate-once pre-pass of
+// the row-copy form below.
 template <typename IdxT>
 __global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __restrict__ x, int64_t ldx, int h,
                                                              const int32_t* __restrict__ sorted_tok,
@@ -479,7 +481,7 @@ __global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __res
     pdl_enter();
     const int lane = threadIdx.x & 31, t4 = lane & 3, q8 = lane >> 2;
     const int units = h / 32;
-    const IdxT total = static_cast<IdxT>(expert_off[e]) * static_cast<IdxT>(units);
+    const IdxT total = static_cast<IdxT>(sorted_tok != nullptr ? expert_off[e] : e) * static_cast<IdxT>(units);
     const IdxT step = static_cast<IdxT>(gridDim.x) * (blockDim.x >> 5) * 8;
     for (IdxT base = (static_cast<IdxT>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 8; base < total; base += step) {
         const IdxT it = base + q8;
@@ -487,7 +489,7 @@ __global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __res
         const IdxT prq = live ? it / static_cast<IdxT>(units) : 0;
         const int u = live ? static_cast<int>(it - prq * static_cast<IdxT>(units)) : 0;
         const int64_t pr = static_cast<int64_t>(prq);
-        const __half* src = x + static_cast<int64_t>(live ? sorted_tok[pr] : 0) * ldx + u * 32 + 8 * t4;
+        const __half* src = x + static_cast<int64_t>(live ? (sorted_tok != nullptr ? sorted_tok[pr] : static_cast<int32_t>(pr)) : 0) * ldx + u * 32 + 8 * t4;
         uint4 raw = make_uint4(0, 0, 0, 0);
         if (live) {
             if (vec) raw = *reinterpret_cast<const uint4*>(src);
@@ -524,6 +526,32 @@ __global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __res
                              *reinterpret_cast<uint32_t*>(&hv[2]), *reinterpret_cast<uint32_t*>(&hv[3]));
         }
         if (live) *reinterpret_cast<uint4*>(xs + pr * h + u * 32 + 8 * t4) = raw;
+    }
+}
+
+// xs[p, :] = xr[sorted_tok[p], :] for rows that are rotated already: one warp per sorted row, 16 bytes per lane and step, four
+// steps in flight.  A token's row is rotated once (not once per route) and the gather is a plain copy; rows and both bases
+// 16-byte aligned, h a multiple of 8.
+__global__ void __launch_bounds__(256) qwc_moe_gather_rows_kernel(const __half* __restrict__ xr, int64_t ldx, int h,
+                                                                  const int32_t* __restrict__ sorted_tok,
+                                                                  const int32_t* __restrict__ expert_off, int e, __half* __restrict__ xs) {
+    pdl_enter();
+    const int lane = threadIdx.x & 31;
+    const int rows = expert_off[e];
+    const int nwarps = static_cast<int>(gridDim.x) * (blockDim.x >> 5);
+    const int chunks = h / 8;   // 16-byte chunks per row
+    for (int pr = static_cast<int>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); pr < rows; pr += nwarps) {
+        const uint4* src = reinterpret_cast<const uint4*>(xr + static_cast<int64_t>(sorted_tok[pr]) * ldx);
+        uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<int64_t>(pr) * h);
+        int c = lane;
+        for (; c + 96 < chunks; c += 128) {
+            const uint4 a = src[c], b = src[c + 32], cc = src[c + 64], d = src[c + 96];
+            dst[c] = a;
+            dst[c + 32] = b;
+            dst[c + 64] = cc;
+            dst[c + 96] = d;
+        }
+        for (; c < chunks; c += 32) dst[c] = src[c];
     }
 }
 
@@ -780,8 +808,21 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
     return QWC_OK;
 }
 
+static int moe_gather_impl(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t ldx, int64_t h, const int32_t* sorted_tok,
+                           const int32_t* expert_off, int64_t e, int64_t pairs, int32_t x_is_rotated, void* xs_f16, int64_t t,
+                           void* tmp, size_t tmp_bytes);
+
 int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t ldx, int64_t h, const int32_t* sorted_tok,
                    const int32_t* expert_off, int64_t e, int64_t pairs, int32_t x_is_rotated, void* xs_f16) {
+    return moe_gather_impl(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, xs_f16, 0, nullptr, 0);
+}
+
+// t > 0 with a temp of t * h f16 (16-byte aligned): standard-basis rows are rotated once per token into the temp and the gather
+// is a row copy (a token has k routes: the per-route rotation of the one-pass kernel was k times the butterfly work and
+// bounded that kernel by its instruction stream, 27 us at 2048 tokens x 8 routes x 2048 wide against ~10 us of copying).
+static int moe_gather_impl(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t ldx, int64_t h, const int32_t* sorted_tok,
+                           const int32_t* expert_off, int64_t e, int64_t pairs, int32_t x_is_rotated, void* xs_f16, int64_t t,
+                           void* tmp, size_t tmp_bytes) {
     qwc_clear_error();
     if (!hal) return qwc_fail(QWC_ERR_BAD_SHAPE, "hal is null");
     if (h <= 0 || h % 32 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "hidden=%lld must be a positive multiple of 32", (long long)h);
@@ -790,6 +831,25 @@ int qwc_moe_gather(qwc_hal* hal, qwc_stream stream, const void* x_f16, int64_t l
     if (!x_f16 || !sorted_tok || !expert_off || !xs_f16) return qwc_fail(QWC_ERR_BAD_SHAPE, "null buffer");
     const int vec = reinterpret_cast<uintptr_t>(x_f16) % 16 == 0 && ldx % 8 == 0;
     if (reinterpret_cast<uintptr_t>(xs_f16) % 16 != 0) return qwc_fail(QWC_ERR_BAD_SHAPE, "xs must be 16-byte aligned");
+    const bool aligned_out = h % 8 == 0;
+    const bool temp_ok = t > 0 && tmp != nullptr && reinterpret_cast<uintptr_t>(tmp) % 16 == 0 &&
+                         tmp_bytes >= static_cast<size_t>(t) * static_cast<size_t>(h) * 2 && t * (h / 32) < (1ll << 31);
+    if (aligned_out && pairs < (1ll << 31) && ((x_is_rotated && vec) || (!x_is_rotated && temp_ok && pairs > t))) {
+        const __half* rows_src = static_cast<const __half*>(x_f16);
+        int64_t rows_ld = ldx;
+        if (!x_is_rotated) {
+            const int g0 = grid_for(hal, t * (h / 32), 64, 16);
+            QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_gather_kernel<uint32_t>, dim3(g0), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                        static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), static_cast<const int32_t*>(nullptr),
+                                        expert_off, static_cast<int>(t), 1, vec, static_cast<__half*>(tmp)));
+            rows_src = static_cast<const __half*>(tmp);
+            rows_ld = h;
+        }
+        const int g1 = grid_for(hal, pairs, 8, 8);
+        QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_gather_rows_kernel, dim3(g1), dim3(256), 0, static_cast<cudaStream_t>(stream), rows_src, rows_ld,
+                                    static_cast<int>(h), sorted_tok, expert_off, static_cast<int>(e), static_cast<__half*>(xs_f16)));
+        return QWC_OK;
+    }
     const int grid = grid_for(hal, pairs * (h / 32), 64, 16);
     // 32-bit item indices while the last item plus one grid step of the loop still fits
     const bool idx32 = pairs * (h / 32) + static_cast<int64_t>(grid) * 64 < (1ll << 32);
@@ -966,7 +1026,10 @@ int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank
     const int32_t gu_epi = inter % 64 == 0 ? QWC_EPI_SILU_PAIR_FWHT : QWC_EPI_NONE;
     if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h, gu_epi,
                                   tiles_gu, tiles_dn, tile_counts))) return rc;
-    if ((rc = qwc_moe_gather(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs))) return rc;
+    // the gate/up region of the scratch is idle until the gate/up GEMM writes it (never, with the fused epilogue): it holds the
+    // rotated copy of x that the row-copy gather reads
+    if ((rc = moe_gather_impl(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs, t, sc + L.gu,
+                              static_cast<size_t>(pairs) * 2 * inter * 2))) return rc;
     const int32_t xrows = qwc_moe_tile_rows(pairs, e);
     if (gu_epi != QWC_EPI_NONE) {
         if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_gu, sc + L.xs, pairs, tiles_gu, tile_counts, qwc_moe_max_tiles(pairs, e, 2 * inter),
