@@ -294,6 +294,75 @@ __global__ void __launch_bounds__(512) qwc_moe_place_kernel(const int32_t* __res
     }
 }
 
+// xs[p, :] = rot(x[sorted_tok[p], :]).  A quad handles one (sorted row, 32-element unit): lane t holds elements
+// 8t..8t+7 (one 16-byte load), rotates with three in-lane butterfly stages and two xor-shuffle stages (the
+// reference's h = 1, 2, 4, 8, 16 order) and writes one 16-byte chunk.  vec != 0 needs 16-byte aligned rows.
+// IdxT = uint32_t while pairs * units fits (the item index is divided per item: 32-bit division is several times cheaper).
+// sorted_tok == nullptr: rows in place (row p of the output is row p of x): the rotate-once pre-pass of the row-copy gather.
+// Block `block` of `nblocks` blocks of 256 threads.
+template <typename IdxT>
+__device__ __forceinline__ void moe_gather_items(const __half* __restrict__ x, int64_t ldx, int h, const int32_t* __restrict__ sorted_tok,
+                                                 IdxT rows, int rotate, int vec, __half* __restrict__ xs, int block, int nblocks) {
+    const int lane = threadIdx.x & 31, t4 = lane & 3, q8 = lane >> 2;
+    const int units = h / 32;
+    const IdxT total = rows * static_cast<IdxT>(units);
+    const IdxT step = static_cast<IdxT>(nblocks) * (blockDim.x >> 5) * 8;
+    for (IdxT base = (static_cast<IdxT>(block) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 8; base < total; base += step) {
+        const IdxT it = base + q8;
+        const bool live = it < total;
+        const IdxT prq = live ? it / static_cast<IdxT>(units) : 0;
+        const int u = live ? static_cast<int>(it - prq * static_cast<IdxT>(units)) : 0;
+        const int64_t pr = static_cast<int64_t>(prq);
+        const __half* src = x + static_cast<int64_t>(live ? (sorted_tok != nullptr ? sorted_tok[pr] : static_cast<int32_t>(pr)) : 0) * ldx + u * 32 + 8 * t4;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (live) {
+            if (vec) raw = *reinterpret_cast<const uint4*>(src);
+            else {
+                __half tmp[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) tmp[i] = src[i];
+                raw = *reinterpret_cast<const uint4*>(tmp);
+            }
+        }
+        if (rotate) {
+            __half2 hv[4] = {*reinterpret_cast<__half2*>(&raw.x), *reinterpret_cast<__half2*>(&raw.y),
+                             *reinterpret_cast<__half2*>(&raw.z), *reinterpret_cast<__half2*>(&raw.w)};
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(hv[i]); f[2 * i + 1] = __high2float(hv[i]); }
+#pragma unroll
+            for (int s = 1; s < 8; s <<= 1)
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if ((i & s) == 0) {
+                        const float a = f[i], b = f[i + s];
+                        f[i] = __fadd_rn(a, b);
+                        f[i + s] = __fsub_rn(a, b);
+                    }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 1, (t4 & 1) != 0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 2, (t4 & 2) != 0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                hv[i] = __floats2half2_rn(__fmul_rn(f[2 * i], qwc_inv_sqrt32()), __fmul_rn(f[2 * i + 1], qwc_inv_sqrt32()));
+            raw = make_uint4(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[1]),
+                             *reinterpret_cast<uint32_t*>(&hv[2]), *reinterpret_cast<uint32_t*>(&hv[3]));
+        }
+        if (live) *reinterpret_cast<uint4*>(xs + pr * h + u * 32 + 8 * t4) = raw;
+    }
+}
+
+template <typename IdxT>
+__global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __restrict__ x, int64_t ldx, int h,
+                                                             const int32_t* __restrict__ sorted_tok,
+                                                             const int32_t* __restrict__ expert_off, int e, int rotate, int vec,
+                                                             __half* __restrict__ xs) {
+    pdl_enter();
+    moe_gather_items<IdxT>(x, ldx, h, sorted_tok, static_cast<IdxT>(sorted_tok != nullptr ? expert_off[e] : e), rotate, vec, xs,
+                           static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+}
+
 // The whole pair sort in one launch, for pair counts where reading the pair list once per CTA is cheap (the list is
 // 64 KB at 2048 tokens x top-8 and sits in L2).  CTA c owns pairs [256 c, 256 c + 256).  Every CTA histograms ALL
 // pairs in shared memory (one shared atomic per pair), snapshotting the histogram when it reaches its own range: that
@@ -308,13 +377,22 @@ __global__ void __launch_bounds__(kSortCta) qwc_moe_sort_kernel(const int32_t* _
                                                                 int gu_rows, int dn_rows, int gu_paired, int32_t* __restrict__ expert_off,
                                                                 int32_t* __restrict__ sorted_pair, int32_t* __restrict__ sorted_tok,
                                                                 int32_t* __restrict__ inv_perm, qwc_moe_tile* __restrict__ tiles_gu,
-                                                                qwc_moe_tile* __restrict__ tiles_dn, int32_t* __restrict__ tile_counts) {
+                                                                qwc_moe_tile* __restrict__ tiles_dn, int32_t* __restrict__ tile_counts,
+                                                                int sort_blocks, const __half* __restrict__ rot_x, int64_t rot_ldx, int rot_h,
+                                                                int rot_rows, int rot_vec, __half* __restrict__ rot_out) {
     __shared__ int s_cnt[512];
     __shared__ int s_prev[512];
     __shared__ int s_off[513];
     __shared__ int s_tx[513];
     __shared__ int s_wh[kSortCta / 32][512];
     pdl_enter();
+    if (static_cast<int>(blockIdx.x) >= sort_blocks) {
+        // Passenger work: the sort keeps a few dozen CTAs busy for ~10 us; the blocks behind them rotate the tokens' rows (which
+        // does not depend on the routing) for the row-copy gather that follows, instead of a launch of their own.
+        moe_gather_items<uint32_t>(rot_x, rot_ldx, rot_h, nullptr, static_cast<uint32_t>(rot_rows), 1, rot_vec, rot_out,
+                                   static_cast<int>(blockIdx.x) - sort_blocks, static_cast<int>(gridDim.x) - sort_blocks);
+        return;
+    }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lo = blockIdx.x * kSortCta;
     for (int i = tid; i < e; i += kSortCta) s_cnt[i] = 0;
@@ -383,7 +461,7 @@ __global__ void __launch_bounds__(kSortCta) qwc_moe_sort_kernel(const int32_t* _
         }
     }
     // tile lists: weight tiles fastest inside an activation tile, so consecutive tiles re-read the same activations
-    for (int ex = blockIdx.x; ex < e && (tiles_gu != nullptr || tiles_dn != nullptr); ex += gridDim.x) {
+    for (int ex = blockIdx.x; ex < e && (tiles_gu != nullptr || tiles_dn != nullptr); ex += sort_blocks) {
         const int cnt = s_cnt[ex], ntx = s_tx[ex + 1] - s_tx[ex];
         for (int which = 0; which < 2; ++which) {
             const int rows = which == 0 ? gu_rows : dn_rows;
@@ -464,68 +542,6 @@ __global__ void __launch_bounds__(512) qwc_moe_decode_plan_kernel(const int32_t*
     for (int j = 0; j < ndn; ++j) {
         MoeSeg sg{ex * h, j * cols_dn, min(cols_dn, h - j * cols_dn), x0, min(cnt, 8), 0, 0, 0};
         segs_dn[before * ndn + j] = sg;
-    }
-}
-
-// xs[p, :] = rot(x[sorted_tok[p], :]).  A quad handles one (sorted row, 32-element unit): lane t holds elements
-// 8t..8t+7 (one 16-byte load), rotates with three in-lane butterfly stages and two xor-shuffle stages (the
-// reference's h = 1, 2, 4, 8, 16 order) and writes one 16-byte chunk.  vec != 0 needs 16-byte aligned rows.
-// IdxT = uint32_t while pairs * units fits (the item index is divided per item: 32-bit division is several times cheaper).
-// sorted_tok == nullptr: rows in place (row p of the output is row p of x), `e` rows in all: the rotate-once pre-pass of
-// the row-copy form below.
-template <typename IdxT>
-__global__ void __launch_bounds__(256) qwc_moe_gather_kernel(const __half* __restrict__ x, int64_t ldx, int h,
-                                                             const int32_t* __restrict__ sorted_tok,
-                                                             const int32_t* __restrict__ expert_off, int e, int rotate, int vec,
-                                                             __half* __restrict__ xs) {
-    pdl_enter();
-    const int lane = threadIdx.x & 31, t4 = lane & 3, q8 = lane >> 2;
-    const int units = h / 32;
-    const IdxT total = static_cast<IdxT>(sorted_tok != nullptr ? expert_off[e] : e) * static_cast<IdxT>(units);
-    const IdxT step = static_cast<IdxT>(gridDim.x) * (blockDim.x >> 5) * 8;
-    for (IdxT base = (static_cast<IdxT>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 8; base < total; base += step) {
-        const IdxT it = base + q8;
-        const bool live = it < total;
-        const IdxT prq = live ? it / static_cast<IdxT>(units) : 0;
-        const int u = live ? static_cast<int>(it - prq * static_cast<IdxT>(units)) : 0;
-        const int64_t pr = static_cast<int64_t>(prq);
-        const __half* src = x + static_cast<int64_t>(live ? (sorted_tok != nullptr ? sorted_tok[pr] : static_cast<int32_t>(pr)) : 0) * ldx + u * 32 + 8 * t4;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (live) {
-            if (vec) raw = *reinterpret_cast<const uint4*>(src);
-            else {
-                __half tmp[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) tmp[i] = src[i];
-                raw = *reinterpret_cast<const uint4*>(tmp);
-            }
-        }
-        if (rotate) {
-            __half2 hv[4] = {*reinterpret_cast<__half2*>(&raw.x), *reinterpret_cast<__half2*>(&raw.y),
-                             *reinterpret_cast<__half2*>(&raw.z), *reinterpret_cast<__half2*>(&raw.w)};
-            float f[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(hv[i]); f[2 * i + 1] = __high2float(hv[i]); }
-#pragma unroll
-            for (int s = 1; s < 8; s <<= 1)
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if ((i & s) == 0) {
-                        const float a = f[i], b = f[i + s];
-                        f[i] = __fadd_rn(a, b);
-                        f[i + s] = __fsub_rn(a, b);
-                    }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 1, (t4 & 1) != 0);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = fwht_xor_stage(f[i], 2, (t4 & 2) != 0);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                hv[i] = __floats2half2_rn(__fmul_rn(f[2 * i], qwc_inv_sqrt32()), __fmul_rn(f[2 * i + 1], qwc_inv_sqrt32()));
-            raw = make_uint4(*reinterpret_cast<uint32_t*>(&hv[0]), *reinterpret_cast<uint32_t*>(&hv[1]),
-                             *reinterpret_cast<uint32_t*>(&hv[2]), *reinterpret_cast<uint32_t*>(&hv[3]));
-        }
-        if (live) *reinterpret_cast<uint4*>(xs + pr * h + u * 32 + 8 * t4) = raw;
     }
 }
 
@@ -769,11 +785,34 @@ int qwc_moe_route(qwc_hal* hal, qwc_stream stream, const float* logits, int64_t 
     return QWC_OK;
 }
 
+// A rotation job that rides on the sort launch (see qwc_moe_sort_kernel): out[r, :] = rot(x[r, :]) for `rows` rows of h.
+struct MoeRotateJob {
+    const __half* x;
+    int64_t ldx;
+    int h, rows, vec;
+    __half* out;
+};
+static int moe_group_pairs_impl(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int64_t pairs, int64_t e, int64_t k,
+                                int32_t* expert_off, int32_t* sorted_pair, int32_t* sorted_tok, int32_t* inv_perm,
+                                int64_t gu_rows, int64_t dn_rows, int32_t gu_epilogue, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
+                                int32_t* tile_counts, const MoeRotateJob* rot, bool* rot_done);
+
 int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int64_t pairs, int64_t e, int64_t k,
                         int32_t* expert_off, int32_t* sorted_pair, int32_t* sorted_tok, int32_t* inv_perm,
                         int64_t gu_rows, int64_t dn_rows, int32_t gu_epilogue, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
                         int32_t* tile_counts) {
+    return moe_group_pairs_impl(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, gu_rows, dn_rows,
+                                gu_epilogue, tiles_gu, tiles_dn, tile_counts, nullptr, nullptr);
+}
+
+// rot != nullptr: the one-launch sort also carries the rotation job; *rot_done says whether it did (the three-pass sort of long
+// pair lists does not).
+static int moe_group_pairs_impl(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int64_t pairs, int64_t e, int64_t k,
+                                int32_t* expert_off, int32_t* sorted_pair, int32_t* sorted_tok, int32_t* inv_perm,
+                                int64_t gu_rows, int64_t dn_rows, int32_t gu_epilogue, qwc_moe_tile* tiles_gu, qwc_moe_tile* tiles_dn,
+                                int32_t* tile_counts, const MoeRotateJob* rot, bool* rot_done) {
     qwc_clear_error();
+    if (rot_done) *rot_done = false;
     const int paired = gu_epilogue != QWC_EPI_NONE;
     if (paired && gu_rows % kTileW != 0)
         return qwc_fail(QWC_ERR_BAD_GEOMETRY, "a SwiGLU epilogue needs inter %% 64 == 0, got gate||up rows = %lld", (long long)gu_rows);
@@ -788,10 +827,14 @@ int qwc_moe_group_pairs(qwc_hal* hal, qwc_stream stream, const int32_t* idx, int
         int grid = static_cast<int>(pairs > 0 ? (pairs + kSortCta - 1) / kSortCta : 1);
         // the tile lists are written expert by expert, experts dealt over the CTAs: a short pair list still gets 32 CTAs for that
         if ((tiles_gu != nullptr || tiles_dn != nullptr) && grid < 32 && grid < e) grid = static_cast<int>(e < 32 ? e : 32);
-        QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_sort_kernel, dim3(grid), dim3(kSortCta), 0, st, idx, static_cast<int>(pairs),
+        const int rot_blocks = rot != nullptr ? grid_for(hal, static_cast<int64_t>(rot->rows) * (rot->h / 32), 64, 16) : 0;
+        QWC_CUDA_TRY(qwc_launch_pdl(qwc_moe_sort_kernel, dim3(grid + rot_blocks), dim3(kSortCta), 0, st, idx, static_cast<int>(pairs),
                                     static_cast<int>(e), static_cast<int>(k), moe_tile_rows(pairs, e), static_cast<int>(gu_rows),
                                     static_cast<int>(dn_rows), paired, expert_off, sorted_pair, sorted_tok, inv_perm, tiles_gu, tiles_dn,
-                                    tile_counts));
+                                    tile_counts, grid, rot != nullptr ? rot->x : static_cast<const __half*>(nullptr),
+                                    rot != nullptr ? rot->ldx : int64_t(0), rot != nullptr ? rot->h : 0, rot != nullptr ? rot->rows : 0,
+                                    rot != nullptr ? rot->vec : 0, rot != nullptr ? rot->out : static_cast<__half*>(nullptr)));
+        if (rot_done) *rot_done = rot != nullptr;
         return QWC_OK;
     }
     // larger lists: three passes, one warp per expert.
@@ -1024,12 +1067,21 @@ int qwc_moe_forward(qwc_hal* hal, qwc_stream stream, const qwc_weight_view* bank
     }
     // SwiGLU + FWHT run in the gate/up GEMM's epilogue when the tiles can pair 64 gate rows with their up rows
     const int32_t gu_epi = inter % 64 == 0 ? QWC_EPI_SILU_PAIR_FWHT : QWC_EPI_NONE;
-    if ((rc = qwc_moe_group_pairs(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h, gu_epi,
-                                  tiles_gu, tiles_dn, tile_counts))) return rc;
-    // the gate/up region of the scratch is idle until the gate/up GEMM writes it (never, with the fused epilogue): it holds the
-    // rotated copy of x that the row-copy gather reads
-    if ((rc = moe_gather_impl(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs, t, sc + L.gu,
-                              static_cast<size_t>(pairs) * 2 * inter * 2))) return rc;
+    // The gate/up region of the scratch is idle until the gate/up GEMM writes it (never, with the fused epilogue): it holds the
+    // rotated copy of x that the row-copy gather reads.  The rotation rides on the sort launch when it can.
+    const size_t tmp_bytes = static_cast<size_t>(pairs) * 2 * inter * 2;
+    MoeRotateJob rot{static_cast<const __half*>(x_f16), ldx, static_cast<int>(h), static_cast<int>(t),
+                     reinterpret_cast<uintptr_t>(x_f16) % 16 == 0 && ldx % 8 == 0, reinterpret_cast<__half*>(sc + L.gu)};
+    const bool want_rot = !x_is_rotated && k > 1 && h % 32 == 0 && tmp_bytes >= static_cast<size_t>(t) * h * 2 && t * (h / 32) < (1ll << 31);
+    bool rotated_here = false;
+    if ((rc = moe_group_pairs_impl(hal, stream, idx, pairs, e, k, expert_off, sorted_pair, sorted_tok, inv_perm, 2 * inter, h, gu_epi,
+                                   tiles_gu, tiles_dn, tile_counts, want_rot ? &rot : nullptr, &rotated_here))) return rc;
+    if (rotated_here) {
+        if ((rc = moe_gather_impl(hal, stream, sc + L.gu, h, h, sorted_tok, expert_off, e, pairs, 1, sc + L.xs, 0, nullptr, 0))) return rc;
+    } else if ((rc = moe_gather_impl(hal, stream, x_f16, ldx, h, sorted_tok, expert_off, e, pairs, x_is_rotated, sc + L.xs, t, sc + L.gu,
+                                     tmp_bytes))) {
+        return rc;
+    }
     const int32_t xrows = qwc_moe_tile_rows(pairs, e);
     if (gu_epi != QWC_EPI_NONE) {
         if ((rc = qwc_moe_grouped_gemm(hal, stream, bank_gu, sc + L.xs, pairs, tiles_gu, tile_counts, qwc_moe_max_tiles(pairs, e, 2 * inter),
