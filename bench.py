@@ -570,8 +570,9 @@ def bench_moe(q, hal, peaks):
             "weight_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1), "frac_of_hbm_peak": round(wbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
             "decode_T8_us": round(ms8 * 1e3, 1),
             "bound": "the HBM roof (503 MB of expert weights: ~78 us) and the tensor roof (~65 us) are close; neither binds yet: with ~64 "
-                     "tokens per expert every decoded 128 x 64 weight tile feeds one short MMA, so the converters' decode and their "
-                     "hand-offs to the MMA warp set the pace (~0.2 us per 64-wide K step per SM)"}
+                     "tokens per expert every decoded 128 x 64 weight tile feeds one short MMA, and the MMA warp's turn per operand "
+                     "stage (barrier wait, fences, eight short MMAs, commit: ~0.4 us per 128 k per SM, with the copies into shared "
+                     "memory on its critical path) sets the pace, not the decode"}
 
 
 def _max_rel_and_cos(a, b):
